@@ -1,0 +1,273 @@
+#!/usr/bin/env python
+"""Benchmark of the sampling hot path: sampled edges/s, device-timed.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A "step" is one sample() pass over the whole batch of walks.  Default workload (one GPU):
+node2vec p=2 q=0.5, length 100, one walk per vertex, on a synthetic R-MAT graph with 2^20
+vertices and 16M undirected edges (seed 0, generated on the device).  With N ranks every rank
+holds a replica of the graph and samples its own range of seeds (weak scaling: rank r walks the
+samples [r*V, (r+1)*V), sample i starting at vertex i % V); no collective is on the data path.
+
+Prints ONE JSON line (rank 0).  --impl reference times the reference's own next() bodies on the
+host cores (oracle/_ref, else the oracle port) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (app, V, M undirected, steps, params)
+    "c1": dict(app=0, V=56944, M=400_000, steps=100, desc="uniform walk, 56,944 vertices, ~800K CSR entries"),
+    "c2": dict(app=3, V=1 << 20, M=1 << 24, steps=100, desc="node2vec p=2 q=0.5, 2^20 vertices, 16M undirected edges"),
+    "c2u": dict(app=0, V=1 << 20, M=1 << 24, steps=100, desc="uniform walk on the c2 graph"),
+    "c2d": dict(app=1, V=1 << 20, M=1 << 24, steps=100, desc="DeepWalk (weighted rejection) on the c2 graph"),
+    "c5": dict(app=2, V=1 << 24, M=1 << 28, steps=100, stop_prob=0.15, desc="weighted PPR stop 0.15, 2^24 vertices, 256M undirected edges"),
+    "c5s": dict(app=2, V=1 << 22, M=1 << 26, steps=100, stop_prob=0.15, desc="weighted PPR stop 0.15, 2^22 vertices, 64M undirected edges"),
+}
+APP_NAMES = {0: "uniform_walk", 1: "deepwalk", 2: "ppr", 3: "node2vec"}
+MODES = {"tp": 0, "tp_lb": 1, "sp": 2}
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self.stop_flag = index, [], False
+
+    def run(self):
+        while not self.stop_flag:
+            try:
+                r = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                   capture_output=True, text=True, timeout=5)
+                if r.returncode == 0 and r.stdout.strip():
+                    self.rows.append([x.strip() for x in r.stdout.strip().split(",")])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        sm = sorted(int(float(r[0])) for r in self.rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(float(self.rows[0][1])), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def next_bytes(app, st, steps, S):
+    """Algorithmic bytes the next() launches of one sample() move, from the device's own event
+    counters: per live pair 8 B map-in + 8 B row offsets; per sampled edge 4 B neighbour + 4 B
+    output; 8 B map-out per pair of every step but the last; weighted apps + 4 B max weight per
+    next() and 4 B per weight read; node2vec + 4 B load and 4 B store of the previous vertex,
+    8 B for its row, and per try 4 B candidate + 4 B per binary-search probe."""
+    pairs, edges = st["live_pairs"], st["sampled_edges"]
+    b = 16 * pairs + 8 * edges + 8 * pairs * (steps - 1) / steps
+    if app in (1, 2):
+        b += 4 * pairs + 4 * st["weight_tries"]
+    if app == 3:
+        b += 16 * pairs + 4 * st["n2v_tries"] + 4 * st["n2v_probes"]
+    return b
+
+
+def cpu_baseline(hg, wl, seed, budget_s=12.0):
+    """The reference's own next() bodies (oracle/_ref) where built, else the oracle port, on all
+    host threads, on a bounded sample of the workload's walks."""
+    from oracle import ndo
+    app, steps = wl["app"], wl["steps"]
+    use_ref = ndo.ref_available() and not (app == 2 and abs(wl.get("stop_prob", 0.01) - 0.01) > 1e-9)
+    pr = ndo.make_params(app, steps=steps, seed=seed, stop_prob=wl.get("stop_prob", 0.01))
+    threads = ndo.ref().ref_max_threads() if use_ref else ndo.lib().ndo_max_threads()
+
+    def run(n):
+        t0 = time.perf_counter()
+        if use_ref:
+            e = ndo.ref_sample(hg, app, steps, n, seed=seed)["sampled_edges"]
+        else:
+            e = ndo.sample(hg, pr, n, want_adj=False)["counters"]["sampled_edges"]
+        return e, time.perf_counter() - t0
+
+    n = min(hg.V, 20000)
+    e, t = run(n)
+    n2 = int(min(hg.V, max(n, n * budget_s / max(t, 1e-3))))
+    if n2 > 2 * n:
+        n = n2
+        e, t = run(n)
+    return {"value": e / t, "unit": "sampled edges/s", "cores": int(threads), "kind": "reference" if use_ref else "port",
+            "sample": f"first {n} of {hg.V} walks x {steps} steps, {t:.2f} s"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--mode", default="tp_lb", choices=list(MODES))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    wl = WORKLOADS[a.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    seed = 0
+    hbm_peak, peak_kind = peaks()
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        # graph built on the host by the oracle's generator (same definition as the device one)
+        from oracle import ndo
+        t0 = time.perf_counter()
+        hg = ndo.rmat_graph(wl["V"], wl["M"], seed)
+        t_graph = time.perf_counter() - t0
+        vals = []
+        for i in range(a.warmup + a.steps):
+            cb = cpu_baseline(hg, wl, seed, budget_s=8.0)
+            if i >= a.warmup:
+                vals.append(cb)
+        v = float(np.mean([c["value"] for c in vals]))
+        cb = dict(vals[-1], value=v)
+        print(json.dumps({
+            "impl": "reference", "metric": "sampled edges/sec", "value": v, "unit": "sampled edges/s", "n_gpus": a.gpus,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+            "config": {"workload": f"{a.workload}: {wl['desc']}", "graph_build_s": round(t_graph, 2)},
+            "cpu_baseline": cb, "e2e": {"value": v, "unit": "sampled edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch
+    from nextdoor_b200 import api as nd
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    V, M, steps, app = wl["V"], wl["M"], wl["steps"], wl["app"]
+    mode = MODES[a.mode]
+    g = nd.Graph.rmat(V, M, seed, device=local)
+    pr = nd.app_params(app, steps=steps, seed=seed, stop_prob=wl.get("stop_prob", 0.01))
+    S = V
+    first = rank * S
+    smp = nd.Sampler(g, pr, num_samples=S, first_sample=first)
+    stream = torch.cuda.current_stream()
+    smp.set_stream(stream.cuda_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed throughput (inputs resident)
+    for _ in range(a.warmup):
+        smp.sample(mode, sync=False)
+    barrier()
+    clocks = ClockSampler(local)
+    clocks.start()
+    l0 = nd.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(a.steps):
+        smp.sample(mode, sync=False)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = nd.launch_count() - l0
+    st = smp.stats()
+    edges_step = st["sampled_edges"]
+
+    # ---- end to end through the public API with host buffers: seeds H2D, sample, result D2H
+    init_host = torch.from_numpy(((np.arange(first, first + S) % V).astype(np.int32))).pin_memory()
+    out_host = torch.empty(S * steps, dtype=torch.int32).pin_memory()
+    init_np, out_np = init_host.numpy(), out_host.numpy()
+    for _ in range(2):
+        smp.set_initial(init_np)
+        smp.sample(mode, sync=False)
+        smp.final_samples(out_np)
+    barrier()
+    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    x0.record(stream)
+    for _ in range(a.steps):
+        smp.set_initial(init_np)
+        smp.sample(mode, sync=False)
+        smp.final_samples(out_np)
+    x1.record(stream)
+    barrier()
+    clocks.stop_flag = True
+    ms_e2e = x0.elapsed_time(x1)
+
+    # ---- per-phase device time of one instrumented pass (roofline of the next() kernel)
+    smp.set_profiling(True)
+    smp.sample(mode)
+    ph = smp.phase_ms()
+    smp.set_profiling(False)
+    st = smp.stats()
+
+    tms = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
+    tot = torch.tensor([float(edges_step)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    ms, ms_e2e = float(tms[0]), float(tms[1])
+    total_edges = float(tot[0])
+
+    if rank == 0:
+        nb = next_bytes(app, st, steps, S)
+        next_ms, next_launches = ph["next"]
+        achieved = nb / (next_ms * 1e-3) / 1e9 if next_ms > 0 else 0.0
+        cb = None
+        if world == 1 and not a.no_cpu_baseline:
+            from oracle import ndo
+            row_ptr, col, w, mw = g.to_host()
+            cb = cpu_baseline(ndo.HostGraph(row_ptr, col, w, mw), wl, seed)
+        line = {
+            "metric": "sampled edges/sec", "value": total_edges * a.steps / (ms * 1e-3), "unit": "sampled edges/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+            "config": {"workload": f"{a.workload}: {wl['desc']}", "app": APP_NAMES[app], "mode": a.mode,
+                       "samples_per_gpu": S, "walk_length": steps, "graph": f"R-MAT a=.57 b=.19 c=.19 d=.05 seed 0, V={V}, CSR entries={g.E}, max degree={g.max_degree}",
+                       "l2": "working set (graph + walk buffers) larger than L2; no flush between steps",
+                       "sampled_edges_per_step_per_gpu": edges_step},
+            "e2e": {"value": total_edges * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
+                    "h2d_bytes_per_step": int(S * 4), "d2h_bytes_per_step": int(S * steps * 4)},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "walk_next_tp_kernel" if mode != 2 else "walk_sp_kernel",
+                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "peak_kind": f"of {peak_kind}", "traffic": None, "launches": next_launches,
+                         "avg_launch_us": 1e3 * next_ms / max(next_launches, 1), "algorithmic_bytes_per_pass": nb},
+            "phases_ms": {k: round(v[0], 4) for k, v in ph.items()},
+            "cpu_baseline": cb,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

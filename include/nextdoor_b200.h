@@ -1,0 +1,171 @@
+/*
+ * nextdoor_b200.h -- C ABI of the B200-native NextDoor sampling engine (libnextdoor_b200.so).
+ *
+ * Plain pointers and sizes only.  Every function returns an nd_status (0 = ND_OK); the text of
+ * the last failure on the calling thread is available through nd_last_error().  The library
+ * never aborts and has no CPU fallback: without a CUDA device every compute call fails with
+ * ND_ERR_CUDA.
+ *
+ * Each entry point names the piece of the reference (plasma-umass/NextDoor, paths relative to
+ * its tree) that it replaces.
+ */
+#ifndef NEXTDOOR_B200_H
+#define NEXTDOOR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum nd_status {
+  ND_OK = 0,
+  ND_ERR_ARG = 1,     /* bad argument (null pointer, size out of range, unknown app) */
+  ND_ERR_CUDA = 2,    /* a CUDA runtime call failed */
+  ND_ERR_IO = 3,      /* file not found / short read */
+  ND_ERR_RANGE = 4,   /* vertex or edge count does not fit int32 (src/csr.hpp:6-8) */
+  ND_ERR_DEVICE = 5,  /* a kernel reported a problem through the device status word */
+  ND_ERR_STATE = 6    /* call order violated (e.g. final samples before sample) */
+} nd_status;
+
+/* Built-in applications: the App structs of the reference, same sampling rule each. */
+typedef enum nd_app {
+  ND_APP_UNIFORM_WALK = 0,  /* UniformRandomWalkApp, example/uniformRandWalk.cu:15-93 */
+  ND_APP_DEEPWALK = 1,      /* DeepWalkApp, src/apps/randomwalks/randomWalks.cu:65-91 */
+  ND_APP_PPR = 2,           /* PPRApp, src/apps/randomwalks/randomWalks.cu:93-125 */
+  ND_APP_NODE2VEC = 3,      /* Node2VecApp, src/apps/randomwalks/randomWalks.cu:132-173 */
+  ND_APP_KHOP = 4,          /* KHopApp, src/apps/khop/khop.cu:1-77 (with replacement) */
+  ND_APP_KHOP_DISTINCT = 5, /* no counterpart: without replacement, then distinct per hop
+                               (semantics of src/distinct.cuh:45-111) */
+  ND_APP_FASTGCN_REF = 6,   /* FastGCNSamplingApp, src/apps/fastgcn/fastgcnSampling.cu:15-100 */
+  ND_APP_LADIES_REF = 7,    /* ImportanceSampleApp, src/apps/ladies/ladiessampling.cu:15-100 */
+  ND_APP_FASTGCN_IS = 8,    /* no counterpart: importance ~ degree^2 over the neighbour union */
+  ND_APP_LADIES_IS = 9      /* no counterpart: importance ~ sum of squared row-normalised weights */
+} nd_app;
+
+/* kernelType + load-balancing flag of nextdoor<>() (src/nextdoor.cu:3239-3243, src/main.cu:21-29) */
+typedef enum nd_mode {
+  ND_MODE_TRANSIT_PARALLEL = 0,    /* "TransitParallel", -l off: no bins */
+  ND_MODE_TRANSIT_PARALLEL_LB = 1, /* "TransitParallel", -l on: sub-warp / block / grid bins */
+  ND_MODE_SAMPLE_PARALLEL = 2      /* "SampleParallel" (what the Python sample() runs) */
+} nd_mode;
+
+#define ND_MAX_STEPS_FANOUT 8
+
+/* The compile-time constants of the reference's App structs, as run-time parameters. */
+typedef struct nd_app_params {
+  int32_t app;     /* nd_app */
+  int32_t steps;   /* App::steps(): walk length / hops / layers */
+  int32_t fanout[ND_MAX_STEPS_FANOUT]; /* App::stepSize(k) for k-hop; layer size in [0] for collective apps */
+  int32_t batch;   /* App::initialSampleSize() of the collective apps (VERTICES_PER_SAMPLE) */
+  int32_t n2v_ref_compat; /* 1: keep the index-vs-vertex comparison of randomWalks.cu:159; 0: compare vertices */
+  float p, q;      /* node2vec (randomWalks.cu:149-150) */
+  float stop_prob; /* PPR walkEndProb (randomWalks.cu:105) */
+  uint64_t seed;   /* Philox key; draws are keyed by (seed, global sample index, step, slot, draw) */
+} nd_app_params;
+
+typedef struct nd_graph nd_graph;     /* CSR replica resident on one device */
+typedef struct nd_sampler nd_sampler; /* NextDoorData<SampleType,App> of one device (src/libNextDoor.hpp:13-37) */
+
+const char *nd_last_error(void);
+int nd_version(void);
+/* number of CUDA devices visible, 0 when there is none (never fails) */
+int nd_device_count(void);
+/* kernels launched by the library in this process so far (all devices, all handles) */
+int64_t nd_launch_count(void);
+
+/* ------------------------------------------------------------------ graph */
+
+/* transferCSRToGPUs / copyPartitionToGPU (src/nextdoor.cu:1893-1911, src/utils.hpp:378-395):
+ * upload a host CSR.  row_ptr has V+1 entries with exclusive ends; max_w may be NULL (computed
+ * on the device as Vertex::max_weight does, src/graph.hpp:71-80). */
+int nd_graph_from_csr(int device, int32_t V, int64_t E, const int32_t *row_ptr, const int32_t *col,
+                      const float *w, const float *max_w, nd_graph **out);
+/* Graph::load_from_edge_list_binary + csr_from_graph (src/graph.hpp:106-159, src/csr.hpp:399-424),
+ * done on the device: n 12-byte records {int32 src, int32 dst, float32 w} in host memory are
+ * sorted by (src, dst, w) with the library's radix sort; vertex count = max id + 1; duplicates kept. */
+int nd_graph_from_edge_records(int device, int64_t n, const void *records, nd_graph **out);
+/* loadGraph(file, "edge-list", "binary") (src/nextdoor.cu:1845-1891) */
+int nd_graph_load_edge_list_binary(int device, const char *path, nd_graph **out);
+/* Synthetic R-MAT graph (a,b,c,d)=(.57,.19,.19,.05) generated and built on the device: M
+ * undirected edges, both directions stored, weights uniform [1,5).  Stands in for the graph
+ * files the reference's tests read (src/tests/testBase.h:6-12). */
+int nd_graph_rmat(int device, int32_t V, int64_t M, uint64_t seed, nd_graph **out);
+int nd_graph_info(const nd_graph *g, int32_t *V, int64_t *E, int32_t *max_degree, int *device);
+/* copies to host buffers; any pointer may be NULL */
+int nd_graph_to_host(const nd_graph *g, int32_t *row_ptr, int32_t *col, float *w, float *max_w);
+/* device addresses of the replica (GPUCSRPartition, src/csr.hpp:387-393) */
+int nd_graph_device_ptrs(const nd_graph *g, const int32_t **row_ptr, const int32_t **col,
+                         const float **w, const float **max_w);
+int nd_graph_destroy(nd_graph *g);
+/* create_csr_partitions (src/graph_partitioner.cuh:1-173): contiguous vertex ranges under a byte
+ * budget (16 B per vertex record, 4 B per edge); boundaries are found on the device. */
+int nd_graph_partition(const nd_graph *g, int64_t budget_bytes, int32_t max_parts, int32_t *first_v,
+                       int32_t *last_v, int64_t *first_e, int64_t *last_e, int32_t *n_parts);
+
+/* ------------------------------------------------------------------ sampler */
+
+/* App::steps/stepSize folded as getFinalSampleSize (src/nextdoor.cu:1913-1929) */
+int nd_final_sample_size(const nd_app_params *p);
+int nd_initial_sample_size(const nd_app_params *p);
+/* PartStartPointer / PartDivisionSize (src/utils.hpp:26-27): samples of part `idx` of `parts` */
+int nd_shard_range(int64_t total, int idx, int parts, int64_t *first, int64_t *count);
+
+/* allocNextDoorDataOnGPU (src/nextdoor.cu:1931-2086) for this device's shard: samples
+ * [first_sample, first_sample + num_samples) of the job.  `initial` (host, num_samples *
+ * initialSampleSize transits) may be NULL: then App::initialSample of the reference app is used
+ * (sample i starts at vertex i % V; collective batches take consecutive ids). */
+int nd_sampler_create(const nd_graph *g, const nd_app_params *p, int64_t num_samples,
+                      int64_t first_sample, const int32_t *initial, nd_sampler **out);
+/* replaces the initial transits (host pointer) without reallocating: one H2D copy + map set-up */
+int nd_sampler_set_initial(nd_sampler *s, const int32_t *initial);
+/* run on the caller's stream (a cudaStream_t); NULL = the legacy default stream */
+int nd_sampler_set_stream(nd_sampler *s, void *stream);
+/* doTransitParallelSampling / doSampleParallelSampling (src/nextdoor.cu:2191-3006, 3009-3209).
+ * Asynchronous on the sampler's stream. */
+int nd_sampler_sample(nd_sampler *s, int mode);
+/* waits for the stream, checks the device status word */
+int nd_sampler_sync(nd_sampler *s);
+/* getFinalSamples (src/nextdoor.cu:3211-3237): D2H into `out` (num_samples * finalSampleSize) */
+int nd_sampler_final_samples(nd_sampler *s, int32_t *out);
+/* zero-copy variant: device address of the same array */
+int nd_sampler_final_samples_device(nd_sampler *s, const int32_t **out);
+/* collective apps: adjacency rows/cols (num_samples*steps*max(batch,L)*L each) and, for the
+ * importance apps, the probability of every sampled vertex; k-hop distinct: per-hop counts */
+int nd_sampler_aux(nd_sampler *s, int32_t *adj_row, int32_t *adj_col, float *prob, int32_t *hop_counts);
+/* counters of the last sample(): [0] sampled edges (valid vertices written), [1] live
+ * (transit,sample) pairs summed over steps, [2] weight reads of the rejection loops, [3] node2vec
+ * tries, [4] node2vec binary-search probes, [5] neighbour ids gathered for collective unions,
+ * [6] unique candidates; n <= 8 */
+int nd_sampler_stats(nd_sampler *s, int64_t *stats, int n);
+/* per-phase device time of the last sample() when profiling is on: see nd_phase */
+typedef enum nd_phase {
+  ND_PHASE_NEXT = 0, ND_PHASE_INVERT = 1, ND_PHASE_BIN = 2, ND_PHASE_FINALIZE = 3,
+  ND_PHASE_DEDUP = 4, ND_PHASE_COLLECT = 5, ND_PHASE_COUNT = 6
+} nd_phase;
+int nd_sampler_set_profiling(nd_sampler *s, int on);
+int nd_sampler_phase_ms(nd_sampler *s, float *ms, int32_t *launches, int n);
+/* freeDeviceData (src/nextdoor.cu:2088-2115) */
+int nd_sampler_destroy(nd_sampler *s);
+
+/* ------------------------------------------------------------------ single operators (device pointers) */
+
+/* The map inversion of the step loop: cub::DeviceRadixSort::SortPairs + invalidVertexStartPos
+ * (src/nextdoor.cu:2930-2933, 1804-1836).  Stable sort of n (key,val) pairs by key; pairs whose
+ * key equals `invalid` are dropped.  All pointers are device pointers on `device`; keys_in/vals_in
+ * are clobbered.  *n_live_out (host) receives the surviving count. */
+int nd_invert_map(int device, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t invalid,
+                  int32_t *keys_out, int32_t *vals_out, int64_t *n_live_out);
+/* remove_duplicates_in_hop_per_block (src/distinct.cuh:1-111): every segment of seg_len ints is
+ * sorted ascending, made unique, compacted to the front and padded with `invalid`;
+ * counts (device, may be NULL) receives the unique count per segment. */
+int nd_distinct_segments(int device, int32_t *data, int64_t n_segments, int32_t seg_len,
+                         int32_t invalid, int32_t *counts);
+/* the keyed draw the kernels use, evaluated on the device for n (sample, step, slot, draw) tuples */
+int nd_philox_uniform(int device, uint64_t seed, int64_t n, const uint32_t *tuples4, float *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

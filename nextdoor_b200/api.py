@@ -1,0 +1,280 @@
+"""Host-side mirror of the reference's interface for the sampling path, over the C ABI.
+
+* `Graph` / `Sampler` follow the C++ surface of src/libNextDoor.hpp (loadGraph, transferCSRToGPUs,
+  allocNextDoorDataOnGPU, doTransitParallelSampling / doSampleParallelSampling, getFinalSamples,
+  freeDeviceData), one object per device.
+* `SamplingModule` has the five functions of the reference's per-app Python extension modules
+  (src/nextDoorPythonModule.cu:40-102): initSampling, sample, finalSamples, finalSampleLength,
+  freeDeviceMemory -- plus finalSamplesArray, which the reference exports as a C symbol for ctypes
+  (:89-93) and which returns a numpy view here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import (APP_DEEPWALK, APP_FASTGCN_IS, APP_FASTGCN_REF, APP_KHOP, APP_KHOP_DISTINCT,  # noqa: F401
+                   APP_LADIES_IS, APP_LADIES_REF, APP_NODE2VEC, APP_PPR, APP_UNIFORM_WALK,
+                   MODE_SAMPLE_PARALLEL, MODE_TRANSIT_PARALLEL, MODE_TRANSIT_PARALLEL_LB, AppParams,
+                   NdError, check, lib)
+
+KERNEL_TYPES = {"TransitParallel": MODE_TRANSIT_PARALLEL, "SampleParallel": MODE_SAMPLE_PARALLEL}
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def app_params(app, steps=None, fanout=None, batch=64, p=2.0, q=0.5, stop_prob=0.01, seed=0,
+               n2v_ref_compat=1) -> AppParams:
+    """Defaults are the reference's compile-time constants: 100-step walks (randomWalks.cu:4),
+    fan-out 25 then 10 (khop.cu:3-8), 5 layers x 64 with batches of 64 (fastgcnSampling.cu:1-4),
+    p=2, q=0.5 (randomWalks.cu:149-150), walkEndProb 0.01 (randomWalks.cu:105)."""
+    pr = AppParams()
+    pr.app = app
+    if app <= APP_NODE2VEC:
+        pr.steps = 100 if steps is None else steps
+        pr.fanout[0] = 1
+    elif app in (APP_KHOP, APP_KHOP_DISTINCT):
+        fan = list(fanout) if fanout is not None else [25, 10]
+        pr.steps = len(fan) if steps is None else steps
+        for i, f in enumerate(fan[:_lib.MAX_FANOUT]):
+            pr.fanout[i] = f
+    else:
+        pr.steps = 5 if steps is None else steps
+        pr.fanout[0] = 64 if fanout is None else (fanout if isinstance(fanout, int) else fanout[0])
+    pr.batch = batch
+    pr.p, pr.q, pr.stop_prob = p, q, stop_prob
+    pr.seed = seed
+    pr.n2v_ref_compat = n2v_ref_compat
+    return pr
+
+
+def final_sample_size(params: AppParams) -> int:
+    return int(lib.nd_final_sample_size(C.byref(params)))
+
+
+def initial_sample_size(params: AppParams) -> int:
+    return int(lib.nd_initial_sample_size(C.byref(params)))
+
+
+def launch_count() -> int:
+    """Kernels this process has launched through the library so far."""
+    return int(lib.nd_launch_count())
+
+
+def shard_range(total: int, idx: int, parts: int):
+    """PartStartPointer / PartDivisionSize of the reference (src/utils.hpp:26-27)."""
+    f, c = C.c_int64(0), C.c_int64(0)
+    check(lib.nd_shard_range(total, idx, parts, C.byref(f), C.byref(c)))
+    return f.value, c.value
+
+
+class Graph:
+    """A CSR replica in one GPU's HBM."""
+
+    def __init__(self, handle, device):
+        self._h = handle
+        self.device = device
+        V, E, md, dev = C.c_int32(0), C.c_int64(0), C.c_int32(0), C.c_int(0)
+        check(lib.nd_graph_info(self._h, C.byref(V), C.byref(E), C.byref(md), C.byref(dev)))
+        self.V, self.E, self.max_degree = V.value, E.value, md.value
+
+    @classmethod
+    def from_csr(cls, row_ptr, col, w, max_w=None, device=0):
+        row_ptr = np.ascontiguousarray(row_ptr, np.int32)
+        col = np.ascontiguousarray(col, np.int32)
+        w = np.ascontiguousarray(w, np.float32)
+        if max_w is not None:
+            max_w = np.ascontiguousarray(max_w, np.float32)
+        h = C.c_void_p()
+        check(lib.nd_graph_from_csr(device, row_ptr.shape[0] - 1, col.shape[0], _ptr(row_ptr), _ptr(col),
+                                    _ptr(w), _ptr(max_w), C.byref(h)))
+        return cls(h, device)
+
+    @classmethod
+    def from_edge_records(cls, src, dst, w, device=0):
+        rec = np.empty(len(src), dtype=[("s", "<i4"), ("d", "<i4"), ("w", "<f4")])
+        rec["s"], rec["d"], rec["w"] = src, dst, w
+        h = C.c_void_p()
+        check(lib.nd_graph_from_edge_records(device, rec.shape[0], _ptr(rec), C.byref(h)))
+        return cls(h, device)
+
+    @classmethod
+    def load(cls, path, graph_type="edge-list", graph_format="binary", device=0):
+        """loadGraph(file, type, format) of the reference (src/nextdoor.cu:1845-1891); only the
+        binary edge list (12-byte records) is read by the device loader."""
+        if graph_type != "edge-list" or graph_format != "binary":
+            raise NdError(1, f"graph_format '{graph_format}' not supported for graph_type '{graph_type}'")
+        h = C.c_void_p()
+        check(lib.nd_graph_load_edge_list_binary(device, str(path).encode(), C.byref(h)))
+        return cls(h, device)
+
+    @classmethod
+    def rmat(cls, V, M, seed=0, device=0):
+        h = C.c_void_p()
+        check(lib.nd_graph_rmat(device, V, M, seed, C.byref(h)))
+        return cls(h, device)
+
+    def to_host(self):
+        row_ptr = np.empty(self.V + 1, np.int32)
+        col = np.empty(self.E, np.int32)
+        w = np.empty(self.E, np.float32)
+        mw = np.empty(self.V, np.float32)
+        check(lib.nd_graph_to_host(self._h, _ptr(row_ptr), _ptr(col), _ptr(w), _ptr(mw)))
+        return row_ptr, col, w, mw
+
+    def partition(self, budget_bytes, max_parts=4096):
+        fv = np.zeros(max_parts, np.int32)
+        lv = np.zeros(max_parts, np.int32)
+        fe = np.zeros(max_parts, np.int64)
+        le = np.zeros(max_parts, np.int64)
+        n = C.c_int32(0)
+        check(lib.nd_graph_partition(self._h, budget_bytes, max_parts, _ptr(fv), _ptr(lv), _ptr(fe), _ptr(le), C.byref(n)))
+        k = n.value
+        return fv[:k], lv[:k], fe[:k], le[:k]
+
+    def free(self):
+        if self._h:
+            lib.nd_graph_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Sampler:
+    """NextDoorData of one device: the shard [first_sample, first_sample + num_samples) of the job."""
+
+    def __init__(self, graph: Graph, params: AppParams, num_samples=None, first_sample=0, initial=None):
+        self.graph = graph
+        self.params = params
+        self.fs = final_sample_size(params)
+        self.isz = initial_sample_size(params)
+        if num_samples is None:
+            num_samples = graph.V
+        self.S = int(num_samples)
+        self.first = int(first_sample)
+        if initial is not None:
+            initial = np.ascontiguousarray(initial, np.int32)
+            assert initial.size == self.S * self.isz, "initialSampleSize mismatch"
+        h = C.c_void_p()
+        check(lib.nd_sampler_create(graph._h, C.byref(params), self.S, self.first, _ptr(initial), C.byref(h)))
+        self._h = h
+
+    def set_initial(self, initial):
+        initial = np.ascontiguousarray(initial, np.int32)
+        assert initial.size == self.S * self.isz
+        check(lib.nd_sampler_set_initial(self._h, _ptr(initial)))
+
+    def set_stream(self, stream_ptr):
+        check(lib.nd_sampler_set_stream(self._h, C.c_void_p(stream_ptr)))
+
+    def sample(self, mode=MODE_TRANSIT_PARALLEL_LB, sync=True):
+        check(lib.nd_sampler_sample(self._h, mode))
+        if sync:
+            check(lib.nd_sampler_sync(self._h))
+
+    def sync(self):
+        check(lib.nd_sampler_sync(self._h))
+
+    def final_samples(self, out=None):
+        if out is None:
+            out = np.empty(self.S * self.fs, np.int32)
+        check(lib.nd_sampler_final_samples(self._h, _ptr(out)))
+        return out.reshape(self.S, self.fs)
+
+    def final_samples_device_ptr(self):
+        p = C.c_void_p()
+        check(lib.nd_sampler_final_samples_device(self._h, C.byref(p)))
+        return p.value
+
+    def aux(self):
+        L, B = self.params.fanout[0], self.params.batch
+        collective = self.params.app >= APP_FASTGCN_REF
+        adj_row = adj_col = prob = hop = None
+        if collective:
+            n = self.S * self.params.steps * max(L, B) * L
+            adj_row = np.empty(n, np.int32)
+            adj_col = np.empty(n, np.int32)
+            prob = np.zeros(self.S * self.fs, np.float32)
+        if self.params.app == APP_KHOP_DISTINCT:
+            hop = np.zeros(self.S * self.params.steps, np.int32)
+        check(lib.nd_sampler_aux(self._h, _ptr(adj_row), _ptr(adj_col), _ptr(prob), _ptr(hop)))
+        return dict(adj_row=adj_row, adj_col=adj_col, prob=prob, hop_counts=hop)
+
+    def stats(self):
+        st = np.zeros(8, np.int64)
+        check(lib.nd_sampler_stats(self._h, _ptr(st), 8))
+        return dict(sampled_edges=int(st[0]), live_pairs=int(st[1]), weight_tries=int(st[2]),
+                    n2v_tries=int(st[3]), n2v_probes=int(st[4]), union_ids=int(st[5]), union_unique=int(st[6]))
+
+    def set_profiling(self, on=True):
+        check(lib.nd_sampler_set_profiling(self._h, int(on)))
+
+    def phase_ms(self):
+        ms = np.zeros(len(_lib.PHASES), np.float32)
+        ln = np.zeros(len(_lib.PHASES), np.int32)
+        check(lib.nd_sampler_phase_ms(self._h, _ptr(ms), _ptr(ln), len(_lib.PHASES)))
+        return {p: (float(ms[i]), int(ln[i])) for i, p in enumerate(_lib.PHASES)}
+
+    def free(self):
+        if self._h:
+            lib.nd_sampler_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class SamplingModule:
+    """Stand-in for one of the reference's per-app Python modules (e.g. UniformRandomWalkPy3)."""
+
+    def __init__(self, params: AppParams, device=0, mode=MODE_SAMPLE_PARALLEL):
+        self._params = params
+        self._device = device
+        self._mode = mode  # the reference's sample() runs the sample-parallel path (:54-58)
+        self._graph = None
+        self._sampler = None
+        self._final = None
+
+    def initSampling(self, graph_path):
+        self._graph = Graph.load(graph_path, device=self._device)
+        n = self._graph.V
+        if self._params.app <= APP_NODE2VEC and n < 256 * 1024:
+            n = 100 * n  # RandomWalkApp::numSamples, randomWalks.cu:23-26
+        if self._params.app == APP_UNIFORM_WALK:
+            n = self._graph.V  # example/uniformRandWalk.cu:55-58
+        if self._params.app >= APP_FASTGCN_REF:
+            n = 10000  # NUM_SAMPLES, fastgcnSampling.cu:4
+        self._sampler = Sampler(self._graph, self._params, num_samples=n)
+
+    def sample(self):
+        self._final = None
+        self._sampler.sample(self._mode)
+
+    def finalSamplesArray(self):
+        if self._final is None:
+            self._final = self._sampler.final_samples().reshape(-1)
+        return self._final
+
+    def finalSamples(self):
+        return self.finalSamplesArray().tolist()
+
+    def finalSampleLength(self):
+        return int(self.finalSamplesArray().size)
+
+    def freeDeviceMemory(self):
+        if self._sampler:
+            self._sampler.free()
+        if self._graph:
+            self._graph.free()
+        self._sampler = self._graph = None

@@ -1,0 +1,105 @@
+// Per-segment dedup: sort ascending, drop equal neighbours, compact to the front, pad with the
+// invalid id, report the unique count.
+//
+// Semantics of remove_duplicates_in_hop_per_block (src/distinct.cuh:1-111, dead code in the
+// reference: one CTA per root, cub BlockRadixSort, a single thread compacting, segments above
+// 1024 entries skipped).  Here a segment (one hop of one sample: 25 or 250 ids for GraphSAGE) is
+// owned by a thread group sized to it; the group runs a bitonic network over the padded segment
+// in shared memory, flags the first element of every run of equal ids, ranks the flags with a
+// shared-memory scan and writes the survivors back in one coalesced pass.
+#include "nd_common.cuh"
+
+namespace {
+
+constexpr int DTHREADS = 256;
+constexpr int MAX_SEG = 2048;
+
+// P = padded (power of two) segment length, G = threads per segment (P/2 capped at DTHREADS).
+template <int P>
+__global__ void __launch_bounds__(DTHREADS)
+distinct_kernel(int32_t *__restrict__ data, int64_t n_segments, int32_t seg_len, int32_t seg_stride,
+                int32_t invalid, int32_t *__restrict__ counts, int32_t counts_stride) {
+  constexpr int G = (P / 2 < 32) ? 32 : ((P / 2 > DTHREADS) ? DTHREADS : P / 2);
+  constexpr int SEGS_PER_CTA = DTHREADS / G;
+  __shared__ int32_t keys[SEGS_PER_CTA][P];
+  __shared__ int32_t rank[SEGS_PER_CTA][P];
+  const int grp = threadIdx.x / G, t = threadIdx.x % G;
+  const int64_t seg0 = (int64_t)blockIdx.x * SEGS_PER_CTA;
+  // every group runs the same number of barriers, so groups past the end just idle on a dummy
+  const int64_t seg = seg0 + grp;
+  const bool active = seg < n_segments;
+  int32_t *k = keys[grp];
+  int32_t *r = rank[grp];
+  int32_t *base = data + seg * (int64_t)seg_stride;
+  for (int i = t; i < P; i += G) {
+    int32_t v = 0x7fffffff;
+    if (active && i < seg_len) {
+      v = base[i];
+      if (v == invalid || v < 0) v = 0x7fffffff;
+    }
+    k[i] = v;
+  }
+  auto gsync = [&]() { if (G <= 32) __syncwarp(); else __syncthreads(); };
+  gsync();
+  for (int size = 2; size <= P; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = t; i < P / 2; i += G) {
+        const int lo = 2 * i - (i & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = (lo & size) == 0;
+        const int32_t a = k[lo], b = k[hi];
+        if ((a > b) == up) { k[lo] = b; k[hi] = a; }
+      }
+      gsync();
+    }
+  }
+  // flags, then inclusive Hillis-Steele scan in shared memory
+  for (int i = t; i < P; i += G) r[i] = (k[i] != 0x7fffffff && (i == 0 || k[i] != k[i - 1])) ? 1 : 0;
+  gsync();
+  for (int off = 1; off < P; off <<= 1) {
+    int32_t add[(P + G - 1) / G];
+    int c = 0;
+    for (int i = t; i < P; i += G, c++) add[c] = i >= off ? r[i - off] : 0;
+    gsync();
+    c = 0;
+    for (int i = t; i < P; i += G, c++) r[i] += add[c];
+    gsync();
+  }
+  const int32_t uniq = r[P - 1];
+  // survivors to the front (positions only ever move left, and reads come from shared memory)
+  if (active) {
+    for (int i = t; i < seg_len; i += G) {
+      const bool head = k[i] != 0x7fffffff && (i == 0 || k[i] != k[i - 1]);
+      if (head) base[r[i] - 1] = k[i];
+    }
+    for (int i = uniq + t; i < seg_len; i += G) base[i] = invalid;
+    if (t == 0 && counts) counts[seg * (int64_t)counts_stride] = uniq;
+  }
+}
+
+}  // namespace
+
+int nd_distinct_launch(cudaStream_t st, int32_t *data, int64_t n_segments, int32_t seg_len, int32_t seg_stride,
+                       int32_t invalid, int32_t *counts, int32_t counts_stride) {
+  ND_REQUIRE(seg_len >= 1 && seg_len <= MAX_SEG, ND_ERR_ARG, "distinct: segment length %d outside [1,%d]", seg_len, MAX_SEG);
+  int P = 32;
+  while (P < seg_len) P <<= 1;
+#define LAUNCH(PP)                                                                                       \
+  {                                                                                                      \
+    constexpr int G = ((PP) / 2 < 32) ? 32 : (((PP) / 2 > DTHREADS) ? DTHREADS : (PP) / 2);              \
+    const int64_t blocks = (n_segments + (DTHREADS / G) - 1) / (DTHREADS / G);                           \
+    distinct_kernel<PP><<<(unsigned)blocks, DTHREADS, 0, st>>>(data, n_segments, seg_len, seg_stride, invalid, counts, counts_stride); \
+  }
+  switch (P) {
+    case 32: LAUNCH(32) break;
+    case 64: LAUNCH(64) break;
+    case 128: LAUNCH(128) break;
+    case 256: LAUNCH(256) break;
+    case 512: LAUNCH(512) break;
+    case 1024: LAUNCH(1024) break;
+    default: LAUNCH(2048) break;
+  }
+#undef LAUNCH
+  ND_CUDA(cudaGetLastError());
+  return ND_OK;
+}

@@ -1,0 +1,127 @@
+"""GPU parity tests of the random-walk apps through the C ABI: bit-exact against the oracle and the
+golden fixtures in every execution mode; size-independent properties at the benchmark's sizes."""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+MODES = [0, 1, 2]   # TransitParallel, TransitParallel+LB, SampleParallel
+WALKS = [0, 1, 2, 3]
+
+
+def _graph(nd, hg):
+    return nd.Graph.from_csr(hg.row_ptr, hg.col, hg.w, hg.max_w)
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", ["uniform_walk", "deepwalk", "ppr", "node2vec"])
+def test_walks_match_golden(nd, ndo, name, mode):
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    zg = np.load(os.path.join(GOLD, "graph_rmat300.npz"))
+    g = nd.Graph.from_csr(zg["row_ptr"], zg["col"], zg["w"], zg["max_w"])
+    pr = nd.app_params(int(z["app"]), steps=int(z["steps"]), seed=int(z["seed"]))
+    s = nd.Sampler(g, pr, num_samples=int(z["S"]), first_sample=int(z["first"]))
+    s.sample(mode)
+    assert np.array_equal(s.final_samples(), z["out"])
+    assert s.stats()["sampled_edges"] == int(z["sampled_edges"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("app", WALKS)
+def test_walks_match_oracle(nd, ndo, small_graph, app, mode):
+    g = _graph(nd, small_graph)
+    kw = dict(stop_prob=0.15) if app == 2 else {}
+    S, first = 5000, 777          # more samples than vertices: start vertex = index % V
+    for steps in (1, 2, 33):
+        pr = nd.app_params(app, steps=steps, seed=42, **kw)
+        opr = ndo.make_params(app, steps=steps, seed=42, **kw)
+        s = nd.Sampler(g, pr, num_samples=S, first_sample=first)
+        s.sample(mode)
+        exp = ndo.sample(small_graph, opr, S, first=first)
+        got = s.final_samples()
+        assert np.array_equal(got, exp["out"]), f"app {app} mode {mode} steps {steps}"
+        st = s.stats()
+        assert st["sampled_edges"] == exp["counters"]["sampled_edges"]
+        assert st["live_pairs"] == exp["counters"]["live_pairs"]
+        # a second run of the same sampler gives the same answer
+        s.sample(mode)
+        assert np.array_equal(s.final_samples(), exp["out"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_node2vec_corrected_comparison(nd, ndo, small_graph, mode):
+    g = _graph(nd, small_graph)
+    pr = nd.app_params(3, steps=20, seed=9, n2v_ref_compat=0, p=0.5, q=2.0)
+    opr = ndo.make_params(3, steps=20, seed=9, n2v_ref_compat=0, p=0.5, q=2.0)
+    s = nd.Sampler(g, pr, num_samples=3000)
+    s.sample(mode)
+    assert np.array_equal(s.final_samples(), ndo.sample(small_graph, opr, 3000)["out"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_explicit_initial_samples_and_edge_cases(nd, ndo, tiny_graph, mode):
+    g = _graph(nd, tiny_graph)
+    init = np.array([8, 0, 3, 3, 9, 6, 10, -1, 5], np.int32)     # isolated, valid, out of range
+    pr = nd.app_params(1, steps=7, seed=3)
+    opr = ndo.make_params(1, steps=7, seed=3)
+    s = nd.Sampler(g, pr, num_samples=len(init), initial=init)
+    s.sample(mode)
+    got = s.final_samples()
+    clean = np.where((init < 0) | (init >= g.V), g.V, init).astype(np.int32)
+    exp = ndo.sample(tiny_graph, opr, len(init), initial=clean)
+    assert np.array_equal(got, exp["out"])
+    assert (got[0] == g.V).all() and (got[6] == g.V).all() and (got[7] == g.V).all()
+    # new seeds on the same sampler
+    init2 = np.array([0, 1, 2, 3, 4, 5, 6, 7, 8], np.int32)
+    s.set_initial(init2)
+    s.sample(mode)
+    assert np.array_equal(s.final_samples(), ndo.sample(tiny_graph, opr, 9, initial=init2)["out"])
+    # zero samples
+    s0 = nd.Sampler(g, pr, num_samples=0)
+    s0.sample(mode)
+    assert s0.final_samples().shape == (0, 7)
+
+
+def test_shards_concatenate_to_the_single_gpu_answer(nd, ndo, small_graph):
+    """Seed-range sharding (PartStartPointer, src/utils.hpp:26-27): the keyed draws use the global
+    sample index, so shards computed separately equal the unsharded run."""
+    g = _graph(nd, small_graph)
+    pr = nd.app_params(2, steps=30, seed=8, stop_prob=0.15)
+    S = 3001
+    whole = nd.Sampler(g, pr, num_samples=S)
+    whole.sample(1)
+    parts = []
+    for i in range(4):
+        f, c = nd.shard_range(S, i, 4)
+        sh = nd.Sampler(g, pr, num_samples=c, first_sample=f)
+        sh.sample(1)
+        parts.append(sh.final_samples())
+    assert np.array_equal(np.concatenate(parts), whole.final_samples())
+
+
+@pytest.mark.parametrize("app", [0, 3])
+def test_full_size_properties(nd, ndo, app):
+    """Benchmark-sized run (2^20 vertices, 16M undirected edges, one 100-step walk per vertex):
+    every sampled edge exists in the CSR (check_results.cu:162-299 on all steps), modes agree with
+    each other, and a seed subset is bit-exact against the oracle."""
+    V, M = 1 << 20, 1 << 24
+    g = nd.Graph.rmat(V, M, seed=0)
+    row_ptr, col, w, mw = g.to_host()
+    hg = ndo.HostGraph(row_ptr, col, w, mw)
+    pr = nd.app_params(app, steps=100, seed=0)
+    opr = ndo.make_params(app, steps=100, seed=0)
+    s = nd.Sampler(g, pr, num_samples=V)
+    outs = []
+    for mode in (1, 2):
+        s.sample(mode)
+        outs.append(s.final_samples().copy())
+    assert np.array_equal(outs[0], outs[1])
+    out = outs[0]
+    sub = 20000
+    exp = ndo.sample(hg, opr, sub)
+    assert np.array_equal(out[:sub], exp["out"])
+    init = (np.arange(V) % V).astype(np.int32)
+    assert ndo.check_sampled_vertices(hg, opr, V, init, out) == 0
+    assert s.stats()["sampled_edges"] == int((out != V).sum())
