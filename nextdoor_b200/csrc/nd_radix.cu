@@ -174,6 +174,8 @@ radix_scatter_kernel(NdSortArrays arr, int key_word, const int32_t *__restrict__
 
 }  // namespace
 
+static int nd_radix_max_digit(int64_t max_n) { return max_n <= ((int64_t)4 << 20) ? 10 : 8; }
+
 NdRadixPlan nd_radix_plan(int key_bits, int64_t max_n) {
   NdRadixPlan p;
   if (key_bits < 1) key_bits = 1;
@@ -181,7 +183,7 @@ NdRadixPlan nd_radix_plan(int key_bits, int64_t max_n) {
   // Small maps stay L2-resident, where the scattered stores of a wide digit cost nothing extra
   // and every pass saved is three launches saved; large maps need 256-bin passes so that each
   // tile still writes runs of full sectors.
-  const int max_digit = max_n <= (int64_t)4 << 20 ? 10 : 8;
+  const int max_digit = nd_radix_max_digit(max_n);
   p.passes = (key_bits + max_digit - 1) / max_digit;
   int left = key_bits, sh = 0;
   p.max_bins = 0;
@@ -204,8 +206,7 @@ NdRadixPlan nd_radix_plan(int key_bits, int64_t max_n) {
 // serves sorts on keys of different widths (transit ids, edge endpoints, weight bits).
 int nd_radix_scratch_alloc(NdRadixScratch *s, int key_bits, int64_t max_n) {
   s->plan = nd_radix_plan(key_bits, max_n);
-  s->cap_bins = nd_radix_plan(32, max_n).max_bins;
-  if (s->plan.max_bins > s->cap_bins) s->cap_bins = s->plan.max_bins;
+  s->cap_bins = 1 << nd_radix_max_digit(max_n);
   s->bytes = sizeof(uint32_t) * ((size_t)s->cap_bins * s->plan.max_tiles + 8 * (size_t)s->cap_bins);
   void *p = nullptr;
   ND_CUDA(cudaMalloc(&p, s->bytes));
