@@ -230,9 +230,12 @@ int build_from_soa(int device, int64_t n, int32_t V, uint32_t *a[3], uint32_t *b
     max_weight_kernel<<<grid_for(n, 256, dev.sms), 256, 0, st>>>(g->row_ptr, cur[0], (const float *)cur[2], V, n, (int32_t *)g->max_w);
   ND_CUDA(cudaGetLastError());
   ND_CUDA(cudaStreamSynchronize(st));
-  // keep the buffers that hold the sorted dst / weights as col / w; release the rest
+  // keep the buffers that hold the sorted dst / weights as col / w (they carry 32 bytes of
+  // padding for the 16-byte staging windows); release the rest
   g->col = (int32_t *)cur[1];
   g->w = (float *)cur[2];
+  ND_CUDA(cudaMemset(g->col + n, 0, sizeof(int32_t) * 8));
+  ND_CUDA(cudaMemset(g->w + n, 0, sizeof(float) * 8));
   cudaFree(cur[0]);
   for (int w = 0; w < 3; w++) cudaFree(oth[w]);
   nd_radix_scratch_free(&scr);
@@ -274,8 +277,11 @@ int nd_graph_from_csr(int device, int32_t V, int64_t E, const int32_t *row_ptr, 
   nd_graph *g = new nd_graph();
   g->device = device; g->V = V; g->E = E;
   ND_CUDA(cudaMalloc(&g->row_ptr, sizeof(int32_t) * ((size_t)V + 1)));
-  ND_CUDA(cudaMalloc(&g->col, sizeof(int32_t) * (size_t)(E > 0 ? E : 1)));
-  ND_CUDA(cudaMalloc(&g->w, sizeof(float) * (size_t)(E > 0 ? E : 1)));
+  // 32 bytes of padding: staging copies read whole 16-byte windows around a list
+  ND_CUDA(cudaMalloc(&g->col, sizeof(int32_t) * ((size_t)E + 8)));
+  ND_CUDA(cudaMalloc(&g->w, sizeof(float) * ((size_t)E + 8)));
+  ND_CUDA(cudaMemset(g->col + E, 0, sizeof(int32_t) * 8));
+  ND_CUDA(cudaMemset(g->w + E, 0, sizeof(float) * 8));
   ND_CUDA(cudaMemcpy(g->row_ptr, row_ptr, sizeof(int32_t) * ((size_t)V + 1), cudaMemcpyHostToDevice));
   if (E > 0) {
     ND_CUDA(cudaMemcpy(g->col, col, sizeof(int32_t) * (size_t)E, cudaMemcpyHostToDevice));
@@ -300,7 +306,7 @@ int nd_graph_from_edge_records(int device, int64_t n, const void *records, nd_gr
   Rec12 *d_rec = nullptr;
   uint32_t *a[3], *b[3];
   ND_CUDA(cudaMalloc(&d_rec, sizeof(Rec12) * cap));
-  for (int w = 0; w < 3; w++) { ND_CUDA(cudaMalloc(&a[w], 4 * cap)); ND_CUDA(cudaMalloc(&b[w], 4 * cap)); }
+  for (int w = 0; w < 3; w++) { ND_CUDA(cudaMalloc(&a[w], 4 * (cap + 8))); ND_CUDA(cudaMalloc(&b[w], 4 * (cap + 8))); }
   int32_t *d_max = nullptr;
   int *d_status = nullptr;
   ND_CUDA(cudaMalloc(&d_max, sizeof(int32_t)));
@@ -346,7 +352,7 @@ int nd_graph_rmat(int device, int32_t V, int64_t M, uint64_t seed, nd_graph **ou
   ND_TRY(nd_device_info(device, &dev));
   const size_t cap = (size_t)(2 * M);
   uint32_t *a[3], *b[3];
-  for (int w = 0; w < 3; w++) { ND_CUDA(cudaMalloc(&a[w], 4 * cap)); ND_CUDA(cudaMalloc(&b[w], 4 * cap)); }
+  for (int w = 0; w < 3; w++) { ND_CUDA(cudaMalloc(&a[w], 4 * (cap + 8))); ND_CUDA(cudaMalloc(&b[w], 4 * (cap + 8))); }
   int scale = 0;
   while (((int64_t)1 << scale) < V) scale++;
   rmat_kernel<<<grid_for(M, 256, dev.sms), 256>>>(V, scale, M, seed, a[0], a[1], a[2]);

@@ -1,0 +1,106 @@
+"""GPU parity tests of k-hop sampling (with replacement = the reference's KHopApp; without
+replacement + per-hop distinct = the extension) in every execution mode, including the
+load-balanced path whose block / grid bins stage adjacency lists in shared memory."""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+MODES = [0, 1, 2]
+
+
+def _graph(nd, hg):
+    return nd.Graph.from_csr(hg.row_ptr, hg.col, hg.w, hg.max_w)
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_khop_matches_golden(nd, mode):
+    z = np.load(os.path.join(GOLD, "khop.npz"))
+    zg = np.load(os.path.join(GOLD, "graph_rmat300.npz"))
+    g = nd.Graph.from_csr(zg["row_ptr"], zg["col"], zg["w"], zg["max_w"])
+    s = nd.Sampler(g, nd.app_params(nd.APP_KHOP, seed=int(z["seed"])), num_samples=int(z["S"]), first_sample=int(z["first"]))
+    s.sample(mode)
+    assert np.array_equal(s.final_samples(), z["out"])
+    assert s.stats()["sampled_edges"] == int(z["sampled_edges"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("app", [4, 5])
+@pytest.mark.parametrize("fanout", [[25, 10], [3], [2, 3, 4], [32, 1], [7, 16]])
+def test_khop_matches_oracle(nd, ndo, small_graph, app, fanout, mode):
+    g = _graph(nd, small_graph)
+    S, first = 3000, 50
+    pr = nd.app_params(app, fanout=fanout, seed=13)
+    opr = ndo.make_params(app, fanout=fanout, seed=13)
+    s = nd.Sampler(g, pr, num_samples=S, first_sample=first)
+    s.sample(mode)
+    exp = ndo.sample(small_graph, opr, S, first=first)
+    got = s.final_samples()
+    assert np.array_equal(got, exp["out"]), f"app {app} fanout {fanout} mode {mode}"
+    st = s.stats()
+    assert st["sampled_edges"] == exp["counters"]["sampled_edges"]
+    assert st["live_pairs"] == exp["counters"]["live_pairs"]
+    if app == 5:
+        assert np.array_equal(s.aux()["hop_counts"], exp["hop_counts"])
+    s.sample(mode)   # run again on the same handle
+    assert np.array_equal(s.final_samples(), exp["out"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("app", [4, 5])
+def test_khop_batched_random_seeds_hit_every_bin(nd, ndo, app, mode):
+    """Seeds drawn uniformly (batches of 1024), enough of them that hop 1 has transits in the
+    sub-warp, block and grid bins, with hub lists both shorter and longer than the staging buffer."""
+    hg = ndo.rmat_graph(1 << 15, 1 << 19, seed=2)
+    assert hg.degree().max() > 12032 and (hg.degree() == 0).sum() > 0
+    g = _graph(nd, hg)
+    rng = np.random.default_rng(7)
+    S = 16 * 1024
+    init = rng.integers(0, hg.V, S).astype(np.int32)
+    init[5] = hg.V          # a seed that is not a vertex
+    init[6] = int(np.argmax(hg.degree() == 0))   # an isolated seed
+    pr = nd.app_params(app, fanout=[25, 10], seed=21)
+    opr = ndo.make_params(app, fanout=[25, 10], seed=21)
+    s = nd.Sampler(g, pr, num_samples=S, initial=init)
+    s.sample(mode)
+    clean = np.where((init < 0) | (init >= hg.V), hg.V, init).astype(np.int32)
+    exp = ndo.sample(hg, opr, S, initial=clean)
+    got = s.final_samples()
+    assert np.array_equal(got, exp["out"])
+    assert (got[5] == hg.V).all() and (got[6] == hg.V).all()
+    assert ndo.check_sampled_vertices(hg, opr, S, clean, got) == 0
+    assert s.stats()["sampled_edges"] == exp["counters"]["sampled_edges"]
+
+
+def test_khop_full_size_properties(nd, ndo):
+    """GraphSAGE-sized run: 2^21 vertices, 32M undirected edges, 64 batches of 1024 uniform seeds,
+    fan-out 25 then 10 without replacement + distinct.  Modes agree, a subset is bit-exact against
+    the oracle, every sampled vertex is a neighbour of the previous hop, hops are sorted unique."""
+    V, M = 1 << 21, 1 << 25
+    g = nd.Graph.rmat(V, M, seed=0)
+    row_ptr, col, w, mw = g.to_host()
+    hg = ndo.HostGraph(row_ptr, col, w, mw)
+    S = 64 * 1024
+    init = np.random.default_rng(0).integers(0, V, S).astype(np.int32)
+    pr = nd.app_params(5, fanout=[25, 10], seed=0)
+    opr = ndo.make_params(5, fanout=[25, 10], seed=0)
+    s = nd.Sampler(g, pr, num_samples=S, initial=init)
+    outs = []
+    for mode in MODES:
+        s.sample(mode)
+        outs.append(s.final_samples().copy())
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    sub = 4096
+    exp = ndo.sample(hg, opr, sub, initial=init[:sub])
+    assert np.array_equal(outs[1][:sub], exp["out"])
+    assert ndo.check_sampled_vertices(hg, opr, S, init, outs[1]) == 0
+    hop = s.aux()["hop_counts"].reshape(S, 2)
+    o = outs[1]
+    for off, n, k in ((0, 25, 0), (25, 250, 1)):
+        seg = o[:, off:off + n].astype(np.int64)
+        idx = np.arange(n)[None, :]
+        assert ((seg == V) == (idx >= hop[:, k][:, None])).all()
+        d = np.diff(seg, axis=1)
+        assert (d[(idx[:, 1:] < hop[:, k][:, None])] > 0).all()
