@@ -146,12 +146,12 @@ coll_gather_kernel(NdGraphView g, CollParams cp, int64_t s0, int64_t s1, const i
       const int32_t t = tr[i];
       if (t < 0 || t >= cp.V) continue;
       const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
-      float inv_rowsum = 0.f;
-      if (cp.app == ND_APP_LADIES_IS) {
-        float part = 0.f;
-        for (int e = lane; e < deg; e += 32) part = __fadd_rn(part, __ldg(g.w + rs + e));
-        for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
-        inv_rowsum = part;
+      float rowsum = 0.f;
+      if (cp.app == ND_APP_LADIES_IS) {  // fp64 partial sums: the order of the adds does not matter
+        double part = 0.0;
+        for (int e = lane; e < deg; e += 32) part += (double)__ldg(g.w + rs + e);
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        rowsum = (float)part;
       }
       const int64_t dst = base + sh_start[i];
       for (int e = lane; e < deg; e += 32) {
@@ -159,7 +159,7 @@ coll_gather_kernel(NdGraphView g, CollParams cp, int64_t s0, int64_t s1, const i
         c_seg[dst + e] = (uint32_t)(s - s0);
         float term = 0.f;
         if (cp.app == ND_APP_LADIES_IS) {
-          const float r = __fdiv_rn(__ldg(g.w + rs + e), inv_rowsum);
+          const float r = __fdiv_rn(__ldg(g.w + rs + e), rowsum);
           term = __fmul_rn(r, r);
         }
         c_w[dst + e] = __float_as_uint(term);
@@ -199,52 +199,53 @@ coll_weigh_kernel(NdGraphView g, int app, int64_t n, const uint32_t *__restrict_
 __global__ void __launch_bounds__(CTHREADS)
 coll_sample_kernel(NdGraphView g, CollParams cp, int steps, int64_t s0, int64_t s1, const int32_t *__restrict__ initial,
                    int32_t *out, const int64_t *__restrict__ offs, const uint32_t *__restrict__ c_id,
-                   const float *__restrict__ wt, float *__restrict__ cdf, int32_t *__restrict__ adj_row,
+                   const float *__restrict__ wt, double *__restrict__ cdf, int32_t *__restrict__ adj_row,
                    int32_t *__restrict__ adj_col, float *__restrict__ prob, unsigned long long *__restrict__ stats) {
-  __shared__ float warp_tot[CTHREADS / 32];
-  __shared__ float carry_sh;
+  __shared__ double warp_tot[CTHREADS / 32];
+  __shared__ double carry_sh;
   __shared__ int32_t sh_tr[1024];
   __shared__ int32_t sh_layer[1024];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int64_t s = s0 + blockIdx.x; s < s1; s += gridDim.x) {
     const int64_t base = offs[s] - offs[s0];
     const int64_t n = offs[s + 1] - offs[s];
-    if (threadIdx.x == 0) carry_sh = 0.f;
+    // fp64 accumulation of the fp32 weights (sums agree with any other order of addition to
+    // ~1e-16; FastGCN's integer weights sum exactly)
+    if (threadIdx.x == 0) carry_sh = 0.0;
     __syncthreads();
     for (int64_t c0 = 0; c0 < n; c0 += CTHREADS) {
       const int64_t i = c0 + threadIdx.x;
-      const float v = i < n ? wt[base + i] : 0.f;
-      float inc = v;
+      double inc = i < n ? (double)wt[base + i] : 0.0;
       for (int o = 1; o < 32; o <<= 1) {
-        const float t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc = __fadd_rn(inc, t);
+        const double t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
       }
       if (lane == 31) warp_tot[warp] = inc;
       __syncthreads();
-      float woff = carry_sh;
-      for (int w = 0; w < warp; w++) woff = __fadd_rn(woff, warp_tot[w]);
-      if (i < n) cdf[base + i] = __fadd_rn(woff, inc);
+      double woff = carry_sh;
+      for (int w = 0; w < warp; w++) woff += warp_tot[w];
+      if (i < n) cdf[base + i] = woff + inc;
       __syncthreads();
-      if (threadIdx.x == CTHREADS - 1) carry_sh = __fadd_rn(woff, inc);
+      if (threadIdx.x == CTHREADS - 1) carry_sh = woff + inc;
       __syncthreads();
     }
-    const float total = carry_sh;
+    const double total = carry_sh;
     const int32_t *tr = transits_of(cp, initial, out, s);
     for (int i = threadIdx.x; i < cp.ntr; i += CTHREADS) sh_tr[i] = tr[i];
     uint32_t valid = 0;
     for (int j = threadIdx.x; j < cp.L; j += CTHREADS) {
       int32_t pick = cp.V;
       float pr = 0.f;
-      if (n > 0 && total > 0.f) {
+      if (n > 0 && total > 0.0) {
         Rng rng(cp.seed, (uint32_t)(cp.first_sample + s), (uint32_t)cp.step, (uint32_t)j);
-        const float target = __fmul_rn(rng.uniform(), total);
+        const double target = (double)rng.uniform() * total;
         int64_t lo = 0, hi = n - 1;  // first index whose cdf reaches the target
         while (lo < hi) {
           const int64_t mid = lo + (hi - lo) / 2;
           if (cdf[base + mid] >= target) hi = mid; else lo = mid + 1;
         }
         pick = (int32_t)c_id[base + lo];
-        pr = __fdiv_rn(wt[base + lo], total);
+        pr = (float)((double)wt[base + lo] / total);
         valid++;
       }
       sh_layer[j] = pick;
@@ -273,7 +274,7 @@ static int ensure_cand(nd_sampler *s, int64_t need) {
   nd_radix_scratch_free(&s->radix);
   s->d_cand = nullptr; s->d_cand_w = nullptr; s->cand_cap = 0;
   ND_CUDA(cudaMalloc(&s->d_cand, sizeof(uint32_t) * 6 * (size_t)cap));
-  ND_CUDA(cudaMalloc(&s->d_cand_w, sizeof(float) * 2 * (size_t)cap));
+  ND_CUDA(cudaMalloc(&s->d_cand_w, (sizeof(float) + sizeof(double)) * (size_t)cap));  // cdf (fp64) first, then weights
   ND_TRY(nd_radix_scratch_alloc(&s->radix, 32, cap));
   s->cand_cap = cap;
   return ND_OK;
@@ -338,7 +339,8 @@ int nd_collective_sample(nd_sampler *s, int mode) {
     const int64_t cap = s->cand_cap;
     uint32_t *c_a[3] = {(uint32_t *)s->d_cand, (uint32_t *)s->d_cand + cap, (uint32_t *)s->d_cand + 2 * cap};
     uint32_t *c_b[3] = {(uint32_t *)s->d_cand + 3 * cap, (uint32_t *)s->d_cand + 4 * cap, (uint32_t *)s->d_cand + 5 * cap};
-    float *wt = s->d_cand_w, *cdf = s->d_cand_w + cap;
+    double *cdf = (double *)s->d_cand_w;
+    float *wt = (float *)(cdf + cap);
     int64_t s0 = 0;
     while (s0 < S) {  // chunk of samples whose neighbourhoods fit the buffers together
       int64_t s1 = s0 + 1;

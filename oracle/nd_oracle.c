@@ -466,7 +466,7 @@ static void sample_collective(const ndo_graph *g, const ndo_params *p, int64_t g
     for (int64_t i = 0; i < m; i++) if (i == 0 || cand[i] != cand[i - 1]) cand[U++] = cand[i];
     c->union_unique += U;
     float *wt = (float *)calloc((size_t)(U > 0 ? U : 1), sizeof(float));
-    float *cdf = (float *)malloc(sizeof(float) * (size_t)(U > 0 ? U : 1));
+    double *cdf = (double *)malloc(sizeof(double) * (size_t)(U > 0 ? U : 1));
     if (p->app == NDO_APP_FASTGCN_IS) {
       for (int64_t u = 0; u < U; u++) {
         float d = (float)(g->row_ptr[cand[u] + 1] - g->row_ptr[cand[u]]);
@@ -476,8 +476,9 @@ static void sample_collective(const ndo_graph *g, const ndo_params *p, int64_t g
       for (int32_t i = 0; i < ntr; i++) {
         int32_t t = transits[i];
         if (t == INV || t == -1) continue;
-        float rowsum = 0.0f;
-        for (int32_t e = g->row_ptr[t]; e < g->row_ptr[t + 1]; e++) rowsum = rowsum + g->w[e];
+        double rowsum_d = 0.0; /* summed in fp64 so that the order of the adds does not matter */
+        for (int32_t e = g->row_ptr[t]; e < g->row_ptr[t + 1]; e++) rowsum_d += (double)g->w[e];
+        const float rowsum = (float)rowsum_d;
         for (int32_t e = g->row_ptr[t]; e < g->row_ptr[t + 1]; e++) {
           int32_t v = g->col[e];
           int64_t lo = 0, hi = U - 1, pos = -1;
@@ -487,17 +488,19 @@ static void sample_collective(const ndo_graph *g, const ndo_params *p, int64_t g
         }
       }
     }
-    float run = 0.0f;
-    for (int64_t u = 0; u < U; u++) { run = run + wt[u]; cdf[u] = run; }
-    const float total = U > 0 ? cdf[U - 1] : 0.0f;
+    /* the CDF is accumulated in fp64: sums of fp32 weights then agree between any two orders
+     * of addition to ~1e-16, far inside the 1e-5 the probabilities are held to */
+    double run = 0.0;
+    for (int64_t u = 0; u < U; u++) { run += (double)wt[u]; cdf[u] = run; }
+    const double total = U > 0 ? cdf[U - 1] : 0.0;
     for (int32_t j = 0; j < L; j++) {
-      if (U == 0 || !(total > 0.0f)) { dst[j] = INV; if (pdst) pdst[j] = 0.0f; continue; }
+      if (U == 0 || !(total > 0.0)) { dst[j] = INV; if (pdst) pdst[j] = 0.0f; continue; }
       rng_t rng = {p->seed, (uint32_t)gs, (uint32_t)step, (uint32_t)j, 0u};
-      float target = rng_uniform(&rng) * total;
+      double target = (double)rng_uniform(&rng) * total;
       int64_t lo = 0, hi = U - 1; /* first index with cdf >= target */
       while (lo < hi) { int64_t mid = lo + (hi - lo) / 2; if (cdf[mid] >= target) hi = mid; else lo = mid + 1; }
       dst[j] = cand[lo];
-      if (pdst) pdst[j] = wt[lo] / total;
+      if (pdst) pdst[j] = (float)((double)wt[lo] / total);
       c->next_calls++; c->sampled_edges++;
       if (arow) for (int32_t i = 0; i < ntr; i++) {
         int32_t t = transits[i];
