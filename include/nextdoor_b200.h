@@ -157,6 +157,19 @@ int nd_sampler_destroy(nd_sampler *s);
  * are clobbered.  *n_live_out (host) receives the surviving count. */
 int nd_invert_map(int device, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t invalid,
                   int32_t *keys_out, int32_t *vals_out, int64_t *n_live_out);
+/* No counterpart in the reference.  nd_invert_map for callers that must not allocate device
+ * memory: a sampler sharing a process with a training job, where cudaMalloc/cudaFree would
+ * synchronise the device and stall the training streams, or where the framework's allocator has
+ * already taken nearly all of HBM so a raw cudaMalloc may fail.  Same arguments and result as
+ * nd_invert_map, but the scratch is a fixed array inside the library image (about 2 MB, resident
+ * on every GPU that loads the library until the process exits) and no cudaMalloc/cudaFree is
+ * made.  n must not exceed nd_static_max_pairs() (2^20), else ND_ERR_RANGE.  All calls on a device
+ * share the array: calls that overlap on the GPU race, so issue them one after the other.  The
+ * first call on each device looks the array's device address up and should happen before any
+ * stream capture begins. */
+int nd_invert_map_static(int device, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t invalid,
+                         int32_t *keys_out, int32_t *vals_out, int64_t *n_live_out);
+int64_t nd_static_max_pairs(void);
 /* remove_duplicates_in_hop_per_block (src/distinct.cuh:1-111): every segment of seg_len ints is
  * sorted ascending, made unique, compacted to the front and padded with `invalid`;
  * counts (device, may be NULL) receives the unique count per segment. */

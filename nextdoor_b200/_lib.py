@@ -78,7 +78,9 @@ _SIGS = {
     "nd_sampler_phase_ms": (C.c_int, [VP, VP, VP, C.c_int]),
     "nd_sampler_destroy": (C.c_int, [VP]),
     "nd_invert_map": (C.c_int, [C.c_int, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
-    "nd_distinct_segments": (C.c_int, [C.c_int, VP, C.c_int64, C.c_int32, C.c_int32, VP]),
+    "nd_invert_map_static": (C.c_int, [C.c_int, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
+    "nd_static_max_pairs": (C.c_int64, []),
+    "nd_distinct_segments":(C.c_int, [C.c_int, VP, C.c_int64, C.c_int32, C.c_int32, VP]),
     "nd_philox_uniform": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, VP, VP]),
 }
 
