@@ -80,13 +80,20 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.rows)}
 
 
-def next_bytes(app, st, steps, S):
+def next_bytes(app, st, steps, S, sample_parallel=False):
     """Algorithmic bytes the next() launches of one sample() move, from the device's own event
     counters: per live pair 8 B map-in + 8 B row offsets; per sampled edge 4 B neighbour + 4 B
     output; 8 B map-out per pair of every step but the last; weighted apps + 4 B max weight per
     next() and 4 B per weight read; node2vec + 4 B load and 4 B store of the previous vertex,
     8 B for its row, and per try 4 B candidate + 4 B per binary-search probe."""
     pairs, edges = st["live_pairs"], st["sampled_edges"]
+    if sample_parallel:   # no maps: row offsets per visited transit, neighbour + staged output per edge
+        b = 8 * pairs + 8 * edges
+        if app in (1, 2):
+            b += 4 * pairs + 4 * st["weight_tries"]
+        if app == 3:
+            b += 8 * pairs + 4 * st["n2v_tries"] + 4 * st["n2v_probes"]
+        return b
     b = 16 * pairs + 8 * edges + 8 * pairs * (steps - 1) / steps
     if app in (1, 2):
         b += 4 * pairs + 4 * st["weight_tries"]
@@ -131,6 +138,8 @@ def main():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--mode", default="tp_lb", choices=list(MODES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-only", action="store_true",
+                    help="build the graph, run warmup+steps passes of sample() and exit (short launch list for ncu)")
     a = ap.parse_args()
     wl = WORKLOADS[a.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -175,13 +184,21 @@ def main():
     S = V
     first = rank * S
     smp = nd.Sampler(g, pr, num_samples=S, first_sample=first)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()          # a non-default stream, so the library can replay its CUDA graph
+    torch.cuda.set_stream(stream)
     smp.set_stream(stream.cuda_stream)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if a.profile_only:
+        for _ in range(a.warmup + a.steps):
+            smp.sample(mode, sync=False)
+        barrier()
+        print(json.dumps({"profile_only": True, "workload": a.workload, "mode": a.mode, "stats": smp.stats()}))
+        return
 
     # ---- device-timed throughput (inputs resident)
     for _ in range(a.warmup):
@@ -237,7 +254,7 @@ def main():
     total_edges = float(tot[0])
 
     if rank == 0:
-        nb = next_bytes(app, st, steps, S)
+        nb = next_bytes(app, st, steps, S, sample_parallel=(mode == 2))
         next_ms, next_launches = ph["next"]
         achieved = nb / (next_ms * 1e-3) / 1e9 if next_ms > 0 else 0.0
         cb = None

@@ -164,6 +164,13 @@ struct nd_sampler {
   unsigned long long *d_stats = nullptr;  // [8]
   int *d_status = nullptr;
   NdRadixScratch radix;
+  // counting inversion of the walk maps: per-vertex counters, their exclusive scan, chunk sums, ranks
+  uint32_t *d_cnt = nullptr, *d_offs = nullptr, *d_bsum = nullptr;
+  int32_t *d_rank = nullptr;
+  // the step loop of a walk job captured once per mode and replayed (needs a non-default stream)
+  cudaGraphExec_t graph_exec[3] = {nullptr, nullptr, nullptr};
+  int graph_launches[3] = {0, 0, 0};
+  bool graph_off = false;
   // k-hop LB bins
   int32_t *d_runs = nullptr;      // work lists
   int64_t runs_cap = 0;

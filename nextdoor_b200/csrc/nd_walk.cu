@@ -203,6 +203,144 @@ walk_next_tp_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample
   if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
 }
 
+// ---------------------------------------------------------------- next() + counting inversion (load-balanced mode)
+//
+// The transit ids are a dense key space (< V) and the map holds at most one pair per walk, so
+// the inversion does not need a multi-pass sort: next() takes a ticket on its new transit
+// (atomicAdd on cnt[transit], the ticket is the pair's rank inside the transit's run), two small
+// kernels turn the counters into run offsets (chunk sums, then per-chunk exclusive scan, which
+// also clears the counters and publishes the live count), and one kernel moves every pair to
+// offs[transit] + rank.  16 B read + 8 B written per pair beside 12 B per vertex of counter
+// traffic, against 2-3 radix passes.  The order of the pairs inside one transit's run depends on
+// the order the tickets were drawn; results do not, because every draw is keyed by the sample.
+
+constexpr int CNT_THREADS = 256;
+constexpr int CNT_PER_THREAD = 8;
+constexpr int CNT_CHUNK = CNT_THREADS * CNT_PER_THREAD;  // counters per CTA
+
+template <int APP, bool COUNT>
+__global__ void __launch_bounds__(256)
+walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample,
+                       const int32_t *__restrict__ in_key, const int32_t *__restrict__ in_val,
+                       const int32_t *__restrict__ d_n, int32_t *__restrict__ out_key,
+                       int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
+                       uint32_t *__restrict__ cnt, int32_t *__restrict__ tmp_step, int32_t *__restrict__ len,
+                       int32_t *__restrict__ state, int *__restrict__ status,
+                       unsigned long long *__restrict__ stats) {
+  Events ev;
+  const int n = *d_n;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int32_t t = in_key[i];
+    const int32_t s = in_val[i];
+    int32_t nbr = -1;
+    if (t < 0 || t >= g.V) {
+      atomicOr(status, ND_DEV_BAD_TRANSIT);
+    } else {
+      const int32_t rs = __ldg(g.row_ptr + t);
+      const int32_t deg = __ldg(g.row_ptr + t + 1) - rs;
+      if (deg > 0) {
+        Rng rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
+        int32_t st = 0;
+        if (APP == ND_APP_NODE2VEC && step > 0) st = state[s];
+        nbr = app_next<APP>(g, wp, step, t, rs, deg, st, rng, status, ev);
+        if (APP == ND_APP_NODE2VEC && nbr >= 0) state[s] = st;
+      }
+    }
+    if (nbr >= 0) tmp_step[s] = nbr; else len[s] = step;
+    if (COUNT) {
+      out_key[i] = nbr >= 0 ? nbr : g.V;
+      if (nbr >= 0) {
+        out_val[i] = s;
+        out_rank[i] = (int32_t)atomicAdd(&cnt[nbr], 1u);
+      }
+    }
+  }
+  if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
+}
+
+__global__ void __launch_bounds__(CNT_THREADS)
+cnt_chunk_sum_kernel(const uint32_t *__restrict__ cnt, int32_t V, uint32_t *__restrict__ bsum) {
+  __shared__ uint32_t wsum[CNT_THREADS / 32];
+  const int base = blockIdx.x * CNT_CHUNK;
+  uint32_t part = 0;
+#pragma unroll
+  for (int r = 0; r < CNT_PER_THREAD; r++) {
+    const int i = base + r * CNT_THREADS + threadIdx.x;
+    if (i < V) part += cnt[i];
+  }
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t t = 0;
+    for (int w = 0; w < CNT_THREADS / 32; w++) t += wsum[w];
+    bsum[blockIdx.x] = t;
+  }
+}
+
+// CTA b: start of its chunk = sum of the chunk sums before it; exclusive scan of its counters into
+// offs; counters cleared for the next step; the last CTA publishes the number of live pairs.
+__global__ void __launch_bounds__(CNT_THREADS)
+cnt_scan_kernel(uint32_t *__restrict__ cnt, int32_t V, const uint32_t *__restrict__ bsum,
+                uint32_t *__restrict__ offs, int32_t *__restrict__ d_n_out) {
+  __shared__ uint32_t wsum[CNT_THREADS / 32];
+  __shared__ uint32_t base_sh;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t part = 0;
+  for (int i = threadIdx.x; i < (int)blockIdx.x; i += CNT_THREADS) part += bsum[i];
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) wsum[warp] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t t = 0;
+    for (int w = 0; w < CNT_THREADS / 32; w++) t += wsum[w];
+    base_sh = t;
+  }
+  __syncthreads();
+  // each thread owns 8 consecutive counters (one 32-byte sector)
+  const int first = blockIdx.x * CNT_CHUNK + threadIdx.x * CNT_PER_THREAD;
+  uint32_t c[CNT_PER_THREAD];
+  uint32_t tsum = 0;
+#pragma unroll
+  for (int r = 0; r < CNT_PER_THREAD; r++) {
+    c[r] = first + r < V ? cnt[first + r] : 0u;
+    tsum += c[r];
+  }
+  uint32_t inc = tsum;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  __syncthreads();  // wsum reuse
+  if (lane == 31) wsum[warp] = inc;
+  __syncthreads();
+  uint32_t run = base_sh + inc - tsum;
+  for (int w = 0; w < warp; w++) run += wsum[w];
+#pragma unroll
+  for (int r = 0; r < CNT_PER_THREAD; r++) {
+    if (first + r < V) {
+      offs[first + r] = run;
+      cnt[first + r] = 0u;
+    }
+    run += c[r];
+  }
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == CNT_THREADS - 1) *d_n_out = (int32_t)run;
+}
+
+__global__ void __launch_bounds__(256)
+walk_scatter_kernel(const int32_t *__restrict__ d_n, int32_t V, const int32_t *__restrict__ ukey,
+                    const int32_t *__restrict__ uval, const int32_t *__restrict__ urank,
+                    const uint32_t *__restrict__ offs, int32_t *__restrict__ okey, int32_t *__restrict__ oval) {
+  const int n = *d_n;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int32_t k = ukey[i];
+    if (k == V) continue;
+    const uint32_t pos = __ldg(offs + k) + (uint32_t)urank[i];
+    okey[pos] = k;
+    oval[pos] = uval[i];
+  }
+}
+
 // ---------------------------------------------------------------- sample-parallel: a thread owns a walk
 
 template <int APP>
@@ -341,6 +479,14 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_CUDA(cudaMalloc(&s->d_nlive, sizeof(int32_t) * (size_t)(steps + 2)));
   const int key_bits = nd_bit_length((uint32_t)(s->g->V > 1 ? s->g->V - 1 : 1));
   ND_TRY(nd_radix_scratch_alloc(&s->radix, key_bits, S));
+  // counting inversion (load-balanced mode)
+  const size_t V = (size_t)s->g->V;
+  const size_t chunks = (V + CNT_CHUNK - 1) / CNT_CHUNK;
+  ND_CUDA(cudaMalloc(&s->d_cnt, sizeof(uint32_t) * V));
+  ND_CUDA(cudaMalloc(&s->d_offs, sizeof(uint32_t) * V));
+  ND_CUDA(cudaMalloc(&s->d_bsum, sizeof(uint32_t) * chunks));
+  ND_CUDA(cudaMalloc(&s->d_rank, sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
+  ND_CUDA(cudaMemset(s->d_cnt, 0, sizeof(uint32_t) * V));
   return ND_OK;
 }
 
@@ -367,14 +513,18 @@ int nd_sampler_build_initial_map(nd_sampler *s) {
   return ND_OK;
 }
 
-int nd_walk_sample(nd_sampler *s, int mode) {
+// Enqueues one whole job on the sampler's stream: no host synchronisation, no allocation, every
+// size that changes from step to step is read from device memory -- so the sequence can be
+// captured into a CUDA graph once and replayed.
+static int walk_enqueue(nd_sampler *s, int mode) {
   const int64_t S = s->S;
   const int steps = s->p.steps;
   const int app = s->p.app;
+  cudaStream_t st = s->stream;
   WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps};
   const int rblocks = (int)((S + 255) / 256);
-  walk_reset_kernel<<<rblocks > 1 ? rblocks : 1, 256, 0, s->stream>>>(s->d_initial, s->g->V, S, steps, s->d_len,
-                                                                               s->d_state, s->d_stats);
+  walk_reset_kernel<<<rblocks > 1 ? rblocks : 1, 256, 0, st>>>(s->d_initial, s->g->V, S, steps, s->d_len, s->d_state, s->d_stats);
+  nd_count_launches(1);
   if (mode == ND_MODE_SAMPLE_PARALLEL) {
     nd_phase_begin(s, ND_PHASE_NEXT);
     switch (app) {
@@ -384,7 +534,9 @@ int nd_walk_sample(nd_sampler *s, int mode) {
       default: launch_sp<ND_APP_NODE2VEC>(s, wp); break;
     }
     nd_phase_end(s);
-  } else {
+    nd_count_launches(1);
+  } else if (mode == ND_MODE_TRANSIT_PARALLEL) {
+    // plain transit-parallel: sort-based inversion, first digit histogram fused into next()
     const NdRadixPlan &pl = s->radix.plan;
     const int64_t tiles = pl.max_tiles;
     const int grid = (int)(tiles < (int64_t)s->dev.sms * 4 ? tiles : (int64_t)s->dev.sms * 4);
@@ -402,6 +554,7 @@ int nd_walk_sample(nd_sampler *s, int mode) {
         default: launch_next_tp<ND_APP_NODE2VEC>(s, wp, step, !last, grid, in_key, in_val, d_n, ok, ov); break;
       }
       nd_phase_end(s);
+      nd_count_launches(1);
       if (last) break;
       nd_phase_begin(s, ND_PHASE_INVERT);
       NdSortArrays arr;
@@ -409,7 +562,7 @@ int nd_walk_sample(nd_sampler *s, int mode) {
       arr.a[0] = (uint32_t *)s->d_map_key[cur]; arr.a[1] = (uint32_t *)s->d_map_val[cur]; arr.a[2] = nullptr;
       arr.b[0] = (uint32_t *)s->d_map_key[cur ^ 1]; arr.b[1] = (uint32_t *)s->d_map_val[cur ^ 1]; arr.b[2] = nullptr;
       bool in_b = false;
-      ND_TRY(nd_radix_sort(s->dev, s->stream, &s->radix, s->radix.plan, arr, 0, d_n, s->d_nlive + step + 1, true,
+      ND_TRY(nd_radix_sort(s->dev, st, &s->radix, s->radix.plan, arr, 0, d_n, s->d_nlive + step + 1, true,
                            (uint32_t)s->g->V, true, &in_b));
       nd_phase_end(s);
       const int res = in_b ? (cur ^ 1) : cur;
@@ -417,13 +570,81 @@ int nd_walk_sample(nd_sampler *s, int mode) {
       in_val = s->d_map_val[res];
       cur = res ^ 1;
     }
+  } else {
+    // load-balanced transit-parallel: next() draws tickets, counting inversion
+    const int V = s->g->V;
+    const int chunks = (V + CNT_CHUNK - 1) / CNT_CHUNK;
+    const int64_t blocks = (S + 255) / 256;
+    const int grid = (int)(blocks < (int64_t)s->dev.sms * 8 ? blocks : (int64_t)s->dev.sms * 8);
+    NdGraphView gv = nd_view(s->g);
+    const int32_t *in_key = s->d_init_key, *in_val = s->d_init_val;
+    int32_t *ukey = s->d_map_key[0], *uval = s->d_map_val[0];   // unsorted pairs written by next()
+    int32_t *skey = s->d_map_key[1], *sval = s->d_map_val[1];   // sorted map of the following step
+    for (int step = 0; step < steps; step++) {
+      const bool last = step == steps - 1;
+      const int32_t *d_n = s->d_nlive + step;
+      int32_t *tmp_step = s->d_tmp + (int64_t)step * S;
+      nd_phase_begin(s, ND_PHASE_NEXT);
+#define ND_LAUNCH_COUNT(APPID)                                                                                         \
+  if (last) walk_next_count_kernel<APPID, false><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats); \
+  else walk_next_count_kernel<APPID, true><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats);
+      switch (app) {
+        case ND_APP_UNIFORM_WALK: ND_LAUNCH_COUNT(ND_APP_UNIFORM_WALK) break;
+        case ND_APP_DEEPWALK: ND_LAUNCH_COUNT(ND_APP_DEEPWALK) break;
+        case ND_APP_PPR: ND_LAUNCH_COUNT(ND_APP_PPR) break;
+        default: ND_LAUNCH_COUNT(ND_APP_NODE2VEC) break;
+      }
+#undef ND_LAUNCH_COUNT
+      nd_phase_end(s);
+      nd_count_launches(1);
+      if (last) break;
+      nd_phase_begin(s, ND_PHASE_INVERT);
+      cnt_chunk_sum_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, s->d_bsum);
+      cnt_scan_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, s->d_bsum, s->d_offs, s->d_nlive + step + 1);
+      walk_scatter_kernel<<<grid, 256, 0, st>>>(d_n, V, ukey, uval, s->d_rank, s->d_offs, skey, sval);
+      nd_phase_end(s);
+      nd_count_launches(3);
+      in_key = skey;
+      in_val = sval;
+    }
   }
   nd_phase_begin(s, ND_PHASE_FINALIZE);
   const int64_t groups = (S + FIN_SAMPLES - 1) / FIN_SAMPLES;
   const int fgrid = (int)(groups < (int64_t)s->dev.sms * 16 ? groups : (int64_t)s->dev.sms * 16);
-  walk_finalize_kernel<<<fgrid > 0 ? fgrid : 1, FIN_THREADS, 0, s->stream>>>(s->d_tmp, s->d_len, S, steps, s->g->V, s->d_out, s->d_stats);
+  walk_finalize_kernel<<<fgrid > 0 ? fgrid : 1, FIN_THREADS, 0, st>>>(s->d_tmp, s->d_len, S, steps, s->g->V, s->d_out, s->d_stats);
   nd_phase_end(s);
-  nd_count_launches(2 + (mode == ND_MODE_SAMPLE_PARALLEL ? 1 : steps));  // reset, finalize, next()
+  nd_count_launches(1);
   ND_CUDA(cudaGetLastError());
+  return ND_OK;
+}
+
+int nd_walk_sample(nd_sampler *s, int mode) {
+  // Graph replay needs a capturable stream (not the legacy default stream) and no phase timers.
+  const bool capturable = s->stream != nullptr && s->stream != cudaStreamLegacy && s->stream != cudaStreamPerThread;
+  if (!capturable || s->timer.on || s->graph_off) return walk_enqueue(s, mode);
+  if (!s->graph_exec[mode]) {
+    const long long before = nd_launch_count();
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      cudaGetLastError();
+      s->graph_off = true;
+      return walk_enqueue(s, mode);
+    }
+    const int rc = walk_enqueue(s, mode);
+    const cudaError_t ec = cudaStreamEndCapture(s->stream, &graph);
+    s->graph_launches[mode] = (int)(nd_launch_count() - before);
+    nd_count_launches(-s->graph_launches[mode]);  // nothing ran yet
+    if (rc != ND_OK || ec != cudaSuccess || !graph ||
+        cudaGraphInstantiate(&s->graph_exec[mode], graph, 0) != cudaSuccess) {
+      cudaGetLastError();
+      if (graph) cudaGraphDestroy(graph);
+      s->graph_exec[mode] = nullptr;
+      s->graph_off = true;
+      return walk_enqueue(s, mode);
+    }
+    cudaGraphDestroy(graph);
+  }
+  ND_CUDA(cudaGraphLaunch(s->graph_exec[mode], s->stream));
+  nd_count_launches(s->graph_launches[mode]);
   return ND_OK;
 }

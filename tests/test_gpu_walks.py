@@ -125,3 +125,27 @@ def test_full_size_properties(nd, ndo, app):
     init = (np.arange(V) % V).astype(np.int32)
     assert ndo.check_sampled_vertices(hg, opr, V, init, out) == 0
     assert s.stats()["sampled_edges"] == int((out != V).sum())
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("app", [1, 3])
+def test_graph_replay_on_user_stream(nd, ndo, small_graph, app, mode):
+    """On a caller's (non-default) stream the step loop is captured into a CUDA graph at the first
+    sample() and replayed afterwards; new seeds must flow through the replay."""
+    import torch
+    g = _graph(nd, small_graph)
+    pr = nd.app_params(app, steps=25, seed=5)
+    opr = ndo.make_params(app, steps=25, seed=5)
+    S = 4000
+    s = nd.Sampler(g, pr, num_samples=S)
+    st = torch.cuda.Stream()
+    s.set_stream(st.cuda_stream)
+    exp = ndo.sample(small_graph, opr, S)["out"]
+    for _ in range(3):
+        s.sample(mode)
+        assert np.array_equal(s.final_samples(), exp)
+    init2 = np.random.default_rng(1).integers(0, small_graph.V, S).astype(np.int32)
+    s.set_initial(init2)
+    s.sample(mode)
+    assert np.array_equal(s.final_samples(), ndo.sample(small_graph, opr, S, initial=init2)["out"])
+    assert s.stats()["sampled_edges"] == int((s.final_samples() != small_graph.V).sum())
