@@ -261,12 +261,12 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
 __global__ void __launch_bounds__(CNT_THREADS)
 cnt_chunk_sum_kernel(const uint32_t *__restrict__ cnt, int32_t V, uint32_t *__restrict__ bsum) {
   __shared__ uint32_t wsum[CNT_THREADS / 32];
-  const int base = blockIdx.x * CNT_CHUNK;
+  const uint4 *src = reinterpret_cast<const uint4 *>(cnt + (size_t)blockIdx.x * CNT_CHUNK);
   uint32_t part = 0;
 #pragma unroll
-  for (int r = 0; r < CNT_PER_THREAD; r++) {
-    const int i = base + r * CNT_THREADS + threadIdx.x;
-    if (i < V) part += cnt[i];
+  for (int r = 0; r < CNT_PER_THREAD / 4; r++) {
+    const uint4 a = src[r * CNT_THREADS + threadIdx.x];
+    part += a.x + a.y + a.z + a.w;
   }
   for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
   if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = part;
@@ -298,14 +298,17 @@ cnt_scan_kernel(uint32_t *__restrict__ cnt, int32_t V, const uint32_t *__restric
   }
   __syncthreads();
   // each thread owns 8 consecutive counters (one 32-byte sector)
+  // (the arrays are padded to whole chunks, so the two 16-byte accesses never leave them)
   const int first = blockIdx.x * CNT_CHUNK + threadIdx.x * CNT_PER_THREAD;
   uint32_t c[CNT_PER_THREAD];
   uint32_t tsum = 0;
-#pragma unroll
-  for (int r = 0; r < CNT_PER_THREAD; r++) {
-    c[r] = first + r < V ? cnt[first + r] : 0u;
-    tsum += c[r];
+  {
+    const uint4 a = *reinterpret_cast<const uint4 *>(cnt + first);
+    const uint4 b = *reinterpret_cast<const uint4 *>(cnt + first + 4);
+    c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
   }
+#pragma unroll
+  for (int r = 0; r < CNT_PER_THREAD; r++) tsum += c[r];
   uint32_t inc = tsum;
   for (int o = 1; o < 32; o <<= 1) {
     const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
@@ -316,14 +319,13 @@ cnt_scan_kernel(uint32_t *__restrict__ cnt, int32_t V, const uint32_t *__restric
   __syncthreads();
   uint32_t run = base_sh + inc - tsum;
   for (int w = 0; w < warp; w++) run += wsum[w];
+  uint32_t o[CNT_PER_THREAD];
 #pragma unroll
-  for (int r = 0; r < CNT_PER_THREAD; r++) {
-    if (first + r < V) {
-      offs[first + r] = run;
-      cnt[first + r] = 0u;
-    }
-    run += c[r];
-  }
+  for (int r = 0; r < CNT_PER_THREAD; r++) { o[r] = run; run += c[r]; }
+  *reinterpret_cast<uint4 *>(offs + first) = make_uint4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<uint4 *>(offs + first + 4) = make_uint4(o[4], o[5], o[6], o[7]);
+  *reinterpret_cast<uint4 *>(cnt + first) = make_uint4(0u, 0u, 0u, 0u);
+  *reinterpret_cast<uint4 *>(cnt + first + 4) = make_uint4(0u, 0u, 0u, 0u);
   if (blockIdx.x == gridDim.x - 1 && threadIdx.x == CNT_THREADS - 1) *d_n_out = (int32_t)run;
 }
 
@@ -482,11 +484,11 @@ int nd_walk_alloc(nd_sampler *s) {
   // counting inversion (load-balanced mode)
   const size_t V = (size_t)s->g->V;
   const size_t chunks = (V + CNT_CHUNK - 1) / CNT_CHUNK;
-  ND_CUDA(cudaMalloc(&s->d_cnt, sizeof(uint32_t) * V));
-  ND_CUDA(cudaMalloc(&s->d_offs, sizeof(uint32_t) * V));
+  ND_CUDA(cudaMalloc(&s->d_cnt, sizeof(uint32_t) * chunks * CNT_CHUNK));   // padded to whole chunks
+  ND_CUDA(cudaMalloc(&s->d_offs, sizeof(uint32_t) * chunks * CNT_CHUNK));
   ND_CUDA(cudaMalloc(&s->d_bsum, sizeof(uint32_t) * chunks));
   ND_CUDA(cudaMalloc(&s->d_rank, sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
-  ND_CUDA(cudaMemset(s->d_cnt, 0, sizeof(uint32_t) * V));
+  ND_CUDA(cudaMemset(s->d_cnt, 0, sizeof(uint32_t) * chunks * CNT_CHUNK));
   return ND_OK;
 }
 
@@ -575,7 +577,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     const int V = s->g->V;
     const int chunks = (V + CNT_CHUNK - 1) / CNT_CHUNK;
     const int64_t blocks = (S + 255) / 256;
-    const int grid = (int)(blocks < (int64_t)s->dev.sms * 8 ? blocks : (int64_t)s->dev.sms * 8);
+    const int grid = (int)(blocks < (int64_t)s->dev.sms * 64 ? blocks : (int64_t)s->dev.sms * 64);
     NdGraphView gv = nd_view(s->g);
     const int32_t *in_key = s->d_init_key, *in_val = s->d_init_val;
     int32_t *ukey = s->d_map_key[0], *uval = s->d_map_val[0];   // unsorted pairs written by next()

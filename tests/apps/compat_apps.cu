@@ -1,0 +1,205 @@
+// Test applications written against NextDoor's App struct contract, compiled through the
+// source-compatibility headers of include/nextdoor/ and run on the GPU by tests/test_gpu_compat.py.
+// The first group is this project's own; with -DNDC_WITH_REFERENCE the reference's application
+// files are compiled in as well, unchanged, from the reference tree (never copied into the repo).
+#include "nextdoor.cu"
+#include "libNextDoor.hpp"
+#include "main.cu"
+
+// ---------------------------------------------------------------- own apps
+
+struct PlainSample {};
+
+struct WalkBase {
+  __host__ __device__ int stepSize(int) { return 1; }
+  __host__ __device__ int samplingType() { return SamplingType::IndividualNeighborhood; }
+  __host__ __device__ OutputFormat outputFormat() { return SampledVertices; }
+  __host__ __device__ EdgePos_t numSamples(CSR *graph) { return 3 * graph->get_n_vertices() + 7; }
+  template <class SampleType>
+  __host__ std::vector<VertexID_t> initialSample(int sampleIdx, CSR *graph, SampleType &) {
+    return std::vector<VertexID_t>(1, sampleIdx % graph->get_n_vertices());
+  }
+  __host__ __device__ EdgePos_t initialSampleSize(CSR *) { return 1; }
+  __host__ __device__ bool hasExplicitTransits() { return false; }
+  template <class SampleType>
+  __host__ __device__ VertexID_t stepTransits(int, const VertexID_t, SampleType &, int, curandState *) { return -1; }
+  template <class SampleType>
+  __host__ SampleType initializeSample(CSR *, const VertexID_t) { return SampleType(); }
+};
+
+// uniform neighbour, 40 steps
+struct OwnUniformWalk : WalkBase {
+  __host__ __device__ int steps() { return 40; }
+  template <typename SampleType, typename EdgeArray, typename WeightArray>
+  __device__ inline VertexID next(int, CSRPartition *, const VertexID *, const VertexID, SampleType *, const float,
+                                  EdgeArray &edges, WeightArray &, const EdgePos_t numEdges, const VertexID_t, curandState *state) {
+    return edges[RandNumGen::rand_int(state, numEdges)];
+  }
+};
+
+// weight-proportional neighbour by rejection against the row's maximum weight, 30 steps
+struct OwnWeightedWalk : WalkBase {
+  __host__ __device__ int steps() { return 30; }
+  template <typename SampleType, typename EdgeArray, typename WeightArray>
+  __device__ inline VertexID next(int, CSRPartition *, const VertexID *, const VertexID, SampleType *, const float maxW,
+                                  EdgeArray &edges, WeightArray &weights, const EdgePos_t numEdges, const VertexID_t, curandState *state) {
+    if (numEdges == 1) return edges[0];
+    for (;;) {
+      const EdgePos_t pick = RandNumGen::rand_int(state, numEdges);
+      const float bar = curand_uniform(state) * maxW;
+      if (!(bar > weights[pick])) return edges[pick];
+    }
+  }
+};
+
+// second-order walk with return/in-out biases; the previous vertex lives in the sample
+struct PrevSample { VertexID prev; };
+struct OwnSecondOrderWalk : WalkBase {
+  __host__ __device__ int steps() { return 25; }
+  template <typename SampleType, typename EdgeArray, typename WeightArray>
+  __device__ inline VertexID next(int step, CSRPartition *csr, const VertexID *transit, const VertexID, SampleType *sample,
+                                  const float, EdgeArray &edges, WeightArray &, const EdgePos_t numEdges, const VertexID_t,
+                                  curandState *state) {
+    const float p = 0.5f, q = 2.0f;
+    if (numEdges == 1 || step == 0) { sample->prev = *transit; return edges[0]; }
+    const float bound = fmaxf(fmaxf(p, 1.0f / q), 1.0f);
+    const VertexID before = sample->prev;
+    for (;;) {
+      const EdgePos_t pick = RandNumGen::rand_int(state, numEdges);
+      const VertexID cand = edges[pick];
+      const float bar = curand_uniform(state) * bound;
+      float keep = 1.0f;
+      if (cand == before) keep = p;
+      else {
+        const CSR::Edge *lst = csr->get_edges(before);
+        if (utils::binarySearch(lst, cand, csr->get_n_edges_for_vertex(before))) keep = 1.0f / q;
+      }
+      if (bar < keep) { sample->prev = *transit; return cand; }
+    }
+  }
+};
+
+// three hops, fan-outs 4, 3, 2, with replacement
+struct OwnKHop : WalkBase {
+  __host__ __device__ int steps() { return 3; }
+  __host__ __device__ int stepSize(int k) { return k == 0 ? 4 : (k == 1 ? 3 : 2); }
+  __host__ __device__ EdgePos_t numSamples(CSR *graph) { return graph->get_n_vertices(); }
+  template <typename SampleType, typename EdgeArray, typename WeightArray>
+  __device__ inline VertexID next(int, CSRPartition *, const VertexID *, const VertexID, SampleType *, const float,
+                                  EdgeArray &edges, WeightArray &, const EdgePos_t numEdges, const VertexID_t, curandState *state) {
+    return edges[RandNumGen::rand_int(state, numEdges)];
+  }
+};
+
+// collective layer sampling, 2 layers of 8 from batches of 8: a vertex uniform over the graph plus
+// the batch-to-layer adjacency kept in the sample
+struct LayerSample { int row[2][64]; int col[2][64]; };
+struct OwnLayerApp {
+  __host__ __device__ int steps() { return 2; }
+  __host__ __device__ int stepSize(int) { return 8; }
+  __host__ __device__ int samplingType() { return SamplingType::CollectiveNeighborhood; }
+  __host__ __device__ OutputFormat outputFormat() { return AdjacencyMatrix; }
+  __host__ EdgePos_t numSamples(CSR *) { return 500; }
+  __host__ __device__ EdgePos_t initialSampleSize(CSR *) { return 8; }
+  __host__ __device__ bool hasExplicitTransits() { return false; }
+  template <class SampleType>
+  __device__ VertexID_t stepTransits(int, const VertexID_t, SampleType &, int, curandState *) { return -1; }
+  template <class SampleType>
+  __host__ std::vector<VertexID_t> initialSample(int sampleIdx, CSR *graph, SampleType &) {
+    std::vector<VertexID_t> v;
+    for (int i = 0; i < 8; i++) v.push_back((sampleIdx * 8 + i) % graph->get_n_vertices());
+    return v;
+  }
+  template <class SampleType>
+  __host__ SampleType initializeSample(CSR *, const VertexID_t) {
+    SampleType s;
+    for (int l = 0; l < 2; l++) for (int e = 0; e < 64; e++) { s.row[l][e] = -1; s.col[l][e] = -1; }
+    return s;
+  }
+  template <typename SampleType, typename EdgeArray, typename WeightArray>
+  __device__ inline VertexID next(int step, CSRPartition *csr, const VertexID *transits, const VertexID, SampleType *sample,
+                                  const float, EdgeArray &, WeightArray &, const EdgePos_t, const VertexID_t slot, curandState *state) {
+    const VertexID pick = RandNumGen::rand_int(state, csr->get_n_vertices());
+    for (int i = 0; i < 8; i++) {
+      const bool e = csr->has_edge_logn(transits[i], pick);
+      sample->row[step][i * 8 + slot] = e ? i : -1;
+      sample->col[step][i * 8 + slot] = e ? slot : -1;
+    }
+    return pick;
+  }
+};
+
+// ---------------------------------------------------------------- the reference's own application files
+#ifdef NDC_WITH_REFERENCE
+#include "apps/randomwalks/randomWalks.cu"
+#undef VERTICES_PER_SAMPLE
+#include "apps/khop/khop.cu"
+#undef VERTICES_PER_SAMPLE
+#define main ndc_reference_example_main
+#include "uniformRandWalk.cu"
+#undef main
+#endif
+
+// ---------------------------------------------------------------- runners
+
+template <class SampleType, typename App>
+static int run_app(const char *file, const char *kernel, int lb, int32_t *out, int64_t cap, int64_t *n_out, int *fs_out,
+                   NextDoorData<SampleType, App> *keep = nullptr) {
+  Graph graph;
+  CSR *csr = loadGraph(graph, (char *)file, (char *)"edge-list", (char *)"binary");
+  if (!csr) return 1;
+  NextDoorData<SampleType, App> local;
+  NextDoorData<SampleType, App> &data = keep ? *keep : local;
+  if (!allocNextDoorDataOnGPU<SampleType, App>(csr, data)) return 2;
+  data.gpuCSRPartitions = transferCSRToGPUs(data, csr);
+  bool ok = strcmp(kernel, "SampleParallel") == 0 ? doSampleParallelSampling<SampleType, App>(csr, data)
+                                                  : doTransitParallelSampling<SampleType, App>(csr, data, lb != 0);
+  if (!ok) return 3;
+  std::vector<VertexID_t> &fin = getFinalSamples(data);
+  *n_out = (int64_t)fin.size();
+  *fs_out = getFinalSampleSize<App>();
+  if ((int64_t)fin.size() > cap) return 4;
+  memcpy(out, fin.data(), sizeof(int32_t) * fin.size());
+  freeDeviceData(data);
+  delete csr;
+  return 0;
+}
+
+extern "C" int ndc_run(int which, const char *file, const char *kernel, int lb, int32_t *out, int64_t cap, int64_t *n_out,
+                       int *fs_out, int32_t *adj_row, int32_t *adj_col) {
+  switch (which) {
+    case 0: return run_app<PlainSample, OwnUniformWalk>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 1: return run_app<PlainSample, OwnWeightedWalk>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 2: return run_app<PrevSample, OwnSecondOrderWalk>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 3: return run_app<PlainSample, OwnKHop>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 4: {
+      NextDoorData<LayerSample, OwnLayerApp> data;
+      int rc = run_app<LayerSample, OwnLayerApp>(file, kernel, lb, out, cap, n_out, fs_out, &data);
+      if (rc == 0 && adj_row)
+        for (size_t s = 0; s < data.samples.size(); s++) {
+          memcpy(adj_row + s * 128, data.samples[s].row, sizeof(int) * 128);
+          memcpy(adj_col + s * 128, data.samples[s].col, sizeof(int) * 128);
+        }
+      return rc;
+    }
+#ifdef NDC_WITH_REFERENCE
+    case 10: return run_app<UniformRandomWalkSample, UniformRandomWalkApp>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 11: return run_app<DummySample, DeepWalkApp>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 12: return run_app<DummySample, PPRApp>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 13: return run_app<Node2VecSample, Node2VecApp>(file, kernel, lb, out, cap, n_out, fs_out);
+    case 14: return run_app<KHopSample, KHopApp>(file, kernel, lb, out, cap, n_out, fs_out);
+#endif
+    default: return -1;
+  }
+}
+
+extern "C" int ndc_has_reference_apps(void) {
+#ifdef NDC_WITH_REFERENCE
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// the command line of the reference's per-app binaries, for the own uniform walk
+extern "C" int ndc_app_main(int argc, char **argv) { return appMain<PlainSample, OwnUniformWalk>(argc, argv, nullptr); }

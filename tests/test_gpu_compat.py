@@ -1,0 +1,106 @@
+"""GPU tests of the source-compatibility layer (include/nextdoor/): applications written against the
+reference's App struct contract, compiled unchanged through those headers, must produce the oracle's
+samples bit for bit in both kernel types.  Where the reference tree was present at build time the
+reference's OWN application files (randomWalks.cu, khop.cu, example/uniformRandWalk.cu) are part of
+the test library too."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+OWN = os.path.join(HERE, "apps", "libnd_compat_apps.so")
+WITH_REF = os.path.join(HERE, "apps", "_ref", "libnd_compat_ref.so")
+KERNELS = [("TransitParallel", 0), ("TransitParallel", 1), ("SampleParallel", 0)]
+
+
+@pytest.fixture(scope="module")
+def world(ndo, tmp_path_factory):
+    src, dst, w = ndo.rmat_records(1500, 9000, seed=8)
+    path = str(tmp_path_factory.mktemp("compat") / "graph.bin")
+    ndo.write_edge_list_binary(path, src, dst, w)
+    return path, ndo.csr_from_records(src, dst, w)   # vertex count = max id + 1, as the loader decides
+
+
+def _lib(path):
+    L = C.CDLL(path)
+    L.ndc_run.restype = C.c_int
+    L.ndc_run.argtypes = [C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_void_p, C.c_int64, C.POINTER(C.c_int64),
+                          C.POINTER(C.c_int), C.c_void_p, C.c_void_p]
+    return L
+
+
+def _run(L, which, path, kernel, lb, cap, adj=None):
+    out = np.empty(cap, np.int32)
+    n, fs = C.c_int64(0), C.c_int(0)
+    ar = ac = None
+    if adj:
+        ar, ac = np.empty(adj, np.int32), np.empty(adj, np.int32)
+    rc = L.ndc_run(which, path.encode(), kernel.encode(), lb, out.ctypes.data, cap, C.byref(n), C.byref(fs),
+                   ar.ctypes.data if adj else None, ac.ctypes.data if adj else None)
+    assert rc == 0, f"ndc_run({which}) failed with {rc}"
+    return out[:n.value].reshape(-1, fs.value), ar, ac
+
+
+@pytest.mark.parametrize("kernel,lb", KERNELS)
+def test_own_apps_match_oracle(ndo, world, kernel, lb):
+    path, hg = world
+    L = _lib(OWN)
+    V = hg.V
+    cases = [
+        (0, ndo.make_params(ndo.APP_UNIFORM_WALK, steps=40), 3 * V + 7),
+        (1, ndo.make_params(ndo.APP_DEEPWALK, steps=30), 3 * V + 7),
+        (2, ndo.make_params(ndo.APP_NODE2VEC, steps=25, p=0.5, q=2.0, n2v_ref_compat=0), 3 * V + 7),
+        (3, ndo.make_params(ndo.APP_KHOP, fanout=[4, 3, 2]), V),
+    ]
+    for which, pr, S in cases:
+        fs = ndo.final_sample_size(pr)
+        got, _, _ = _run(L, which, path, kernel, lb, S * fs)
+        exp = ndo.sample(hg, pr, S)["out"]
+        assert got.shape == exp.shape
+        assert np.array_equal(got, exp), f"app {which} kernel {kernel} lb {lb}"
+
+
+def test_own_collective_app_matches_oracle(ndo, world):
+    path, hg = world
+    L = _lib(OWN)
+    pr = ndo.make_params(ndo.APP_FASTGCN_REF, steps=2, fanout=8, batch=8)
+    S = 500
+    got, ar, ac = _run(L, 4, path, "SampleParallel", 0, S * 16, adj=S * 128)
+    exp = ndo.sample(hg, pr, S)
+    assert np.array_equal(got, exp["out"])
+    assert np.array_equal(ar, exp["adj_row"]) and np.array_equal(ac, exp["adj_col"])
+
+
+@pytest.mark.parametrize("kernel,lb", KERNELS)
+def test_reference_app_files_drop_in(ndo, world, kernel, lb):
+    if not os.path.exists(WITH_REF):
+        pytest.skip("built without the reference tree")
+    path, hg = world
+    L = _lib(WITH_REF)
+    V = hg.V
+    cases = [(10, ndo.APP_UNIFORM_WALK, V), (11, ndo.APP_DEEPWALK, 100 * V), (12, ndo.APP_PPR, 100 * V),
+             (13, ndo.APP_NODE2VEC, 100 * V), (14, ndo.APP_KHOP, V)]
+    for which, app, S in cases:
+        pr = ndo.make_params(app)          # the reference's compile-time constants
+        fs = ndo.final_sample_size(pr)
+        got, _, _ = _run(L, which, path, kernel, lb, S * fs)
+        exp = ndo.sample(hg, pr, S)["out"]
+        assert np.array_equal(got, exp), f"reference app {which} kernel {kernel} lb {lb}"
+
+
+def test_app_main_command_line(ndo, world, capfd):
+    path, hg = world
+    L = _lib(OWN)
+    args = [b"app", b"-g", path.encode(), b"-t", b"edge-list", b"-f", b"binary", b"-n", b"1", b"-k", b"TransitParallel", b"-l"]
+    argv = (C.c_char_p * len(args))(*args)
+    assert L.ndc_app_main(len(args), argv) == 0
+    outp = capfd.readouterr().out
+    pr = ndo.make_params(ndo.APP_UNIFORM_WALK, steps=40)
+    exp = ndo.sample(hg, pr, 3 * hg.V + 7)["counters"]["sampled_edges"]
+    assert f"totalSampledVertices {exp}" in outp
+    bad = [b"app", b"-g", b"/nonexistent.bin", b"-t", b"edge-list", b"-f", b"binary"]
+    assert L.ndc_app_main(len(bad), (C.c_char_p * len(bad))(*bad)) == 0
+    assert "not found" in capfd.readouterr().out
