@@ -238,6 +238,25 @@ def main():
     clocks.stop_flag = True
     ms_e2e = x0.elapsed_time(x1)
 
+    # ---- the final sample gather (the only step that crosses NVLink): sample() + NCCL all-gather
+    ms_gather = None
+    if world > 1:
+        from nextdoor_b200 import dist as nd_dist
+        local = nd_dist.device_samples(smp)
+        for _ in range(2):
+            smp.sample(mode, sync=False)
+            nd_dist.all_gather_samples(local, world * S)
+        barrier()
+        y0, y1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        y0.record(stream)
+        for _ in range(a.steps):
+            smp.sample(mode, sync=False)
+            full = nd_dist.all_gather_samples(local, world * S)
+        y1.record(stream)
+        barrier()
+        ms_gather = y0.elapsed_time(y1)
+        del full
+
     # ---- per-phase device time of one instrumented pass (roofline of the next() kernel)
     smp.set_profiling(True)
     smp.sample(mode)
@@ -245,12 +264,12 @@ def main():
     smp.set_profiling(False)
     st = smp.stats()
 
-    tms = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
+    tms = torch.tensor([ms, ms_e2e, ms_gather or 0.0], dtype=torch.float64, device="cuda")
     tot = torch.tensor([float(edges_step)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-    ms, ms_e2e = float(tms[0]), float(tms[1])
+    ms, ms_e2e, ms_gather = float(tms[0]), float(tms[1]), float(tms[2])
     total_edges = float(tot[0])
 
     if rank == 0:
@@ -273,6 +292,9 @@ def main():
             "e2e": {"value": total_edges * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
                     "h2d_bytes_per_step": int(S * 4), "d2h_bytes_per_step": int(S * steps * 4)},
             "gpu_launches": int(launches),
+            "with_gather": None if world == 1 else {
+                "value": total_edges * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",
+                "collective": "ncclAllGather of the final samples", "bytes_per_rank_per_step": int(S * steps * 4)},
             "roofline": {"bound": "hbm", "kernel": "walk_next_tp_kernel" if mode != 2 else "walk_sp_kernel",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "peak_kind": f"of {peak_kind}", "traffic": None, "launches": next_launches,
