@@ -1,14 +1,15 @@
 #!/usr/bin/env python
 """Benchmark of the sampling hot path: sampled edges/s, device-timed.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2] [--mode tp_lb]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-A "step" is one sample() pass over the whole batch of walks.  Default workload (one GPU):
+A "step" is one sample() pass over the whole batch of samples.  Default workload (one GPU):
 node2vec p=2 q=0.5, length 100, one walk per vertex, on a synthetic R-MAT graph with 2^20
-vertices and 16M undirected edges (seed 0, generated on the device).  With N ranks every rank
-holds a replica of the graph and samples its own range of seeds (weak scaling: rank r walks the
-samples [r*V, (r+1)*V), sample i starting at vertex i % V); no collective is on the data path.
+vertices and 16M undirected edges (seed 0, generated on the device), transit-parallel mode with
+load balancing.  With N ranks every rank holds a replica of the graph and samples its own range
+of seeds (weak scaling: rank r owns the samples [r*S, (r+1)*S)); no collective is on the data
+path, the final all-gather is timed separately.
 
 Prints ONE JSON line (rank 0).  --impl reference times the reference's own next() bodies on the
 host cores (oracle/_ref, else the oracle port) on a bounded sample of the same workload.
@@ -28,16 +29,24 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+WALK, KHOP, COLL = "walk", "khop", "collective"
 WORKLOADS = {
-    # name: (app, V, M undirected, steps, params)
-    "c1": dict(app=0, V=56944, M=400_000, steps=100, desc="uniform walk, 56,944 vertices, ~800K CSR entries"),
-    "c2": dict(app=3, V=1 << 20, M=1 << 24, steps=100, desc="node2vec p=2 q=0.5, 2^20 vertices, 16M undirected edges"),
-    "c2u": dict(app=0, V=1 << 20, M=1 << 24, steps=100, desc="uniform walk on the c2 graph"),
-    "c2d": dict(app=1, V=1 << 20, M=1 << 24, steps=100, desc="DeepWalk (weighted rejection) on the c2 graph"),
-    "c5": dict(app=2, V=1 << 24, M=1 << 28, steps=100, stop_prob=0.15, desc="weighted PPR stop 0.15, 2^24 vertices, 256M undirected edges"),
-    "c5s": dict(app=2, V=1 << 22, M=1 << 26, steps=100, stop_prob=0.15, desc="weighted PPR stop 0.15, 2^22 vertices, 64M undirected edges"),
+    "c1": dict(kind=WALK, app=0, V=56944, M=400_000, steps=100, desc="uniform walk, length 100, one walk per vertex, 56,944 vertices, ~800K CSR entries"),
+    "c2": dict(kind=WALK, app=3, V=1 << 20, M=1 << 24, steps=100, desc="node2vec p=2 q=0.5, length 100, one walk per vertex, 2^20 vertices, 16M undirected edges"),
+    "c2u": dict(kind=WALK, app=0, V=1 << 20, M=1 << 24, steps=100, desc="uniform walk on the c2 graph"),
+    "c2d": dict(kind=WALK, app=1, V=1 << 20, M=1 << 24, steps=100, desc="DeepWalk (weighted rejection) on the c2 graph"),
+    "c3": dict(kind=KHOP, app=5, V=1 << 21, M=1 << 25, fanout=[25, 10], S=256 * 1024,
+               desc="GraphSAGE 2-hop, fan-out 25 then 10 without replacement + distinct, 256 batches of 1024 uniform seeds, 2^21 vertices, 32M undirected edges"),
+    "c3r": dict(kind=KHOP, app=4, V=1 << 21, M=1 << 25, fanout=[25, 10], S=256 * 1024,
+                desc="k-hop with replacement (the reference's KHopApp) on the c3 graph and seeds"),
+    "c4f": dict(kind=COLL, app=8, V=1 << 20, M=1 << 24, steps=2, L=64, B=64, S=1024,
+                desc="FastGCN importance sampling (degree^2), 2 layers x 64, 1024 batches of 64 uniform seeds, 2^20 vertices, 16M undirected edges"),
+    "c4l": dict(kind=COLL, app=9, V=1 << 20, M=1 << 24, steps=2, L=64, B=64, S=1024,
+                desc="LADIES importance sampling (squared row-normalised weights), 2 layers x 64, 1024 batches of 64 uniform seeds, c4 graph"),
+    "c5": dict(kind=WALK, app=2, V=1 << 24, M=1 << 28, steps=100, stop_prob=0.15, desc="weighted PPR, stop probability 0.15, max length 100, one walk per vertex, 2^24 vertices, 256M undirected edges"),
+    "c5s": dict(kind=WALK, app=2, V=1 << 22, M=1 << 26, steps=100, stop_prob=0.15, desc="weighted PPR stop 0.15 on 2^22 vertices, 64M undirected edges"),
 }
-APP_NAMES = {0: "uniform_walk", 1: "deepwalk", 2: "ppr", 3: "node2vec"}
+APP_NAMES = {0: "uniform_walk", 1: "deepwalk", 2: "ppr", 3: "node2vec", 4: "khop", 5: "khop_distinct", 8: "fastgcn_is", 9: "ladies_is"}
 MODES = {"tp": 0, "tp_lb": 1, "sp": 2}
 
 
@@ -80,53 +89,88 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.rows)}
 
 
-def next_bytes(app, st, steps, S, sample_parallel=False):
-    """Algorithmic bytes the next() launches of one sample() move, from the device's own event
-    counters: per live pair 8 B map-in + 8 B row offsets; per sampled edge 4 B neighbour + 4 B
-    output; 8 B map-out per pair of every step but the last; weighted apps + 4 B max weight per
-    next() and 4 B per weight read; node2vec + 4 B load and 4 B store of the previous vertex,
-    8 B for its row, and per try 4 B candidate + 4 B per binary-search probe."""
+def params_for(mod, wl, seed):
+    """AppParams (product) or oracle Params for a workload; `mod` is nextdoor_b200.api or oracle.ndo."""
+    make = mod.app_params if hasattr(mod, "app_params") else mod.make_params
+    if wl["kind"] == WALK:
+        return make(wl["app"], steps=wl["steps"], seed=seed, stop_prob=wl.get("stop_prob", 0.01))
+    if wl["kind"] == KHOP:
+        return make(wl["app"], fanout=wl["fanout"], seed=seed)
+    return make(wl["app"], steps=wl["steps"], fanout=wl["L"], batch=wl["B"], seed=seed)
+
+
+def seeds_for(wl, first, S):
+    """Initial transits of samples [first, first+S): walks start sample i at vertex i % V; k-hop and
+    collective batches draw their seeds uniformly (numpy Philox stream keyed by the sample range)."""
+    V = wl["V"]
+    if wl["kind"] == WALK:
+        return (np.arange(first, first + S, dtype=np.int64) % V).astype(np.int32)
+    per = 1 if wl["kind"] == KHOP else wl["B"]
+    rng = np.random.Generator(np.random.Philox(key=first + 1))
+    return rng.integers(0, V, S * per, dtype=np.int64).astype(np.int32)
+
+
+def next_bytes(wl, st, mode):
+    """Algorithmic bytes of the next() launches of one sample(), from the device's event counters.
+    Walks: per live pair 8 B map-in + 8 B row offsets, per sampled edge 4 B neighbour + 4 B output,
+    8 B map-out per pair of every step but the last (no maps in sample-parallel mode); weighted
+    apps + 4 B max weight per next() and 4 B per weight read; node2vec + previous vertex (4+4 B,
+    kept in a register in sample-parallel mode), 8 B for its row, and per try 4 B candidate + 4 B per
+    binary-search probe.  k-hop: per pair 8 B map-in + 8 B row offsets, per neighbour 4 B + 4 B,
+    8 B map-out per neighbour of every hop but the last.  Collective: 4 B per gathered neighbour id
+    (+4 B weight for LADIES), 8 B per unique candidate, 8 B per sampled vertex."""
     pairs, edges = st["live_pairs"], st["sampled_edges"]
-    if sample_parallel:   # no maps: row offsets per visited transit, neighbour + staged output per edge
+    app = wl["app"]
+    if wl["kind"] == WALK:
+        steps = wl["steps"]
         b = 8 * pairs + 8 * edges
+        if mode != 2:
+            b += 8 * pairs + 8 * pairs * (steps - 1) / steps
         if app in (1, 2):
             b += 4 * pairs + 4 * st["weight_tries"]
         if app == 3:
-            b += 8 * pairs + 4 * st["n2v_tries"] + 4 * st["n2v_probes"]
+            b += (16 if mode != 2 else 8) * pairs + 4 * st["n2v_tries"] + 4 * st["n2v_probes"]
         return b
-    b = 16 * pairs + 8 * edges + 8 * pairs * (steps - 1) / steps
-    if app in (1, 2):
-        b += 4 * pairs + 4 * st["weight_tries"]
-    if app == 3:
-        b += 16 * pairs + 4 * st["n2v_tries"] + 4 * st["n2v_probes"]
-    return b
+    if wl["kind"] == KHOP:
+        f = wl["fanout"]
+        last_share = 1.0  # neighbours of the last hop carry no map-out
+        n, tot = 1, 0
+        for k in f:
+            n *= k
+            tot += n
+        last_share = n / tot
+        return (16 if mode != 2 else 8) * pairs + 8 * edges + (8 * edges * (1 - last_share) if mode != 2 else 0)
+    return (8 if app == 9 else 4) * st["union_ids"] + 8 * st["union_unique"] + 8 * edges
 
 
 def cpu_baseline(hg, wl, seed, budget_s=12.0):
-    """The reference's own next() bodies (oracle/_ref) where built, else the oracle port, on all
-    host threads, on a bounded sample of the workload's walks."""
+    """The reference's own next() bodies (oracle/_ref) where they exist for the workload, else the
+    oracle port, on all host threads, on a bounded prefix of the workload's samples."""
     from oracle import ndo
-    app, steps = wl["app"], wl["steps"]
-    use_ref = ndo.ref_available() and not (app == 2 and abs(wl.get("stop_prob", 0.01) - 0.01) > 1e-9)
-    pr = ndo.make_params(app, steps=steps, seed=seed, stop_prob=wl.get("stop_prob", 0.01))
+    app = wl["app"]
+    use_ref = ndo.ref_available() and wl["kind"] == WALK and not (app == 2 and abs(wl.get("stop_prob", 0.01) - 0.01) > 1e-9)
+    use_ref = use_ref or (ndo.ref_available() and app == 4 and wl["fanout"] == [25, 10])
+    pr = params_for(ndo, wl, seed)
     threads = ndo.ref().ref_max_threads() if use_ref else ndo.lib().ndo_max_threads()
+    S_all = wl.get("S", wl["V"])
 
     def run(n):
+        init = seeds_for(wl, 0, n)
         t0 = time.perf_counter()
         if use_ref:
-            e = ndo.ref_sample(hg, app, steps, n, seed=seed)["sampled_edges"]
+            e = ndo.ref_sample(hg, app, pr.steps, n, seed=seed, initial=init)["sampled_edges"]
         else:
-            e = ndo.sample(hg, pr, n, want_adj=False)["counters"]["sampled_edges"]
+            e = ndo.sample(hg, pr, n, initial=init, want_adj=False)["counters"]["sampled_edges"]
         return e, time.perf_counter() - t0
 
-    n = min(hg.V, 20000)
+    n = max(1, min(S_all, 20000 if wl["kind"] == WALK else (2000 if wl["kind"] == KHOP else 8)))
     e, t = run(n)
-    n2 = int(min(hg.V, max(n, n * budget_s / max(t, 1e-3))))
+    n2 = int(min(S_all, max(n, n * budget_s / max(t, 1e-3))))
     if n2 > 2 * n:
         n = n2
         e, t = run(n)
     return {"value": e / t, "unit": "sampled edges/s", "cores": int(threads), "kind": "reference" if use_ref else "port",
-            "sample": f"first {n} of {hg.V} walks x {steps} steps, {t:.2f} s"}
+            "sample": f"first {n} of {S_all} samples, {t:.2f} s"}
 
 
 def main():
@@ -135,7 +179,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--workload", default="c2", choices=list(WORKLOADS))
     ap.add_argument("--mode", default="tp_lb", choices=list(MODES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-only", action="store_true",
@@ -147,18 +191,19 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     seed = 0
     hbm_peak, peak_kind = peaks()
+    V, M, app = wl["V"], wl["M"], wl["app"]
+    S = wl.get("S", V)
 
     if a.impl == "reference":
         if rank != 0:
             return
-        # graph built on the host by the oracle's generator (same definition as the device one)
         from oracle import ndo
         t0 = time.perf_counter()
-        hg = ndo.rmat_graph(wl["V"], wl["M"], seed)
+        hg = ndo.rmat_graph(V, M, seed)      # same generator definition as the device one
         t_graph = time.perf_counter() - t0
         vals = []
         for i in range(a.warmup + a.steps):
-            cb = cpu_baseline(hg, wl, seed, budget_s=8.0)
+            cb = cpu_baseline(hg, wl, seed, budget_s=6.0)
             if i >= a.warmup:
                 vals.append(cb)
         v = float(np.mean([c["value"] for c in vals]))
@@ -167,7 +212,7 @@ def main():
             "impl": "reference", "metric": "sampled edges/sec", "value": v, "unit": "sampled edges/s", "n_gpus": a.gpus,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int32", "data": "synthetic",
-            "config": {"workload": f"{a.workload}: {wl['desc']}", "graph_build_s": round(t_graph, 2)},
+            "config": {"workload": f"{a.workload}: {wl['desc']}", "host_graph_build_s": round(t_graph, 2)},
             "cpu_baseline": cb, "e2e": {"value": v, "unit": "sampled edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
@@ -177,13 +222,13 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    V, M, steps, app = wl["V"], wl["M"], wl["steps"], wl["app"]
     mode = MODES[a.mode]
     g = nd.Graph.rmat(V, M, seed, device=local)
-    pr = nd.app_params(app, steps=steps, seed=seed, stop_prob=wl.get("stop_prob", 0.01))
-    S = V
+    pr = params_for(nd, wl, seed)
     first = rank * S
-    smp = nd.Sampler(g, pr, num_samples=S, first_sample=first)
+    init_np = seeds_for(wl, first, S)
+    smp = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=init_np)
+    fs = smp.fs
     stream = torch.cuda.Stream()          # a non-default stream, so the library can replay its CUDA graph
     torch.cuda.set_stream(stream)
     smp.set_stream(stream.cuda_stream)
@@ -215,24 +260,23 @@ def main():
     barrier()
     ms = e0.elapsed_time(e1)
     launches = nd.launch_count() - l0
-    st = smp.stats()
-    edges_step = st["sampled_edges"]
+    edges_step = smp.stats()["sampled_edges"]
 
     # ---- end to end through the public API with host buffers: seeds H2D, sample, result D2H
-    init_host = torch.from_numpy(((np.arange(first, first + S) % V).astype(np.int32))).pin_memory()
-    out_host = torch.empty(S * steps, dtype=torch.int32).pin_memory()
-    init_np, out_np = init_host.numpy(), out_host.numpy()
+    init_host = torch.from_numpy(init_np).pin_memory()
+    out_host = torch.empty(S * fs, dtype=torch.int32).pin_memory()
+    init_pin, out_pin = init_host.numpy(), out_host.numpy()
     for _ in range(2):
-        smp.set_initial(init_np)
+        smp.set_initial(init_pin)
         smp.sample(mode, sync=False)
-        smp.final_samples(out_np)
+        smp.final_samples(out_pin)
     barrier()
     x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     x0.record(stream)
     for _ in range(a.steps):
-        smp.set_initial(init_np)
+        smp.set_initial(init_pin)
         smp.sample(mode, sync=False)
-        smp.final_samples(out_np)
+        smp.final_samples(out_pin)
     x1.record(stream)
     barrier()
     clocks.stop_flag = True
@@ -242,22 +286,22 @@ def main():
     ms_gather = None
     if world > 1:
         from nextdoor_b200 import dist as nd_dist
-        local = nd_dist.device_samples(smp)
+        shard_t = nd_dist.device_samples(smp)
         for _ in range(2):
             smp.sample(mode, sync=False)
-            nd_dist.all_gather_samples(local, world * S)
+            nd_dist.all_gather_samples(shard_t, world * S)
         barrier()
         y0, y1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         y0.record(stream)
         for _ in range(a.steps):
             smp.sample(mode, sync=False)
-            full = nd_dist.all_gather_samples(local, world * S)
+            full = nd_dist.all_gather_samples(shard_t, world * S)
         y1.record(stream)
         barrier()
         ms_gather = y0.elapsed_time(y1)
         del full
 
-    # ---- per-phase device time of one instrumented pass (roofline of the next() kernel)
+    # ---- per-phase device time of one instrumented pass (roofline of the next() kernels)
     smp.set_profiling(True)
     smp.sample(mode)
     ph = smp.phase_ms()
@@ -273,9 +317,12 @@ def main():
     total_edges = float(tot[0])
 
     if rank == 0:
-        nb = next_bytes(app, st, steps, S, sample_parallel=(mode == 2))
-        next_ms, next_launches = ph["next"]
+        nb = next_bytes(wl, st, mode)
+        next_ms, next_launches = ph["next"] if wl["kind"] != COLL else (ph["next"][0] + ph["collect"][0], ph["next"][1] + ph["collect"][1])
         achieved = nb / (next_ms * 1e-3) / 1e9 if next_ms > 0 else 0.0
+        kernel = {WALK: {0: "walk_next_tp_kernel", 1: "walk_next_count_kernel", 2: "walk_sp_kernel"}[mode],
+                  KHOP: "khop_pairs_kernel + khop_staged_kernel" if mode == 1 else "khop_pairs_kernel",
+                  COLL: "coll_gather/sort/weigh/sample kernels"}[wl["kind"]]
         cb = None
         if world == 1 and not a.no_cpu_baseline:
             from oracle import ndo
@@ -286,20 +333,22 @@ def main():
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
             "config": {"workload": f"{a.workload}: {wl['desc']}", "app": APP_NAMES[app], "mode": a.mode,
-                       "samples_per_gpu": S, "walk_length": steps, "graph": f"R-MAT a=.57 b=.19 c=.19 d=.05 seed 0, V={V}, CSR entries={g.E}, max degree={g.max_degree}",
-                       "l2": "working set (graph + walk buffers) larger than L2; no flush between steps",
+                       "samples_per_gpu": S, "final_sample_size": fs,
+                       "graph": f"R-MAT a=.57 b=.19 c=.19 d=.05 seed 0, V={V}, CSR entries={g.E}, max degree={g.max_degree}",
+                       "l2": "working set (graph + sample buffers) larger than L2; no flush between steps",
                        "sampled_edges_per_step_per_gpu": edges_step},
             "e2e": {"value": total_edges * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
-                    "h2d_bytes_per_step": int(S * 4), "d2h_bytes_per_step": int(S * steps * 4)},
+                    "h2d_bytes_per_step": int(init_np.nbytes), "d2h_bytes_per_step": int(S * fs * 4)},
             "gpu_launches": int(launches),
             "with_gather": None if world == 1 else {
                 "value": total_edges * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",
-                "collective": "ncclAllGather of the final samples", "bytes_per_rank_per_step": int(S * steps * 4)},
-            "roofline": {"bound": "hbm", "kernel": "walk_next_tp_kernel" if mode != 2 else "walk_sp_kernel",
-                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "peak_kind": f"of {peak_kind}", "traffic": None, "launches": next_launches,
-                         "avg_launch_us": 1e3 * next_ms / max(next_launches, 1), "algorithmic_bytes_per_pass": nb},
+                "collective": "ncclAllGather of the final samples", "bytes_per_rank_per_step": int(S * fs * 4)},
+            "roofline": {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "launches": next_launches, "avg_launch_us": 1e3 * next_ms / max(next_launches, 1),
+                         "algorithmic_bytes_per_pass": nb},
             "phases_ms": {k: round(v[0], 4) for k, v in ph.items()},
+            "counters": st,
             "cpu_baseline": cb,
             "clocks": clocks.summary(),
         }
