@@ -77,6 +77,79 @@ distinct_kernel(int32_t *__restrict__ data, int64_t n_segments, int32_t seg_len,
   }
 }
 
+// Segments of up to 256 ids: one warp per segment, the whole segment in registers (E ids per
+// lane, lane l owns positions l*E .. l*E+E-1).  The bitonic network exchanges inside a lane for
+// strides below E and with warp shuffles above; run heads are ranked with a shuffle scan.  No shared
+// memory and no block barrier.
+template <int E>
+__global__ void __launch_bounds__(DTHREADS)
+distinct_warp_kernel(int32_t *__restrict__ data, int64_t n_segments, int32_t seg_len, int32_t seg_stride,
+                     int32_t invalid, int32_t *__restrict__ counts, int32_t counts_stride) {
+  constexpr int P = 32 * E;
+  const int lane = threadIdx.x & 31;
+  const int64_t seg = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (seg >= n_segments) return;  // whole warps leave together
+  int32_t *base = data + seg * (int64_t)seg_stride;
+  int32_t v[E];
+#pragma unroll
+  for (int e = 0; e < E; e++) {
+    const int g = lane * E + e;
+    int32_t x = 0x7fffffff;
+    if (g < seg_len) {
+      x = base[g];
+      if (x == invalid || x < 0) x = 0x7fffffff;
+    }
+    v[e] = x;
+  }
+#pragma unroll
+  for (int size = 2; size <= P; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (stride >= E) {
+        const int ls = stride / E;
+        const bool lower = (lane & ls) == 0;
+#pragma unroll
+        for (int e = 0; e < E; e++) {
+          const int32_t other = __shfl_xor_sync(0xffffffffu, v[e], ls);
+          const bool up = (((lane * E + e) & size) == 0);
+          v[e] = (lower == up) ? min(v[e], other) : max(v[e], other);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; e++) {
+          if ((e & stride) == 0) {
+            const bool up = (((lane * E + e) & size) == 0);
+            const int32_t a = v[e], b = v[e + stride];
+            if ((a > b) == up) { v[e] = b; v[e + stride] = a; }
+          }
+        }
+      }
+    }
+  }
+  int32_t before = __shfl_up_sync(0xffffffffu, v[E - 1], 1);  // last id of the lane to the left
+  bool head[E];
+  int cnt = 0;
+#pragma unroll
+  for (int e = 0; e < E; e++) {
+    const int32_t prev = e == 0 ? before : v[e - 1];
+    head[e] = v[e] != 0x7fffffff && ((lane == 0 && e == 0) || v[e] != prev);
+    cnt += head[e] ? 1 : 0;
+  }
+  int inc = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  const int uniq = __shfl_sync(0xffffffffu, inc, 31);
+  int pos = inc - cnt;
+#pragma unroll
+  for (int e = 0; e < E; e++)
+    if (head[e]) base[pos++] = v[e];
+  for (int i = uniq + lane; i < seg_len; i += 32) base[i] = invalid;
+  if (lane == 0 && counts) counts[seg * (int64_t)counts_stride] = uniq;
+}
+
 }  // namespace
 
 int nd_distinct_launch(cudaStream_t st, int32_t *data, int64_t n_segments, int32_t seg_len, int32_t seg_stride,
@@ -84,6 +157,17 @@ int nd_distinct_launch(cudaStream_t st, int32_t *data, int64_t n_segments, int32
   ND_REQUIRE(seg_len >= 1 && seg_len <= MAX_SEG, ND_ERR_ARG, "distinct: segment length %d outside [1,%d]", seg_len, MAX_SEG);
   int P = 32;
   while (P < seg_len) P <<= 1;
+  if (P <= 256) {  // a warp per segment, ids in registers
+    const int64_t blocks = (n_segments * 32 + DTHREADS - 1) / DTHREADS;
+    switch (P) {
+      case 32: distinct_warp_kernel<1><<<(unsigned)blocks, DTHREADS, 0, st>>>(data, n_segments, seg_len, seg_stride, invalid, counts, counts_stride); break;
+      case 64: distinct_warp_kernel<2><<<(unsigned)blocks, DTHREADS, 0, st>>>(data, n_segments, seg_len, seg_stride, invalid, counts, counts_stride); break;
+      case 128: distinct_warp_kernel<4><<<(unsigned)blocks, DTHREADS, 0, st>>>(data, n_segments, seg_len, seg_stride, invalid, counts, counts_stride); break;
+      default: distinct_warp_kernel<8><<<(unsigned)blocks, DTHREADS, 0, st>>>(data, n_segments, seg_len, seg_stride, invalid, counts, counts_stride); break;
+    }
+    ND_CUDA(cudaGetLastError());
+    return ND_OK;
+  }
 #define LAUNCH(PP)                                                                                       \
   {                                                                                                      \
     constexpr int G = ((PP) / 2 < 32) ? 32 : (((PP) / 2 > DTHREADS) ? DTHREADS : (PP) / 2);              \

@@ -31,7 +31,7 @@ namespace {
 using ndrng::Rng;
 
 constexpr int KTHREADS = 256;
-constexpr int STAGE_CAP = 12032;         // ints of shared memory for a staged list (47 KB)
+constexpr int STAGE_CAP = 11776;         // ints of shared memory for a staged list (46 KB)
 constexpr int TMA_MIN_INTS = 64;         // below this the list is staged with int4 loads
 constexpr int WAIT_CAP = 1 << 22;        // iteration limit of the mbarrier wait
 constexpr uint8_t FLAG_PLAIN = 1, FLAG_STAGED = 2;
@@ -221,31 +221,51 @@ khop_bin_kernel(NdGraphView g, const int32_t *__restrict__ keys, const int32_t *
                 int item_pairs, int64_t items_cap, uint8_t *__restrict__ flags, int2 *__restrict__ items,
                 BinCounts *__restrict__ bc, int *__restrict__ status) {
   const int n = *d_n;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const int32_t t = keys[i];
-    if (i > 0 && keys[i - 1] == t) continue;
-    if (t < 0 || t >= g.V) continue;
-    int lo = i + 1, hi = n;  // first position whose key differs
-    while (lo < hi) {
-      const int mid = lo + (hi - lo) / 2;
-      if (keys[mid] == t) lo = mid + 1; else hi = mid;
+  const int lane = threadIdx.x & 31;
+  const int warp_id = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int n_warps = (gridDim.x * blockDim.x) >> 5;
+  for (int base = warp_id * 32; base < n; base += n_warps * 32) {
+    // a warp looks at 32 consecutive map positions; run heads are found with one ballot, and a
+    // run that ends inside the window needs no search at all
+    const int i = base + lane;
+    const int32_t t = i < n ? keys[i] : -2;
+    int32_t prev = __shfl_up_sync(0xffffffffu, t, 1);
+    if (lane == 0) prev = base > 0 ? keys[base - 1] : -1;
+    const bool head = i < n && (i == 0 || prev != t);
+    const uint32_t heads = __ballot_sync(0xffffffffu, head);
+    if (!head || t < 0 || t >= g.V) continue;
+    const uint32_t later = lane == 31 ? 0u : (heads & ~((2u << lane) - 1u));
+    int end;
+    if (later) {
+      end = base + __ffs(later) - 1;
+    } else {
+      const int wend = min(base + 32, n);
+      end = wend;
+      if (wend < n && keys[wend] == t) {  // the run leaves the window: bisect for its end
+        int lo = wend + 1, hi = n;
+        while (lo < hi) {
+          const int mid = lo + (hi - lo) / 2;
+          if (keys[mid] == t) lo = mid + 1; else hi = mid;
+        }
+        end = lo;
+      }
     }
-    const int count = lo - i;
+    const int count = end - i;
     const int32_t deg = __ldg(g.row_ptr + t + 1) - __ldg(g.row_ptr + t);
     const int64_t work = (int64_t)count * sw;  // threads the run occupies (src/nextdoor.cu:1565-1573)
     // staging reads deg/8 sectors once; gathering reads up to count*f sectors
-    const bool worth = deg > 0 && (deg <= 64 || (int64_t)deg <= 8ll * count * f);
+    const bool worth = deg > 0 && (int64_t)deg <= 8ll * count * f;
     uint8_t flag = FLAG_PLAIN;
-    if (work >= 32 && worth) {  // LoadBalancingThreshold::BlockLevel
+    if (work >= 256 && worth) {  // a CTA's worth of draws: LoadBalancingThreshold::GridLevel
       const int n_items = (count + item_pairs - 1) / item_pairs;
       const int at = atomicAdd(&bc->items, n_items);
       if ((int64_t)at + n_items <= items_cap) {
         for (int c = 0; c < n_items; c++) {
           const int st = i + c * item_pairs;
-          items[at + c] = make_int2(st, min(item_pairs, lo - st));
+          items[at + c] = make_int2(st, min(item_pairs, end - st));
         }
         flag = FLAG_STAGED;
-        atomicAdd(work >= 256 ? &bc->grid_transits : &bc->block_transits, 1);  // GridLevel
+        atomicAdd(n_items > 1 ? &bc->grid_transits : &bc->block_transits, 1);
       } else {
         atomicOr(status, ND_DEV_OVERFLOW);
       }
@@ -264,6 +284,7 @@ khop_staged_kernel(NdGraphView g, KhopParams kp, const int32_t *__restrict__ in_
                    int *__restrict__ status, unsigned long long *__restrict__ stats) {
   __shared__ __align__(128) int32_t stage[STAGE_CAP];
   __shared__ __align__(8) uint64_t bar;
+  __shared__ int32_t sh_q[KTHREADS];   // pair ids of the work item (item_pairs <= KTHREADS)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int per_warp = 32 / kp.sw;
   const int sub = lane / kp.sw, j = lane % kp.sw;
@@ -287,6 +308,7 @@ khop_staged_kernel(NdGraphView g, KhopParams kp, const int32_t *__restrict__ in_
     const int32_t a1 = (rs + deg + 3) & ~3;
     const int win = a1 - a0;
     bool staged = win <= STAGE_CAP;
+    sh_q[threadIdx.x] = threadIdx.x < item.y ? in_val[item.x + threadIdx.x] : 0;  // one coalesced load, overlaps the copy
     if (staged) {
       if (win >= TMA_MIN_INTS && tma_ok) {
         if (threadIdx.x == 0) {
@@ -311,13 +333,15 @@ khop_staged_kernel(NdGraphView g, KhopParams kp, const int32_t *__restrict__ in_
         for (int v = threadIdx.x; v < win / 4; v += KTHREADS) dst[v] = __ldg(src + v);
         __syncthreads();
       }
+    } else {
+      __syncthreads();  // list longer than the staging buffer: only sh_q needs publishing
     }
     const int32_t *sh_edges = stage + (rs - a0);
     const int32_t *gl_edges = g.col + rs;
     for (int p0 = 0; p0 < item.y; p0 += subs_per_cta) {
       const int p = p0 + warp * per_warp + sub;
       const bool ok = p < item.y;
-      const int32_t q = ok ? in_val[item.x + p] : 0;
+      const int32_t q = ok ? sh_q[p] : 0;
       if (ok && j == 0) pairs_cnt++;
       if (staged) process_pair<DISTINCT>(kp, sh_edges, deg, q, out, mkey, mval, j, sub_base, sub_mask, ok, edges_cnt);
       else process_pair<DISTINCT>(kp, gl_edges, deg, q, out, mkey, mval, j, sub_base, sub_mask, ok, edges_cnt);
@@ -437,7 +461,8 @@ int nd_khop_sample(nd_sampler *s, int mode) {
       const bool lb = mode == ND_MODE_TRANSIT_PARALLEL_LB;
       uint8_t *flags = lb ? (uint8_t *)s->d_state : nullptr;
       BinCounts *bc = (BinCounts *)s->d_bin_counts + k;
-      const int item_pairs = 16 * (KTHREADS / kp.sw);  // 16 rounds of a CTA's sub-warps (TRANSITS_PER_THREAD, src/nextdoor.cu:976)
+      // up to 16 rounds of a CTA's sub-warps (TRANSITS_PER_THREAD, src/nextdoor.cu:976), at most one pair per thread
+      const int item_pairs = 16 * (KTHREADS / kp.sw) < KTHREADS ? 16 * (KTHREADS / kp.sw) : KTHREADS;
       if (lb) {
         nd_phase_begin(s, ND_PHASE_BIN);
         khop_bin_kernel<<<grid_for(n_pairs_full, s->dev.sms, 16), KTHREADS, 0, st>>>(gv, in_key, d_n, kp.f, kp.sw, item_pairs, s->runs_cap, flags, (int2 *)s->d_runs, bc, s->d_status);
