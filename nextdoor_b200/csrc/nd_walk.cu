@@ -26,7 +26,28 @@ struct WalkParams {
   float p, q, stop_prob;
   int n2v_compat;
   int steps;
+  const unsigned long long *filter;  // node2vec: adjacency pre-filter of the high-degree vertices (may be null)
 };
+
+// node2vec asks "is v a neighbour of the previous vertex t?" once per try, and t is usually a hub
+// (a 17-probe bisection).  Most answers are "no", so every vertex with at least FILTER_MIN_DEG
+// neighbours gets a blocked Bloom filter over its list: 16 bits per neighbour, stored in the 64-bit
+// words [row_ptr[t]/4, row_ptr[t]/4 + deg/4) of one array (regions of consecutive vertices cannot
+// overlap), two bits per neighbour inside one word, so a test is a single 8-byte load.  A filter
+// has no false negatives: when it says "no" the bisection is skipped, otherwise it runs as usual,
+// and the accepted vertex is the same either way.
+constexpr int FILTER_MIN_DEG = 32;
+
+__device__ __forceinline__ uint32_t filter_mix(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ void filter_slot(int32_t v, uint32_t n_words, uint32_t &word, unsigned long long &mask) {
+  const uint32_t h = filter_mix((uint32_t)v);
+  word = (uint32_t)(((unsigned long long)h * n_words) >> 32);
+  const uint32_t g = filter_mix(h ^ 0x9e3779b9u);
+  mask = (1ull << (g & 63u)) | (1ull << ((g >> 6) & 63u));
+}
 
 constexpr int RETRY_CAP = 1 << 16;
 
@@ -97,14 +118,37 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
       if (is_ret) {
         h = wp.p;
       } else {
-        int32_t l = 0, r = tn - 1;  // utils::binarySearch, src/utils.hpp:30-48
+        // membership of v in the sorted list of t: the answer of utils::binarySearch
+        // (src/utils.hpp:30-48), found with fewer dependent loads
+        int32_t l = 0, r = tn;  // candidates in [l, r)
         bool found = false;
-        while (l <= r) {
-          const int32_t m = l + (r - l) / 2;
-          ev.n2v_probes++;
-          const int32_t am = __ldg(tedges + m);
-          if (am == v) { found = true; break; }
-          if (am < v) l = m + 1; else r = m - 1;
+        if (wp.filter && tn >= FILTER_MIN_DEG) {
+          uint32_t word;
+          unsigned long long mask;
+          filter_slot(v, (uint32_t)tn >> 2, word, mask);
+          ev.n2v_probes += 2;  // one 8-byte load
+          if ((__ldg(wp.filter + ((uint32_t)ts >> 2) + word) & mask) != mask) r = 0;  // certainly not a neighbour
+        }
+        // 5-ary search: the four pivots of a level are loaded together, so a level costs one
+        // memory latency and a 138K-entry list is searched in 8 levels instead of 17
+        while (r - l > 4 && !found) {
+          const int32_t q5 = (r - l) / 5;
+          const int32_t p1 = l + q5, p2 = p1 + q5, p3 = p2 + q5, p4 = p3 + q5;
+          const int32_t e1 = __ldg(tedges + p1), e2 = __ldg(tedges + p2), e3 = __ldg(tedges + p3), e4 = __ldg(tedges + p4);
+          ev.n2v_probes += 4;
+          if (v == e1 || v == e2 || v == e3 || v == e4) found = true;
+          else if (v < e1) r = p1;
+          else if (v < e2) { l = p1 + 1; r = p2; }
+          else if (v < e3) { l = p2 + 1; r = p3; }
+          else if (v < e4) { l = p3 + 1; r = p4; }
+          else l = p4 + 1;
+        }
+        if (!found && r > l) {  // at most four left: load them together
+          int32_t e[4];
+#pragma unroll
+          for (int k = 0; k < 4; k++) e[k] = l + k < r ? __ldg(tedges + l + k) : -1;
+          ev.n2v_probes += r - l;
+          found = v == e[0] || v == e[1] || v == e[2] || v == e[3];
         }
         h = found ? inv_q : 1.0f;
       }
@@ -119,6 +163,24 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
 }
 
 // ---------------------------------------------------------------- set-up kernels
+
+// one warp per vertex: set the two bits of every neighbour in the vertex's filter region
+__global__ void filter_build_kernel(NdGraphView g, unsigned long long *__restrict__ filter) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_id = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t t = warp_id; t < g.V; t += n_warps) {
+    const int32_t rs = g.row_ptr[t], deg = g.row_ptr[t + 1] - rs;
+    if (deg < FILTER_MIN_DEG) continue;
+    unsigned long long *region = filter + ((uint32_t)rs >> 2);
+    for (int e = lane; e < deg; e += 32) {
+      uint32_t word;
+      unsigned long long mask;
+      filter_slot(g.col[rs + e], (uint32_t)deg >> 2, word, mask);
+      atomicOr(region + word, mask);
+    }
+  }
+}
 
 __global__ void walk_reset_kernel(const int32_t *__restrict__ initial, int32_t V, int64_t S, int steps,
                                   int32_t *__restrict__ len, int32_t *__restrict__ state,
@@ -470,7 +532,15 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_REQUIRE(steps >= 1 && steps <= 4096, ND_ERR_ARG, "walk length %d out of range [1,4096]", steps);
   ND_CUDA(cudaMalloc(&s->d_tmp, sizeof(int32_t) * (size_t)S * steps));
   ND_CUDA(cudaMalloc(&s->d_len, sizeof(int32_t) * (size_t)S));
-  if (s->p.app == ND_APP_NODE2VEC) ND_CUDA(cudaMalloc(&s->d_state, sizeof(int32_t) * (size_t)S));
+  if (s->p.app == ND_APP_NODE2VEC) {
+    ND_CUDA(cudaMalloc(&s->d_state, sizeof(int32_t) * (size_t)S));
+    // adjacency pre-filter: 2 bytes per CSR entry, built once per sampler
+    const size_t words = (size_t)(s->g->E / 4) + 2;
+    ND_CUDA(cudaMalloc(&s->d_filter, sizeof(unsigned long long) * words));
+    ND_CUDA(cudaMemset(s->d_filter, 0, sizeof(unsigned long long) * words));
+    filter_build_kernel<<<s->dev.sms * 16, 256>>>(nd_view(s->g), s->d_filter);
+    ND_CUDA(cudaGetLastError());
+  }
   s->map_cap = S;
   for (int i = 0; i < 2; i++) {
     ND_CUDA(cudaMalloc(&s->d_map_key[i], sizeof(int32_t) * (size_t)S));
@@ -523,7 +593,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
   const int steps = s->p.steps;
   const int app = s->p.app;
   cudaStream_t st = s->stream;
-  WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps};
+  WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps, s->d_filter};
   const int rblocks = (int)((S + 255) / 256);
   walk_reset_kernel<<<rblocks > 1 ? rblocks : 1, 256, 0, st>>>(s->d_initial, s->g->V, S, steps, s->d_len, s->d_state, s->d_stats);
   nd_count_launches(1);
