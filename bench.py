@@ -48,6 +48,7 @@ WORKLOADS = {
 }
 APP_NAMES = {0: "uniform_walk", 1: "deepwalk", 2: "ppr", 3: "node2vec", 4: "khop", 5: "khop_distinct", 8: "fastgcn_is", 9: "ladies_is"}
 MODES = {"tp": 0, "tp_lb": 1, "sp": 2}
+E2E_CHUNKS = 2   # the per-step kernels are latency-bound at these sizes: finer chunks cost more than the overlap gains
 
 
 def peaks():
@@ -262,25 +263,28 @@ def main():
     launches = nd.launch_count() - l0
     edges_step = smp.stats()["sampled_edges"]
 
-    # ---- end to end through the public API with host buffers: seeds H2D, sample, result D2H
+    # ---- end to end through the public API with host buffers: seeds H2D from pinned memory,
+    # sample, result D2H into pinned memory.  The job runs as E2E_CHUNKS seed-range chunks
+    # (nextdoor_b200.api.PipelinedSampler): a finished chunk is copied on a second stream while the next one is sampled.
     init_host = torch.from_numpy(init_np).pin_memory()
     out_host = torch.empty(S * fs, dtype=torch.int32).pin_memory()
     init_pin, out_pin = init_host.numpy(), out_host.numpy()
+    copy_stream = torch.cuda.Stream()
+    pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init_np, chunks=E2E_CHUNKS,
+                               stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream)
     for _ in range(2):
-        smp.set_initial(init_pin)
-        smp.sample(mode, sync=False)
-        smp.final_samples(out_pin)
+        pipe.run(init_pin, out_pin, mode)
     barrier()
     x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     x0.record(stream)
     for _ in range(a.steps):
-        smp.set_initial(init_pin)
-        smp.sample(mode, sync=False)
-        smp.final_samples(out_pin)
+        pipe.run(init_pin, out_pin, mode)     # returns when every chunk has landed in out_pin
     x1.record(stream)
     barrier()
     clocks.stop_flag = True
     ms_e2e = x0.elapsed_time(x1)
+    e2e_check = int((out_pin != V).sum()) if wl["kind"] != COLL else None
+    pipe.free()
 
     # ---- the final sample gather (the only step that crosses NVLink): sample() + NCCL all-gather
     ms_gather = None
@@ -338,7 +342,8 @@ def main():
                        "l2": "working set (graph + sample buffers) larger than L2; no flush between steps",
                        "sampled_edges_per_step_per_gpu": edges_step},
             "e2e": {"value": total_edges * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
-                    "h2d_bytes_per_step": int(init_np.nbytes), "d2h_bytes_per_step": int(S * fs * 4)},
+                    "h2d_bytes_per_step": int(init_np.nbytes), "d2h_bytes_per_step": int(S * fs * 4),
+                    "chunks": E2E_CHUNKS, "valid_vertices_in_host_result": e2e_check},
             "gpu_launches": int(launches),
             "with_gather": None if world == 1 else {
                 "value": total_edges * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",

@@ -129,6 +129,12 @@ int nd_sampler_sample(nd_sampler *s, int mode);
 int nd_sampler_sync(nd_sampler *s);
 /* getFinalSamples (src/nextdoor.cu:3211-3237): D2H into `out` (num_samples * finalSampleSize) */
 int nd_sampler_final_samples(nd_sampler *s, int32_t *out);
+/* same copy, enqueued without waiting: on `copy_stream` (a cudaStream_t) after the sampling issued
+ * so far on the sampler's stream, or on the sampler's stream itself when copy_stream is NULL.  With
+ * pinned `out` the copy overlaps the sampling of the next chunk.  Wait for the copy stream
+ * (nd_stream_sync) before reading `out` and before the next sample() of this sampler. */
+int nd_sampler_final_samples_async(nd_sampler *s, int32_t *out, void *copy_stream);
+int nd_stream_sync(int device, void *stream);
 /* zero-copy variant: device address of the same array */
 int nd_sampler_final_samples_device(nd_sampler *s, const int32_t **out);
 /* collective apps: adjacency rows/cols (num_samples*steps*max(batch,L)*L each) and, for the

@@ -71,6 +71,8 @@ _SIGS = {
     "nd_sampler_sample": (C.c_int, [VP, C.c_int]),
     "nd_sampler_sync": (C.c_int, [VP]),
     "nd_sampler_final_samples": (C.c_int, [VP, VP]),
+    "nd_sampler_final_samples_async": (C.c_int, [VP, VP, VP]),
+    "nd_stream_sync": (C.c_int, [C.c_int, VP]),
     "nd_sampler_final_samples_device": (C.c_int, [VP, C.POINTER(VP)]),
     "nd_sampler_aux": (C.c_int, [VP, VP, VP, VP, VP]),
     "nd_sampler_stats": (C.c_int, [VP, VP, C.c_int]),

@@ -189,6 +189,12 @@ class Sampler:
         check(lib.nd_sampler_final_samples(self._h, _ptr(out)))
         return out.reshape(self.S, self.fs)
 
+    def final_samples_async(self, out, copy_stream=None):
+        """Enqueue the device-to-host copy (on `copy_stream`, a raw cudaStream_t, ordered after the
+        sampling issued so far; or on the sampler's own stream).  Synchronise that stream before
+        reading `out`."""
+        check(lib.nd_sampler_final_samples_async(self._h, _ptr(out), C.c_void_p(copy_stream) if copy_stream else None))
+
     def final_samples_device_ptr(self):
         p = C.c_void_p()
         check(lib.nd_sampler_final_samples_device(self._h, C.byref(p)))
@@ -233,6 +239,51 @@ class Sampler:
             self.free()
         except Exception:
             pass
+
+
+class PipelinedSampler:
+    """The job cut into `chunks` seed ranges that are sampled one after the other on one stream
+    while the result of each finished chunk is copied to the host on a second stream, so the
+    device-to-host copy overlaps the sampling of the following chunks.  Output is identical to one
+    Sampler over the whole range: the draws are keyed by the global sample index.
+    `stream` / `copy_stream` are raw cudaStream_t values (a non-default `stream` lets every chunk
+    replay its CUDA graph)."""
+
+    def __init__(self, graph: Graph, params: AppParams, num_samples, first_sample=0, initial=None, chunks=4,
+                 stream=None, copy_stream=None):
+        self.S, self.fs, self.isz = int(num_samples), final_sample_size(params), initial_sample_size(params)
+        self.device, self.copy_stream = graph.device, copy_stream
+        self.parts = []
+        for c in range(chunks):
+            f, n = shard_range(self.S, c, chunks)
+            init = None if initial is None else np.ascontiguousarray(initial[f * self.isz:(f + n) * self.isz], np.int32)
+            smp = Sampler(graph, params, num_samples=n, first_sample=first_sample + f, initial=init)
+            if stream is not None:
+                smp.set_stream(stream)
+            self.parts.append((f, n, smp))
+
+    def run(self, initial_host, out_host, mode=MODE_TRANSIT_PARALLEL_LB):
+        """initial_host / out_host: (pinned) numpy int32 arrays of the whole job; returns after everything landed."""
+        for f, n, smp in self.parts:
+            if initial_host is not None:
+                smp.set_initial(initial_host[f * self.isz:(f + n) * self.isz])
+            smp.sample(mode, sync=False)
+            smp.final_samples_async(out_host[f * self.fs:(f + n) * self.fs], self.copy_stream)
+        for _, _, smp in self.parts:
+            smp.sync()
+        if self.copy_stream:
+            check(lib.nd_stream_sync(self.device, C.c_void_p(self.copy_stream)))
+
+    def stats(self):
+        tot = {}
+        for _, _, smp in self.parts:
+            for k, v in smp.stats().items():
+                tot[k] = tot.get(k, 0) + v
+        return tot
+
+    def free(self):
+        for _, _, smp in self.parts:
+            smp.free()
 
 
 class SamplingModule:

@@ -81,6 +81,7 @@ void free_sampler(nd_sampler *s) {
   cudaFree(s->d_adj_row); cudaFree(s->d_adj_col); cudaFree(s->d_prob); cudaFree(s->d_cand); cudaFree(s->d_cand_w);
   cudaFree(s->d_cnt); cudaFree(s->d_offs); cudaFree(s->d_bsum); cudaFree(s->d_rank); cudaFree(s->d_filter);
   for (int i = 0; i < 3; i++) if (s->graph_exec[i]) cudaGraphExecDestroy(s->graph_exec[i]);
+  if (s->copy_event) cudaEventDestroy(s->copy_event);
   nd_radix_scratch_free(&s->radix);
   for (cudaEvent_t e : s->timer.ev) cudaEventDestroy(e);
   delete s;
@@ -239,6 +240,26 @@ int nd_sampler_final_samples(nd_sampler *s, int32_t *out) {
   ND_REQUIRE(s->sampled, ND_ERR_STATE, "final samples requested before sample()");
   ND_TRY(nd_sampler_sync(s));
   if (s->S > 0) ND_CUDA(cudaMemcpy(out, s->d_out, sizeof(int32_t) * (size_t)s->S * s->fs, cudaMemcpyDeviceToHost));
+  return ND_OK;
+}
+
+int nd_sampler_final_samples_async(nd_sampler *s, int32_t *out, void *copy_stream) {
+  ND_REQUIRE(s && (out || s->S == 0), ND_ERR_ARG, "nd_sampler_final_samples_async: null argument");
+  ND_REQUIRE(s->sampled, ND_ERR_STATE, "final samples requested before sample()");
+  ND_CUDA(cudaSetDevice(s->g->device));
+  cudaStream_t cs = copy_stream ? (cudaStream_t)copy_stream : s->stream;
+  if (cs != s->stream) {  // the copy waits for the sampling enqueued so far, the sampling stream does not wait for the copy
+    if (!s->copy_event) ND_CUDA(cudaEventCreateWithFlags(&s->copy_event, cudaEventDisableTiming));
+    ND_CUDA(cudaEventRecord(s->copy_event, s->stream));
+    ND_CUDA(cudaStreamWaitEvent(cs, s->copy_event, 0));
+  }
+  if (s->S > 0) ND_CUDA(cudaMemcpyAsync(out, s->d_out, sizeof(int32_t) * (size_t)s->S * s->fs, cudaMemcpyDeviceToHost, cs));
+  return ND_OK;
+}
+
+int nd_stream_sync(int device, void *stream) {
+  ND_CUDA(cudaSetDevice(device));
+  ND_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   return ND_OK;
 }
 

@@ -172,6 +172,7 @@ struct nd_sampler {
   cudaGraphExec_t graph_exec[3] = {nullptr, nullptr, nullptr};
   int graph_launches[3] = {0, 0, 0};
   bool graph_off = false;
+  cudaEvent_t copy_event = nullptr;  // orders a result copy on another stream after the sampling
   // k-hop LB bins
   int32_t *d_runs = nullptr;      // work lists
   int64_t runs_cap = 0;

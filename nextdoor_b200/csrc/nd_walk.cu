@@ -71,36 +71,42 @@ struct Events {
 };
 
 // One next() of the app on a transit with n > 0 neighbours; -1 = no vertex.
+// Gathers from the big graph arrays (neighbour ids, weights, filter words) are used once per
+// launch: they are loaded with the streaming policy (evict-first) so that they do not push the
+// small per-sample and per-vertex arrays (maps, counters, staged output row, row offsets) out of L2.
+template <typename T>
+__device__ __forceinline__ T ld_stream(const T *p) { return __ldcs(p); }
+
 template <int APP>
 __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkParams &wp, int step,
                                             int32_t transit, int32_t rs, int32_t n, int32_t &state_t,
                                             Rng &rng, int *status, Events &ev) {
   const int32_t *__restrict__ edges = g.col + rs;
   if (APP == ND_APP_UNIFORM_WALK) {  // example/uniformRandWalk.cu:35-36
-    return __ldg(edges + rng.rand_int(n));
+    return ld_stream(edges + rng.rand_int(n));
   }
   if (APP == ND_APP_DEEPWALK || APP == ND_APP_PPR) {  // randomWalks.cu:74-90, 102-124
     if (APP == ND_APP_PPR) {
       const float pr = rng.uniform();
       if (pr < wp.stop_prob) return -1;
     }
-    if (n == 1) return __ldg(edges);
+    if (n == 1) return ld_stream(edges);
     const float *__restrict__ weights = g.w + rs;
     const float max_w = __ldg(g.max_w + transit);
     int32_t x = rng.rand_int(n);
     float y = __fmul_rn(rng.uniform(), max_w);
     int it = 0;
     ev.weight_tries++;
-    while (y > __ldg(weights + x)) {
+    while (y > ld_stream(weights + x)) {
       if (++it > RETRY_CAP) { atomicOr(status, ND_DEV_RETRY_LIMIT); break; }
       x = rng.rand_int(n);
       y = __fmul_rn(rng.uniform(), max_w);
       ev.weight_tries++;
     }
-    return __ldg(edges + x);
+    return ld_stream(edges + x);
   }
   if (APP == ND_APP_NODE2VEC) {  // randomWalks.cu:141-172
-    if (n == 1 || step == 0) { state_t = transit; return __ldg(edges); }
+    if (n == 1 || step == 0) { state_t = transit; return ld_stream(edges); }
     const float inv_q = __fdiv_rn(1.0f, wp.q);
     float bound = wp.p > inv_q ? wp.p : inv_q;
     if (bound < 1.0f) bound = 1.0f;
@@ -110,7 +116,7 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
     const int32_t *__restrict__ tedges = g.col + ts;
     for (int it = 0;; it++) {
       const int32_t x = rng.rand_int(n);
-      const int32_t v = __ldg(edges + x);
+      const int32_t v = ld_stream(edges + x);
       const float y = __fmul_rn(rng.uniform(), bound);
       float h;
       ev.n2v_tries++;
@@ -127,14 +133,14 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
           unsigned long long mask;
           filter_slot(v, (uint32_t)tn >> 2, word, mask);
           ev.n2v_probes += 2;  // one 8-byte load
-          if ((__ldg(wp.filter + ((uint32_t)ts >> 2) + word) & mask) != mask) r = 0;  // certainly not a neighbour
+          if ((ld_stream(wp.filter + ((uint32_t)ts >> 2) + word) & mask) != mask) r = 0;  // certainly not a neighbour
         }
         // 5-ary search: the four pivots of a level are loaded together, so a level costs one
         // memory latency and a 138K-entry list is searched in 8 levels instead of 17
         while (r - l > 4 && !found) {
           const int32_t q5 = (r - l) / 5;
           const int32_t p1 = l + q5, p2 = p1 + q5, p3 = p2 + q5, p4 = p3 + q5;
-          const int32_t e1 = __ldg(tedges + p1), e2 = __ldg(tedges + p2), e3 = __ldg(tedges + p3), e4 = __ldg(tedges + p4);
+          const int32_t e1 = ld_stream(tedges + p1), e2 = ld_stream(tedges + p2), e3 = ld_stream(tedges + p3), e4 = ld_stream(tedges + p4);
           ev.n2v_probes += 4;
           if (v == e1 || v == e2 || v == e3 || v == e4) found = true;
           else if (v < e1) r = p1;
@@ -146,7 +152,7 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
         if (!found && r > l) {  // at most four left: load them together
           int32_t e[4];
 #pragma unroll
-          for (int k = 0; k < 4; k++) e[k] = l + k < r ? __ldg(tedges + l + k) : -1;
+          for (int k = 0; k < 4; k++) e[k] = l + k < r ? ld_stream(tedges + l + k) : -1;
           ev.n2v_probes += r - l;
           found = v == e[0] || v == e[1] || v == e[2] || v == e[3];
         }
@@ -581,8 +587,7 @@ int nd_sampler_build_initial_map(nd_sampler *s) {
   const int src = in_b ? 1 : 0;
   ND_CUDA(cudaMemcpyAsync(s->d_init_key, s->d_map_key[src], sizeof(int32_t) * n, cudaMemcpyDeviceToDevice, s->stream));
   ND_CUDA(cudaMemcpyAsync(s->d_init_val, s->d_map_val[src], sizeof(int32_t) * n, cudaMemcpyDeviceToDevice, s->stream));
-  ND_CUDA(cudaStreamSynchronize(s->stream));
-  return ND_OK;
+  return ND_OK;  // stream-ordered: no host synchronisation, so chunks on different streams overlap
 }
 
 // Enqueues one whole job on the sampler's stream: no host synchronisation, no allocation, every

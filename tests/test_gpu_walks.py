@@ -149,3 +149,23 @@ def test_graph_replay_on_user_stream(nd, ndo, small_graph, app, mode):
     s.sample(mode)
     assert np.array_equal(s.final_samples(), ndo.sample(small_graph, opr, S, initial=init2)["out"])
     assert s.stats()["sampled_edges"] == int((s.final_samples() != small_graph.V).sum())
+
+
+def test_pipelined_sampler_equals_single_sampler(nd, ndo, small_graph):
+    """Seed-range chunks sampled back to back while finished chunks are copied to pinned memory on a second stream."""
+    import torch
+    g = _graph(nd, small_graph)
+    pr = nd.app_params(2, steps=40, seed=12, stop_prob=0.15)
+    opr = ndo.make_params(2, steps=40, seed=12, stop_prob=0.15)
+    S, first = 10_003, 31
+    init = ((np.arange(first, first + S)) % small_graph.V).astype(np.int32)
+    st, cst = torch.cuda.Stream(), torch.cuda.Stream()
+    pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init, chunks=3, stream=st.cuda_stream, copy_stream=cst.cuda_stream)
+    init_pin = torch.from_numpy(init).pin_memory().numpy()
+    out_pin = torch.empty(S * 40, dtype=torch.int32).pin_memory().numpy()
+    exp = ndo.sample(small_graph, opr, S, first=first, initial=init)
+    for mode in MODES:
+        out_pin[:] = -7
+        pipe.run(init_pin, out_pin, mode)
+        assert np.array_equal(out_pin.reshape(S, 40), exp["out"])
+    assert pipe.stats()["sampled_edges"] == exp["counters"]["sampled_edges"]
