@@ -167,6 +167,7 @@ struct nd_sampler {
   // counting inversion of the walk maps: per-vertex counters, their exclusive scan, chunk sums, ranks
   uint32_t *d_cnt = nullptr, *d_offs = nullptr, *d_bsum = nullptr;
   int32_t *d_rank = nullptr;
+  uint8_t *d_dirty = nullptr;   // per chunk of counters: a ticket was drawn there this step
   unsigned long long *d_filter = nullptr;  // node2vec adjacency pre-filter
   // the step loop of a walk job captured once per mode and replayed (needs a non-default stream)
   cudaGraphExec_t graph_exec[3] = {nullptr, nullptr, nullptr};

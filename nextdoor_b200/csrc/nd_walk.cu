@@ -292,8 +292,8 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
                        const int32_t *__restrict__ in_key, const int32_t *__restrict__ in_val,
                        const int32_t *__restrict__ d_n, int32_t *__restrict__ out_key,
                        int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
-                       uint32_t *__restrict__ cnt, int32_t *__restrict__ tmp_step, int32_t *__restrict__ len,
-                       int32_t *__restrict__ state, int *__restrict__ status,
+                       uint32_t *__restrict__ cnt, uint8_t *__restrict__ dirty, int32_t *__restrict__ tmp_step,
+                       int32_t *__restrict__ len, int32_t *__restrict__ state, int *__restrict__ status,
                        unsigned long long *__restrict__ stats) {
   Events ev;
   const int n = *d_n;
@@ -320,6 +320,10 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
       if (nbr >= 0) {
         out_val[i] = s;
         out_rank[i] = (int32_t)atomicAdd(&cnt[nbr], 1u);
+        if (dirty) {  // this chunk of counters has work for the scan (test first: hub chunks are hit by everyone)
+          uint8_t *d = dirty + nbr / CNT_CHUNK;
+          if (__ldcg(d) == 0) *d = 1;
+        }
       }
     }
   }
@@ -327,8 +331,13 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
 }
 
 __global__ void __launch_bounds__(CNT_THREADS)
-cnt_chunk_sum_kernel(const uint32_t *__restrict__ cnt, int32_t V, uint32_t *__restrict__ bsum) {
+cnt_chunk_sum_kernel(const uint32_t *__restrict__ cnt, int32_t V, const uint8_t *__restrict__ dirty,
+                     uint32_t *__restrict__ bsum) {
   __shared__ uint32_t wsum[CNT_THREADS / 32];
+  if (dirty && !dirty[blockIdx.x]) {  // no ticket was drawn in this chunk: its counters are all zero
+    if (threadIdx.x == 0) bsum[blockIdx.x] = 0u;
+    return;
+  }
   const uint4 *src = reinterpret_cast<const uint4 *>(cnt + (size_t)blockIdx.x * CNT_CHUNK);
   uint32_t part = 0;
 #pragma unroll
@@ -350,10 +359,15 @@ cnt_chunk_sum_kernel(const uint32_t *__restrict__ cnt, int32_t V, uint32_t *__re
 // offs; counters cleared for the next step; the last CTA publishes the number of live pairs.
 __global__ void __launch_bounds__(CNT_THREADS)
 cnt_scan_kernel(uint32_t *__restrict__ cnt, int32_t V, const uint32_t *__restrict__ bsum,
-                uint32_t *__restrict__ offs, int32_t *__restrict__ d_n_out) {
+                uint8_t *__restrict__ dirty, uint32_t *__restrict__ offs, int32_t *__restrict__ d_n_out) {
   __shared__ uint32_t wsum[CNT_THREADS / 32];
   __shared__ uint32_t base_sh;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool is_dirty = !dirty || dirty[blockIdx.x] != 0;
+  const bool is_last = blockIdx.x == gridDim.x - 1;
+  // a chunk nobody drew a ticket in holds no transit of the next step: its offsets are never
+  // read, so the CTA has nothing to do (the last CTA still publishes the live count)
+  if (!is_dirty && !is_last) return;
   uint32_t part = 0;
   for (int i = threadIdx.x; i < (int)blockIdx.x; i += CNT_THREADS) part += bsum[i];
   for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
@@ -394,7 +408,8 @@ cnt_scan_kernel(uint32_t *__restrict__ cnt, int32_t V, const uint32_t *__restric
   *reinterpret_cast<uint4 *>(offs + first + 4) = make_uint4(o[4], o[5], o[6], o[7]);
   *reinterpret_cast<uint4 *>(cnt + first) = make_uint4(0u, 0u, 0u, 0u);
   *reinterpret_cast<uint4 *>(cnt + first + 4) = make_uint4(0u, 0u, 0u, 0u);
-  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == CNT_THREADS - 1) *d_n_out = (int32_t)run;
+  if (is_last && threadIdx.x == CNT_THREADS - 1) *d_n_out = (int32_t)run;
+  if (dirty && threadIdx.x == 0) dirty[blockIdx.x] = 0;
 }
 
 __global__ void __launch_bounds__(256)
@@ -563,6 +578,8 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_CUDA(cudaMalloc(&s->d_cnt, sizeof(uint32_t) * chunks * CNT_CHUNK));   // padded to whole chunks
   ND_CUDA(cudaMalloc(&s->d_offs, sizeof(uint32_t) * chunks * CNT_CHUNK));
   ND_CUDA(cudaMalloc(&s->d_bsum, sizeof(uint32_t) * chunks));
+  ND_CUDA(cudaMalloc(&s->d_dirty, chunks));
+  ND_CUDA(cudaMemset(s->d_dirty, 0, chunks));
   ND_CUDA(cudaMalloc(&s->d_rank, sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
   ND_CUDA(cudaMemset(s->d_cnt, 0, sizeof(uint32_t) * chunks * CNT_CHUNK));
   return ND_OK;
@@ -651,6 +668,10 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     // load-balanced transit-parallel: next() draws tickets, counting inversion
     const int V = s->g->V;
     const int chunks = (V + CNT_CHUNK - 1) / CNT_CHUNK;
+    // Tracking which counter chunks were touched lets the scan skip the others; it pays when the
+    // counter array is large against the live pairs (late PPR steps on 2^24 vertices).  On small
+    // graphs every chunk is touched every step and the flag traffic would only add contention.
+    uint8_t *dirty = chunks >= 2048 ? s->d_dirty : nullptr;
     const int64_t blocks = (S + 255) / 256;
     const int grid = (int)(blocks < (int64_t)s->dev.sms * 64 ? blocks : (int64_t)s->dev.sms * 64);
     NdGraphView gv = nd_view(s->g);
@@ -663,8 +684,8 @@ static int walk_enqueue(nd_sampler *s, int mode) {
       int32_t *tmp_step = s->d_tmp + (int64_t)step * S;
       nd_phase_begin(s, ND_PHASE_NEXT);
 #define ND_LAUNCH_COUNT(APPID)                                                                                         \
-  if (last) walk_next_count_kernel<APPID, false><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats); \
-  else walk_next_count_kernel<APPID, true><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats);
+  if (last) walk_next_count_kernel<APPID, false><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, dirty, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats); \
+  else walk_next_count_kernel<APPID, true><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, dirty, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats);
       switch (app) {
         case ND_APP_UNIFORM_WALK: ND_LAUNCH_COUNT(ND_APP_UNIFORM_WALK) break;
         case ND_APP_DEEPWALK: ND_LAUNCH_COUNT(ND_APP_DEEPWALK) break;
@@ -676,8 +697,8 @@ static int walk_enqueue(nd_sampler *s, int mode) {
       nd_count_launches(1);
       if (last) break;
       nd_phase_begin(s, ND_PHASE_INVERT);
-      cnt_chunk_sum_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, s->d_bsum);
-      cnt_scan_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, s->d_bsum, s->d_offs, s->d_nlive + step + 1);
+      cnt_chunk_sum_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, dirty, s->d_bsum);
+      cnt_scan_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, s->d_bsum, dirty, s->d_offs, s->d_nlive + step + 1);
       walk_scatter_kernel<<<grid, 256, 0, st>>>(d_n, V, ukey, uval, s->d_rank, s->d_offs, skey, sval);
       nd_phase_end(s);
       nd_count_launches(3);
