@@ -88,6 +88,11 @@ int nd_graph_from_csr(int device, int32_t V, int64_t E, const int32_t *row_ptr, 
 int nd_graph_from_edge_records(int device, int64_t n, const void *records, nd_graph **out);
 /* loadGraph(file, "edge-list", "binary") (src/nextdoor.cu:1845-1891) */
 int nd_graph_load_edge_list_binary(int device, const char *path, nd_graph **out);
+/* loadGraph(file, type, format) with all three formats of the reference (src/nextdoor.cu:1845-1891):
+ * ("edge-list","binary"), ("edge-list","text") (src/graph.hpp:162-254: topology only, weights are
+ * stored as 0 as the reference does) and ("adj-list","text") (src/graph.hpp:256-326: vertices
+ * renumbered by line).  Parsing is on the host, the CSR is built on the device. */
+int nd_graph_load(int device, const char *path, const char *graph_type, const char *graph_format, nd_graph **out);
 /* Synthetic R-MAT graph (a,b,c,d)=(.57,.19,.19,.05) generated and built on the device: M
  * undirected edges, both directions stored, weights uniform [1,5).  Stands in for the graph
  * files the reference's tests read (src/tests/testBase.h:6-12). */

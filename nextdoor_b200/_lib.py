@@ -56,6 +56,7 @@ _SIGS = {
     "nd_graph_from_csr": (C.c_int, [C.c_int, C.c_int32, C.c_int64, VP, VP, VP, VP, C.POINTER(VP)]),
     "nd_graph_from_edge_records": (C.c_int, [C.c_int, C.c_int64, VP, C.POINTER(VP)]),
     "nd_graph_load_edge_list_binary": (C.c_int, [C.c_int, C.c_char_p, C.POINTER(VP)]),
+    "nd_graph_load": (C.c_int, [C.c_int, C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(VP)]),
     "nd_graph_rmat": (C.c_int, [C.c_int, C.c_int32, C.c_int64, C.c_uint64, C.POINTER(VP)]),
     "nd_graph_info": (C.c_int, [VP, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int)]),
     "nd_graph_to_host": (C.c_int, [VP, VP, VP, VP, VP]),

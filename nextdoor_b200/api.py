@@ -104,12 +104,10 @@ class Graph:
 
     @classmethod
     def load(cls, path, graph_type="edge-list", graph_format="binary", device=0):
-        """loadGraph(file, type, format) of the reference (src/nextdoor.cu:1845-1891); only the
-        binary edge list (12-byte records) is read by the device loader."""
-        if graph_type != "edge-list" or graph_format != "binary":
-            raise NdError(1, f"graph_format '{graph_format}' not supported for graph_type '{graph_type}'")
+        """loadGraph(file, type, format) of the reference (src/nextdoor.cu:1845-1891): binary edge
+        list (12-byte records), text edge list, text adjacency list."""
         h = C.c_void_p()
-        check(lib.nd_graph_load_edge_list_binary(device, str(path).encode(), C.byref(h)))
+        check(lib.nd_graph_load(device, str(path).encode(), graph_type.encode(), graph_format.encode(), C.byref(h)))
         return cls(h, device)
 
     @classmethod

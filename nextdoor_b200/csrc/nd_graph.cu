@@ -8,7 +8,11 @@
 // sort (weight bits, then dst, then src), row offsets come from the boundaries of the sorted src
 // array, and the sorted dst / weight arrays become col / w in place.
 #include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 
+#include <algorithm>
+#include <string>
 #include <vector>
 
 #include "nd_common.cuh"
@@ -296,7 +300,15 @@ int nd_graph_from_csr(int device, int32_t V, int64_t E, const int32_t *row_ptr, 
   return ND_OK;
 }
 
+static int from_edge_records_min_v(int device, int64_t n, const void *records, int32_t min_v, nd_graph **out);
+
 int nd_graph_from_edge_records(int device, int64_t n, const void *records, nd_graph **out) {
+  return from_edge_records_min_v(device, n, records, 0, out);
+}
+
+// min_v: lower bound of the vertex count (the adjacency-list format numbers vertices by line,
+// including lines without edges)
+static int from_edge_records_min_v(int device, int64_t n, const void *records, int32_t min_v, nd_graph **out) {
   ND_REQUIRE(out && (records || n == 0) && n >= 0, ND_ERR_ARG, "nd_graph_from_edge_records: bad argument");
   ND_REQUIRE(n < ((int64_t)1 << 31), ND_ERR_RANGE, "%lld edges do not fit the int32 edge index of the CSR", (long long)n);
   ND_CUDA(cudaSetDevice(device));
@@ -325,7 +337,8 @@ int nd_graph_from_edge_records(int device, int64_t n, const void *records, nd_gr
     nd_set_error("edge records hold a negative or out-of-range vertex id");
     return ND_ERR_RANGE;
   }
-  const int32_t V = max_id + 1 > 0 ? max_id + 1 : 1;  // vertex count = max id + 1 (src/graph.hpp:131-142)
+  int32_t V = max_id + 1 > 0 ? max_id + 1 : 1;  // vertex count = max id + 1 (src/graph.hpp:131-142)
+  if (V < min_v) V = min_v;
   return build_from_soa(device, n, V, a, b, nullptr, out);
 }
 
@@ -342,6 +355,80 @@ int nd_graph_load_edge_list_binary(int device, const char *path, nd_graph **out)
   fclose(fp);
   if (got != (size_t)(n * 12)) { nd_set_error("short read on '%s'", path); return ND_ERR_IO; }
   return nd_graph_from_edge_records(device, n, buf.data(), out);
+}
+
+// Text edge list (Graph::load_from_edge_list_txt, src/graph.hpp:162-254): whitespace-separated
+// "src dst weight" triples, reading stops at the first zero (or missing) weight, and -- as the
+// reference does (:210) -- every edge is stored with weight 0: this format carries topology only.
+static int load_edge_list_text(int device, const char *path, nd_graph **out) {
+  FILE *fp = fopen(path, "r");
+  if (!fp) { nd_set_error("File '%s' not found", path); return ND_ERR_IO; }
+  std::vector<Rec12> recs;
+  long long a = 0, b = 0;
+  double w = 0;
+  while (fscanf(fp, "%lld %lld %lf", &a, &b, &w) == 3) {
+    if (w == 0.0) break;
+    if (a < 0 || b < 0 || a > 0x7ffffffe || b > 0x7ffffffe) { fclose(fp); nd_set_error("vertex id out of range in '%s'", path); return ND_ERR_RANGE; }
+    recs.push_back(Rec12{(int32_t)a, (int32_t)b, 0.0f});
+  }
+  fclose(fp);
+  return from_edge_records_min_v(device, (int64_t)recs.size(), recs.data(), 0, out);
+}
+
+// Text adjacency list (Graph::load_from_adjacency_list, src/graph.hpp:256-326): one vertex per
+// line, "id nbr weight nbr weight ..."; vertices are renumbered by line order and neighbour ids
+// are translated through that numbering (an id that never heads a line maps to 0, as the
+// reference's unordered_map lookup does).
+static int load_adjacency_list_text(int device, const char *path, nd_graph **out) {
+  FILE *fp = fopen(path, "r");
+  if (!fp) { nd_set_error("File '%s' cannot open", path); return ND_ERR_IO; }
+  std::vector<Rec12> recs;
+  std::vector<long long> ids;
+  std::string line;
+  std::vector<char> buf(1 << 20);
+  while (fgets(buf.data(), (int)buf.size(), fp)) {
+    line.assign(buf.data());
+    while (!line.empty() && line.back() != '\n' && fgets(buf.data(), (int)buf.size(), fp)) line += buf.data();
+    const char *p = line.c_str();
+    char *end = nullptr;
+    const long long id = strtoll(p, &end, 10);
+    if (end == p) continue;  // blank line
+    const int32_t row = (int32_t)ids.size();
+    ids.push_back(id);
+    p = end;
+    for (;;) {
+      const long long nb = strtoll(p, &end, 10);
+      if (end == p) break;
+      p = end;
+      const float wt = strtof(p, &end);
+      if (end == p) break;
+      p = end;
+      recs.push_back(Rec12{row, (int32_t)nb, wt});  // dst still holds the file's id
+    }
+  }
+  fclose(fp);
+  std::vector<std::pair<long long, int32_t>> order(ids.size());
+  for (size_t i = 0; i < ids.size(); i++) order[i] = {ids[i], (int32_t)i};
+  std::sort(order.begin(), order.end());
+  for (Rec12 &r : recs) {
+    auto it = std::lower_bound(order.begin(), order.end(), std::make_pair((long long)r.d, (int32_t)-1));
+    // several lines with one id: the last one wins, like repeated assignment into the reference's map
+    int32_t to = 0;
+    while (it != order.end() && it->first == r.d) { to = it->second; ++it; }
+    r.d = to;
+  }
+  return from_edge_records_min_v(device, (int64_t)recs.size(), recs.data(), (int32_t)ids.size(), out);
+}
+
+int nd_graph_load(int device, const char *path, const char *graph_type, const char *graph_format, nd_graph **out) {
+  ND_REQUIRE(path && graph_type && graph_format && out, ND_ERR_ARG, "nd_graph_load: null argument");
+  const bool edge_list = strcmp(graph_type, "edge-list") == 0, adj_list = strcmp(graph_type, "adj-list") == 0;
+  ND_REQUIRE(edge_list || adj_list, ND_ERR_ARG, "Incorrect graph file type '%s'", graph_type);
+  if (edge_list && strcmp(graph_format, "binary") == 0) return nd_graph_load_edge_list_binary(device, path, out);
+  if (edge_list && strcmp(graph_format, "text") == 0) return load_edge_list_text(device, path, out);
+  if (adj_list && strcmp(graph_format, "text") == 0) return load_adjacency_list_text(device, path, out);
+  nd_set_error("graph_format '%s' not supported for graph_type '%s'", graph_format, graph_type);
+  return ND_ERR_ARG;
 }
 
 int nd_graph_rmat(int device, int32_t V, int64_t M, uint64_t seed, nd_graph **out) {

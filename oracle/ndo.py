@@ -290,6 +290,22 @@ def ref_load_edge_list_binary(path):
     return HostGraph(row_ptr, col, w, mw)
 
 
+def ref_load_text(path, kind):
+    """kind 1: text edge list, 2: text adjacency list -- through the reference's own loaders."""
+    R = ref()
+    R.ref_load_text.restype = C.c_int
+    R.ref_load_text.argtypes = [C.c_char_p, C.c_int] + [C.c_void_p] * 6
+    V = C.c_int32(0)
+    E = C.c_int64(0)
+    R.ref_load_text(path.encode(), kind, C.addressof(V), C.addressof(E), None, None, None, None)
+    row_ptr = np.empty(V.value + 1, np.int32)
+    col = np.empty(E.value, np.int32)
+    w = np.empty(E.value, np.float32)
+    mw = np.empty(V.value, np.float32)
+    R.ref_load_text(path.encode(), kind, C.addressof(V), C.addressof(E), _p(row_ptr), _p(col), _p(w), _p(mw))
+    return HostGraph(row_ptr, col, w, mw)
+
+
 def invert_map(keys, vals, invalid):
     keys = np.ascontiguousarray(keys, np.int32)
     vals = np.ascontiguousarray(vals, np.int32)

@@ -207,4 +207,34 @@ int ref_load_edge_list_binary(const char *path, int32_t *V_out, int64_t *E_out, 
   return 0;
 }
 
+/* The reference's two text loaders, Graph::load_from_edge_list_txt (src/graph.hpp:162-254) and
+ * Graph::load_from_adjacency_list (:256-326), followed by csr_from_graph.  kind: 1 = text edge
+ * list, 2 = text adjacency list.  Call once with row_ptr == NULL for the sizes. */
+int ref_load_text(const char *path, int kind, int32_t *V_out, int64_t *E_out, int32_t *row_ptr,
+                  int32_t *col, float *w, float *max_w) {
+  Graph graph;
+  if (kind == 1) {
+    FILE *fp = fopen(path, "r");
+    if (!fp) return -1;
+    graph.load_from_edge_list_txt(fp, true);
+    fclose(fp);
+  } else {
+    graph.load_from_adjacency_list((char *)path);
+  }
+  int32_t V = (int32_t)graph.get_vertices().size();
+  int64_t E = graph.get_n_edges();
+  *V_out = V; *E_out = E;
+  if (!row_ptr) return 0;
+  CSR *csr = new CSR(V, (EdgePos_t)E);
+  csr_from_graph(csr, graph);
+  for (int32_t v = 0; v < V; v++) {
+    row_ptr[v] = csr->get_vertices()[v].start_edge_id;
+    max_w[v] = csr->get_vertices()[v].max_weight;
+  }
+  row_ptr[V] = (int32_t)E;
+  std::memcpy(col, csr->get_edges(), sizeof(int32_t) * E);
+  std::memcpy(w, csr->get_weights(), sizeof(float) * E);
+  return 0;
+}
+
 }  // extern "C"

@@ -49,3 +49,31 @@ os.remove(path)
 np.savez_compressed(os.path.join(HERE, "loader_rmat300.npz"), src=src[perm], dst=dst[perm], w=w[perm],
                     row_ptr=lg.row_ptr, col=lg.col, wout=lg.w, max_w=lg.max_w)
 print("loader", lg.V, lg.E)
+
+# the reference's text loaders.  The edge-list file lists every vertex's edges in ascending
+# neighbour order and names the largest id first (the reference neither sorts this format nor
+# grows its vertex array for an id equal to the current size, src/graph.hpp:196-210).
+rng = np.random.default_rng(4)
+pairs = sorted({(int(a), int(b)) for a, b in rng.integers(0, 40, (300, 2)) if a != b})
+pairs = [(39, 0)] + [p for p in pairs if p != (39, 0)]
+# The file ends with a zero-weight triple: both loaders stop reading there (src/graph.hpp:199-202),
+# which also keeps the reference from parsing past its unterminated read buffer (:171-178).
+edge_txt = "".join(f"{a} {b} 1.5\n" for a, b in pairs) + "0 0 0\n"
+path = os.path.join(HERE, "_tmp_edges.txt")
+open(path, "w").write(edge_txt)
+lg = ndo.ref_load_text(path, 1)
+os.remove(path)
+ids = [100 + 7 * i for i in range(25)]          # arbitrary ids, renumbered by line order
+lines = []
+for i, vid in enumerate(ids):
+    nb = sorted(set(int(x) for x in rng.integers(0, 25, int(rng.integers(0, 6)))) - {i})
+    lines.append(str(vid) + "".join(f" {ids[j]} {1 + 0.25 * ((i + j) % 9)}" for j in nb))
+adj_txt = "\n".join(lines) + "\n"
+path = os.path.join(HERE, "_tmp_adj.txt")
+open(path, "w").write(adj_txt)
+ag = ndo.ref_load_text(path, 2)
+os.remove(path)
+np.savez_compressed(os.path.join(HERE, "loader_text.npz"),
+                    edge_txt=np.frombuffer(edge_txt.encode(), np.uint8), e_row_ptr=lg.row_ptr, e_col=lg.col, e_w=lg.w, e_max_w=lg.max_w,
+                    adj_txt=np.frombuffer(adj_txt.encode(), np.uint8), a_row_ptr=ag.row_ptr, a_col=ag.col, a_w=ag.w, a_max_w=ag.max_w)
+print("text loaders", lg.V, lg.E, ag.V, ag.E)

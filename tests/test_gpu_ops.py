@@ -140,3 +140,23 @@ def test_partition_matches_oracle(nd, ndo, small_graph, budget):
     exp = ndo.partition(small_graph, budget, max_parts=100000)
     for a, b in zip(got, exp):
         assert np.array_equal(a, b)
+
+
+def test_text_loaders_match_reference_loaders(nd, tmp_path):
+    """Golden CSRs produced by the reference's own text loaders (edge list: topology only, weights
+    stored as 0; adjacency list: vertices renumbered by line, a vertex without edges still counts)."""
+    z = np.load(os.path.join(GOLD, "loader_text.npz"))
+    for kind, gtype, key in (("edge", "edge-list", "e_"), ("adj", "adj-list", "a_")):
+        path = str(tmp_path / f"{kind}.txt")
+        with open(path, "wb") as f:
+            f.write(z[f"{kind}_txt"].tobytes())
+        g = nd.Graph.load(path, gtype, "text")
+        row_ptr, col, w, mw = g.to_host()
+        assert np.array_equal(row_ptr, z[key + "row_ptr"]), kind
+        assert np.array_equal(col, z[key + "col"]) and np.array_equal(w, z[key + "w"]) and np.array_equal(mw, z[key + "max_w"])
+    with pytest.raises(nd.NdError) as e:
+        nd.Graph.load(str(tmp_path / "edge.txt"), "adj-list", "binary")
+    assert "not supported" in str(e.value)
+    with pytest.raises(nd.NdError) as e:
+        nd.Graph.load(str(tmp_path / "edge.txt"), "matrix-market", "text")
+    assert "Incorrect graph file type" in str(e.value)
