@@ -262,7 +262,7 @@ template <class SampleType, typename App, bool FROM_MAP>
 __global__ void step_kernel(CSRPartition part, int step, uint64_t seed, int64_t first_sample, int64_t n_pairs,
                             const VertexID_t *in_key, const VertexID_t *in_val, const VertexID_t *initial,
                             SampleType *samples, VertexID_t *out, int fs, VertexID_t *mkey, VertexID_t *mval,
-                            bool write_map) {
+                            bool write_map, const VertexID_t *explicit_prev) {
   const int f = App().stepSize(step);
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (tid >= n_pairs * f) return;
@@ -275,7 +275,11 @@ __global__ void step_kernel(CSRPartition part, int step, uint64_t seed, int64_t 
   else {
     q = (VertexID_t)i;
     const int64_t s = q / n_prev;
-    transit = step == 0 ? initial[s] : out[s * fs + prefix_of<App>(step - 1) + (q - s * n_prev)];
+    // apps with explicit transits walk from what stepTransits returned at the previous step
+    // (kept per pair id), the others from the vertex sampled at the previous hop
+    if (step == 0) transit = initial[s];
+    else if (explicit_prev) transit = explicit_prev[q];
+    else transit = out[s * fs + prefix_of<App>(step - 1) + (q - s * n_prev)];
   }
   const int64_t s = q / n_prev;
   const int parent = (int)(q - s * n_prev);
@@ -351,12 +355,14 @@ inline CSR *loadGraph(Graph &graph, char *graph_file, char *graph_type, char *gr
     printf("Incorrect graph file type '%s'\n", graph_type);
     return nullptr;
   }
-  if (strcmp(graph_type, "edge-list") != 0 || strcmp(graph_format, "binary") != 0) {
+  const bool known = (strcmp(graph_type, "edge-list") == 0 && (strcmp(graph_format, "binary") == 0 || strcmp(graph_format, "text") == 0)) ||
+                     (strcmp(graph_type, "adj-list") == 0 && strcmp(graph_format, "text") == 0);
+  if (!known) {
     printf("graph_format '%s' not supported for graph_type '%s'\n", graph_format, graph_type);
     return nullptr;
   }
   nd_graph *g = nullptr;
-  if (nd_graph_load_edge_list_binary(0, graph_file, &g) != ND_OK) {
+  if (nd_graph_load(0, graph_file, graph_type, graph_format, &g) != ND_OK) {
     std::cout << nd_last_error() << std::endl;
     return nullptr;
   }
@@ -495,16 +501,20 @@ bool run(CSR *csr, NextDoorData<SampleType, App> &data, bool transit_parallel) {
       const int f = App().stepSize(step);
       const int64_t full_pairs = n * pairs_per_sample<App>(step);
       const int64_t pairs = transit_parallel ? n_pairs : full_pairs;
-      const bool write_map = transit_parallel && !last;
+      const bool explicit_tr = App().hasExplicitTransits();
+      const bool write_map = (transit_parallel || explicit_tr) && !last;
+      // sample-parallel runs of explicit-transit apps ping-pong the unsorted per-pair transits
+      if (!transit_parallel && explicit_tr) cur = step & 1;
       VertexID_t *mk = data.dMapKeys[cur][d], *mv = data.dMapVals[cur][d];
+      const VertexID_t *explicit_prev = (!transit_parallel && explicit_tr && step > 0) ? data.dMapKeys[cur ^ 1][d] : nullptr;
       if (write_map) fill_kernel<VertexID_t><<<(unsigned)((full_pairs * f + 255) / 256), 256>>>(mk, full_pairs * f, INV);
       const int64_t threads = pairs * f;
       if (threads > 0) {
-        if (transit_parallel) step_kernel<SampleType, App, true><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, in_key, in_val, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map);
-        else step_kernel<SampleType, App, false><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, nullptr, nullptr, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, false);
+        if (transit_parallel) step_kernel<SampleType, App, true><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, in_key, in_val, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, nullptr);
+        else step_kernel<SampleType, App, false><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, nullptr, nullptr, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, explicit_prev);
       }
       NDC_CHECK(cudaGetLastError());
-      if (write_map) {  // the map inversion of the step loop (src/nextdoor.cu:2924-2939)
+      if (write_map && transit_parallel) {  // the map inversion of the step loop (src/nextdoor.cu:2924-2939)
         // buffer 0 = unsorted pairs just written, buffer 1 = sorted map (its old content, this step's
         // input, is dead once the step kernel has run)
         if (nd_invert_map(data.devices[d], full_pairs * f, mk, mv, INV, data.dMapKeys[1][d], data.dMapVals[1][d], &n_pairs) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }

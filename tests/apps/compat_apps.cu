@@ -129,6 +129,38 @@ struct OwnLayerApp {
   }
 };
 
+// walk that teleports: after every step the next transit is one of four roots kept in the sample
+// (explicit transits, the mechanism of the reference's multiRW app), and the vertex just sampled
+// replaces the root the walk came from
+struct TeleportSample { int roots[4]; int last; };
+struct OwnTeleportWalk : WalkBase {
+  __host__ __device__ int steps() { return 12; }
+  __host__ __device__ EdgePos_t numSamples(CSR *graph) { return graph->get_n_vertices(); }
+  __host__ __device__ bool hasExplicitTransits() { return true; }
+  template <class SampleType>
+  __host__ SampleType initializeSample(CSR *graph, const VertexID_t id) {
+    SampleType s;
+    for (int i = 0; i < 4; i++) s.roots[i] = (id * 7 + i * 13) % graph->get_n_vertices();
+    s.last = 0;
+    return s;
+  }
+  template <class SampleType>
+  __host__ std::vector<VertexID_t> initialSample(int, CSR *, SampleType &sample) { return std::vector<VertexID_t>(1, sample.roots[0]); }
+  template <class SampleType>
+  __device__ VertexID_t stepTransits(int, const VertexID_t, SampleType &sample, int, curandState *state) {
+    const int pick = RandNumGen::rand_int(state, 4);
+    sample.last = pick;
+    return sample.roots[pick];
+  }
+  template <typename SampleType, typename EdgeArray, typename WeightArray>
+  __device__ inline VertexID next(int step, CSRPartition *, const VertexID *, const VertexID, SampleType *sample, const float,
+                                  EdgeArray &edges, WeightArray &, const EdgePos_t numEdges, const VertexID_t, curandState *state) {
+    const VertexID v = numEdges == 1 ? edges[0] : edges[RandNumGen::rand_int(state, numEdges)];
+    if (step > 0) sample->roots[sample->last] = v;
+    return v;
+  }
+};
+
 // ---------------------------------------------------------------- the reference's own application files
 #ifdef NDC_WITH_REFERENCE
 #include "apps/randomwalks/randomWalks.cu"
@@ -138,6 +170,7 @@ struct OwnLayerApp {
 #define main ndc_reference_example_main
 #include "uniformRandWalk.cu"
 #undef main
+#include "apps/multiRW/multiRW.cu"
 #endif
 
 // ---------------------------------------------------------------- runners
@@ -148,6 +181,7 @@ static int run_app(const char *file, const char *kernel, int lb, int32_t *out, i
   Graph graph;
   CSR *csr = loadGraph(graph, (char *)file, (char *)"edge-list", (char *)"binary");
   if (!csr) return 1;
+  srand(1);  // apps that seed their samples with rand() start from the same state on every run
   NextDoorData<SampleType, App> local;
   NextDoorData<SampleType, App> &data = keep ? *keep : local;
   if (!allocNextDoorDataOnGPU<SampleType, App>(csr, data)) return 2;
@@ -182,7 +216,9 @@ extern "C" int ndc_run(int which, const char *file, const char *kernel, int lb, 
         }
       return rc;
     }
+    case 5: return run_app<TeleportSample, OwnTeleportWalk>(file, kernel, lb, out, cap, n_out, fs_out);
 #ifdef NDC_WITH_REFERENCE
+    case 15: return run_app<MultiRWSample, MultiRWApp>(file, kernel, lb, out, cap, n_out, fs_out);
     case 10: return run_app<UniformRandomWalkSample, UniformRandomWalkApp>(file, kernel, lb, out, cap, n_out, fs_out);
     case 11: return run_app<DummySample, DeepWalkApp>(file, kernel, lb, out, cap, n_out, fs_out);
     case 12: return run_app<DummySample, PPRApp>(file, kernel, lb, out, cap, n_out, fs_out);

