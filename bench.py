@@ -263,6 +263,20 @@ def main():
     launches = nd.launch_count() - l0
     edges_step = smp.stats()["sampled_edges"]
 
+    # ---- the same job in the reference's other kernel type (-k SampleParallel), for comparison
+    ms_sp = None
+    if mode != 2:
+        for _ in range(2):
+            smp.sample(2, sync=False)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(a.steps):
+            smp.sample(2, sync=False)
+        s1.record(stream)
+        barrier()
+        ms_sp = s0.elapsed_time(s1)
+
     # ---- end to end through the public API with host buffers: seeds H2D from pinned memory,
     # sample, result D2H into pinned memory.  The job runs as E2E_CHUNKS seed-range chunks
     # (nextdoor_b200.api.PipelinedSampler): a finished chunk is copied on a second stream while the next one is sampled.
@@ -312,12 +326,12 @@ def main():
     smp.set_profiling(False)
     st = smp.stats()
 
-    tms = torch.tensor([ms, ms_e2e, ms_gather or 0.0], dtype=torch.float64, device="cuda")
+    tms = torch.tensor([ms, ms_e2e, ms_gather or 0.0, ms_sp or 0.0], dtype=torch.float64, device="cuda")
     tot = torch.tensor([float(edges_step)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-    ms, ms_e2e, ms_gather = float(tms[0]), float(tms[1]), float(tms[2])
+    ms, ms_e2e, ms_gather, ms_sp = float(tms[0]), float(tms[1]), float(tms[2]), float(tms[3])
     total_edges = float(tot[0])
 
     if rank == 0:
@@ -345,6 +359,8 @@ def main():
                     "h2d_bytes_per_step": int(init_np.nbytes), "d2h_bytes_per_step": int(S * fs * 4),
                     "chunks": E2E_CHUNKS, "valid_vertices_in_host_result": e2e_check},
             "gpu_launches": int(launches),
+            "sample_parallel": None if mode == 2 else {"value": total_edges * a.steps / (ms_sp * 1e-3), "unit": "sampled edges/s",
+                                                       "note": "same sampler, same samples, nd_mode SampleParallel"},
             "with_gather": None if world == 1 else {
                 "value": total_edges * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",
                 "collective": "ncclAllGather of the final samples", "bytes_per_rank_per_step": int(S * fs * 4)},

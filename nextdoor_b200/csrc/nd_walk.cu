@@ -74,39 +74,41 @@ struct Events {
 // Gathers from the big graph arrays (neighbour ids, weights, filter words) are used once per
 // launch: they are loaded with the streaming policy (evict-first) so that they do not push the
 // small per-sample and per-vertex arrays (maps, counters, staged output row, row offsets) out of L2.
-template <typename T>
-__device__ __forceinline__ T ld_stream(const T *p) { return __ldcs(p); }
+// (Only the transit-parallel kernels do this; a sample-parallel walk revisits hub lists from the
+// same thread step after step and is faster with the default policy: 60 vs 42 G edges/s measured.)
+template <bool STREAM, typename T>
+__device__ __forceinline__ T ld_graph(const T *p) { return STREAM ? __ldcs(p) : __ldg(p); }
 
-template <int APP>
+template <int APP, bool STREAM = true>
 __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkParams &wp, int step,
                                             int32_t transit, int32_t rs, int32_t n, int32_t &state_t,
                                             Rng &rng, int *status, Events &ev) {
   const int32_t *__restrict__ edges = g.col + rs;
   if (APP == ND_APP_UNIFORM_WALK) {  // example/uniformRandWalk.cu:35-36
-    return ld_stream(edges + rng.rand_int(n));
+    return ld_graph<STREAM>(edges + rng.rand_int(n));
   }
   if (APP == ND_APP_DEEPWALK || APP == ND_APP_PPR) {  // randomWalks.cu:74-90, 102-124
     if (APP == ND_APP_PPR) {
       const float pr = rng.uniform();
       if (pr < wp.stop_prob) return -1;
     }
-    if (n == 1) return ld_stream(edges);
+    if (n == 1) return ld_graph<STREAM>(edges);
     const float *__restrict__ weights = g.w + rs;
     const float max_w = __ldg(g.max_w + transit);
     int32_t x = rng.rand_int(n);
     float y = __fmul_rn(rng.uniform(), max_w);
     int it = 0;
     ev.weight_tries++;
-    while (y > ld_stream(weights + x)) {
+    while (y > ld_graph<STREAM>(weights + x)) {
       if (++it > RETRY_CAP) { atomicOr(status, ND_DEV_RETRY_LIMIT); break; }
       x = rng.rand_int(n);
       y = __fmul_rn(rng.uniform(), max_w);
       ev.weight_tries++;
     }
-    return ld_stream(edges + x);
+    return ld_graph<STREAM>(edges + x);
   }
   if (APP == ND_APP_NODE2VEC) {  // randomWalks.cu:141-172
-    if (n == 1 || step == 0) { state_t = transit; return ld_stream(edges); }
+    if (n == 1 || step == 0) { state_t = transit; return ld_graph<STREAM>(edges); }
     const float inv_q = __fdiv_rn(1.0f, wp.q);
     float bound = wp.p > inv_q ? wp.p : inv_q;
     if (bound < 1.0f) bound = 1.0f;
@@ -116,7 +118,7 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
     const int32_t *__restrict__ tedges = g.col + ts;
     for (int it = 0;; it++) {
       const int32_t x = rng.rand_int(n);
-      const int32_t v = ld_stream(edges + x);
+      const int32_t v = ld_graph<STREAM>(edges + x);
       const float y = __fmul_rn(rng.uniform(), bound);
       float h;
       ev.n2v_tries++;
@@ -133,14 +135,14 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
           unsigned long long mask;
           filter_slot(v, (uint32_t)tn >> 2, word, mask);
           ev.n2v_probes += 2;  // one 8-byte load
-          if ((ld_stream(wp.filter + ((uint32_t)ts >> 2) + word) & mask) != mask) r = 0;  // certainly not a neighbour
+          if ((ld_graph<STREAM>(wp.filter + ((uint32_t)ts >> 2) + word) & mask) != mask) r = 0;  // certainly not a neighbour
         }
         // 5-ary search: the four pivots of a level are loaded together, so a level costs one
         // memory latency and a 138K-entry list is searched in 8 levels instead of 17
         while (r - l > 4 && !found) {
           const int32_t q5 = (r - l) / 5;
           const int32_t p1 = l + q5, p2 = p1 + q5, p3 = p2 + q5, p4 = p3 + q5;
-          const int32_t e1 = ld_stream(tedges + p1), e2 = ld_stream(tedges + p2), e3 = ld_stream(tedges + p3), e4 = ld_stream(tedges + p4);
+          const int32_t e1 = ld_graph<STREAM>(tedges + p1), e2 = ld_graph<STREAM>(tedges + p2), e3 = ld_graph<STREAM>(tedges + p3), e4 = ld_graph<STREAM>(tedges + p4);
           ev.n2v_probes += 4;
           if (v == e1 || v == e2 || v == e3 || v == e4) found = true;
           else if (v < e1) r = p1;
@@ -152,7 +154,7 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
         if (!found && r > l) {  // at most four left: load them together
           int32_t e[4];
 #pragma unroll
-          for (int k = 0; k < 4; k++) e[k] = l + k < r ? ld_stream(tedges + l + k) : -1;
+          for (int k = 0; k < 4; k++) e[k] = l + k < r ? ld_graph<STREAM>(tedges + l + k) : -1;
           ev.n2v_probes += r - l;
           found = v == e[0] || v == e[1] || v == e[2] || v == e[3];
         }
@@ -446,7 +448,7 @@ walk_sp_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_t S,
       int32_t nbr = -1;
       if (deg > 0) {
         Rng rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
-        nbr = app_next<APP>(g, wp, step, cur, rs, deg, st, rng, status, ev);
+        nbr = app_next<APP, false>(g, wp, step, cur, rs, deg, st, rng, status, ev);
       }
       if (nbr < 0) break;
       tmp[(int64_t)step * S + s] = nbr;

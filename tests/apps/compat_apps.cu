@@ -93,7 +93,7 @@ struct OwnKHop : WalkBase {
 
 // collective layer sampling, 2 layers of 8 from batches of 8: a vertex uniform over the graph plus
 // the batch-to-layer adjacency kept in the sample
-struct LayerSample { int row[2][64]; int col[2][64]; };
+struct OwnLayerSample { int row[2][64]; int col[2][64]; };
 struct OwnLayerApp {
   __host__ __device__ int steps() { return 2; }
   __host__ __device__ int stepSize(int) { return 8; }
@@ -171,6 +171,8 @@ struct OwnTeleportWalk : WalkBase {
 #include "uniformRandWalk.cu"
 #undef main
 #include "apps/multiRW/multiRW.cu"
+#undef VERTICES_PER_SAMPLE
+#include "apps/layer/layerSampling.cu"
 #endif
 
 // ---------------------------------------------------------------- runners
@@ -207,8 +209,8 @@ extern "C" int ndc_run(int which, const char *file, const char *kernel, int lb, 
     case 2: return run_app<PrevSample, OwnSecondOrderWalk>(file, kernel, lb, out, cap, n_out, fs_out);
     case 3: return run_app<PlainSample, OwnKHop>(file, kernel, lb, out, cap, n_out, fs_out);
     case 4: {
-      NextDoorData<LayerSample, OwnLayerApp> data;
-      int rc = run_app<LayerSample, OwnLayerApp>(file, kernel, lb, out, cap, n_out, fs_out, &data);
+      NextDoorData<OwnLayerSample, OwnLayerApp> data;
+      int rc = run_app<OwnLayerSample, OwnLayerApp>(file, kernel, lb, out, cap, n_out, fs_out, &data);
       if (rc == 0 && adj_row)
         for (size_t s = 0; s < data.samples.size(); s++) {
           memcpy(adj_row + s * 128, data.samples[s].row, sizeof(int) * 128);
@@ -218,6 +220,7 @@ extern "C" int ndc_run(int which, const char *file, const char *kernel, int lb, 
     }
     case 5: return run_app<TeleportSample, OwnTeleportWalk>(file, kernel, lb, out, cap, n_out, fs_out);
 #ifdef NDC_WITH_REFERENCE
+    case 16: return run_app<LayerSample, LayerSamplingApp>(file, kernel, lb, out, cap, n_out, fs_out);
     case 15: return run_app<MultiRWSample, MultiRWApp>(file, kernel, lb, out, cap, n_out, fs_out);
     case 10: return run_app<UniformRandomWalkSample, UniformRandomWalkApp>(file, kernel, lb, out, cap, n_out, fs_out);
     case 11: return run_app<DummySample, DeepWalkApp>(file, kernel, lb, out, cap, n_out, fs_out);

@@ -126,10 +126,11 @@ def test_reference_app_files_drop_in(ndo, world, kernel, lb):
     path, hg = world
     L = _lib(WITH_REF)
     V = hg.V
-    cases = [(10, ndo.APP_UNIFORM_WALK, V), (11, ndo.APP_DEEPWALK, 100 * V), (12, ndo.APP_PPR, 100 * V),
-             (13, ndo.APP_NODE2VEC, 100 * V), (14, ndo.APP_KHOP, V)]
-    for which, app, S in cases:
-        pr = ndo.make_params(app)          # the reference's compile-time constants
+    cases = [(10, ndo.APP_UNIFORM_WALK, V, None), (11, ndo.APP_DEEPWALK, 100 * V, None), (12, ndo.APP_PPR, 100 * V, None),
+             (13, ndo.APP_NODE2VEC, 100 * V, None), (14, ndo.APP_KHOP, V, None),
+             (16, ndo.APP_KHOP, V, [10, 25])]   # LayerSamplingApp = k-hop with fan-outs 10 then 25 (layerSampling.cu:3-8)
+    for which, app, S, fan in cases:
+        pr = ndo.make_params(app, fanout=fan)          # the reference's compile-time constants
         fs = ndo.final_sample_size(pr)
         got, _, _ = _run(L, which, path, kernel, lb, S * fs)
         exp = ndo.sample(hg, pr, S)["out"]
