@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libnextdoor_b200.so")
+LIB_PATH = os.environ.get("ND_B200_LIB") or os.path.join(HERE, "libnextdoor_b200.so")  # override: another build of the same ABI
 
 ND_OK = 0
 MAX_FANOUT = 8

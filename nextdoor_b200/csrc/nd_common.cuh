@@ -71,6 +71,9 @@ struct nd_graph {
   int32_t *col = nullptr;
   float *w = nullptr;
   float *max_w = nullptr;
+  // Derived layouts, built on the first sampler that needs them and shared by all samplers of the graph:
+  mutable int2 *colw = nullptr;        // [E] (neighbour id, weight bits) records: one 8-byte gather per weighted try
+  mutable int32_t *adjset = nullptr;   // node2vec membership: per-vertex hash sets of the neighbour ids, 8-slot buckets
 };
 
 struct NdGraphView {
@@ -167,8 +170,8 @@ struct nd_sampler {
   // counting inversion of the walk maps: per-vertex counters, their exclusive scan, chunk sums, ranks
   uint32_t *d_cnt = nullptr, *d_offs = nullptr, *d_bsum = nullptr;
   int32_t *d_rank = nullptr;
-  uint8_t *d_dirty = nullptr;   // per chunk of counters: a ticket was drawn there this step
-  unsigned long long *d_filter = nullptr;  // node2vec adjacency pre-filter
+  int32_t *d_lb_key[2] = {nullptr, nullptr};   // second sorted map of the load-balanced walk loop
+  int32_t *d_prev[2] = {nullptr, nullptr};     // node2vec: previous vertex carried with the sorted map
   // the step loop of a walk job captured once per mode and replayed (needs a non-default stream)
   cudaGraphExec_t graph_exec[3] = {nullptr, nullptr, nullptr};
   int graph_launches[3] = {0, 0, 0};

@@ -26,27 +26,27 @@ struct WalkParams {
   float p, q, stop_prob;
   int n2v_compat;
   int steps;
-  const unsigned long long *filter;  // node2vec: adjacency pre-filter of the high-degree vertices (may be null)
+  const int32_t *adjset;  // node2vec: per-vertex hash sets of the neighbour ids
+  const int2 *colw;       // DeepWalk / PPR: (neighbour id, weight bits) records
 };
 
-// node2vec asks "is v a neighbour of the previous vertex t?" once per try, and t is usually a hub
-// (a 17-probe bisection).  Most answers are "no", so every vertex with at least FILTER_MIN_DEG
-// neighbours gets a blocked Bloom filter over its list: 16 bits per neighbour, stored in the 64-bit
-// words [row_ptr[t]/4, row_ptr[t]/4 + deg/4) of one array (regions of consecutive vertices cannot
-// overlap), two bits per neighbour inside one word, so a test is a single 8-byte load.  A filter
-// has no false negatives: when it says "no" the bisection is skipped, otherwise it runs as usual,
-// and the accepted vertex is the same either way.
-constexpr int FILTER_MIN_DEG = 32;
+// node2vec asks "is v a neighbour of the previous vertex t?" for its candidates, and t is usually a
+// hub (a 17-probe bisection of dependent loads).  Every vertex with at least SET_MIN_DEG
+// neighbours gets an open-addressing hash set of its neighbour ids instead: buckets of 8 ids (one
+// 32-byte sector), the buckets [row_ptr[t]/4, (row_ptr[t]+deg)/4) of one array (regions of
+// consecutive vertices cannot overlap; at least deg slots each, load factor about 1/2).  An id
+// lives in the first free slot at or after its home bucket, so a lookup reads the home bucket and
+// is done unless that bucket is full and does not hold the id (about 5 % of the lookups).  The
+// answer is exact, i.e. the answer of utils::binarySearch (src/utils.hpp:30-48).
+constexpr int SET_MIN_DEG = 8;
+constexpr int32_t SET_EMPTY = -1;
 
-__device__ __forceinline__ uint32_t filter_mix(uint32_t x) {
+__device__ __forceinline__ uint32_t set_mix(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
   return x;
 }
-__device__ __forceinline__ void filter_slot(int32_t v, uint32_t n_words, uint32_t &word, unsigned long long &mask) {
-  const uint32_t h = filter_mix((uint32_t)v);
-  word = (uint32_t)(((unsigned long long)h * n_words) >> 32);
-  const uint32_t g = filter_mix(h ^ 0x9e3779b9u);
-  mask = (1ull << (g & 63u)) | (1ull << ((g >> 6) & 63u));
+__device__ __forceinline__ uint32_t set_bucket(int32_t v, uint32_t n_buckets) {
+  return (uint32_t)(((unsigned long long)set_mix((uint32_t)v) * n_buckets) >> 32);
 }
 
 constexpr int RETRY_CAP = 1 << 16;
@@ -70,15 +70,53 @@ struct Events {
   }
 };
 
-// One next() of the app on a transit with n > 0 neighbours; -1 = no vertex.
-// Gathers from the big graph arrays (neighbour ids, weights, filter words) are used once per
-// launch: they are loaded with the streaming policy (evict-first) so that they do not push the
-// small per-sample and per-vertex arrays (maps, counters, staged output row, row offsets) out of L2.
-// (Only the transit-parallel kernels do this; a sample-parallel walk revisits hub lists from the
-// same thread step after step and is faster with the default policy: 60 vs 42 G edges/s measured.)
+// Gathers from the big graph arrays (neighbour ids, weight records, set buckets) are used once per
+// launch in the transit-parallel kernels: there they are loaded with the streaming policy
+// (evict-first) so that they do not push the small per-sample and per-vertex arrays (maps,
+// counters, staged output row, row offsets) out of L2.  A sample-parallel walk revisits hub lists
+// from the same thread step after step and is faster with the default policy.
 template <bool STREAM, typename T>
 __device__ __forceinline__ T ld_graph(const T *p) { return STREAM ? __ldcs(p) : __ldg(p); }
 
+// Exact membership of v in the neighbour list [ts, ts+tn) of t.  `probes` counts the 4-byte words read.
+template <bool STREAM>
+__device__ __forceinline__ bool n2v_member_slow(const NdGraphView &g, const int32_t *adjset, int32_t ts, int32_t tn,
+                                                int32_t v, uint32_t bucket, uint32_t n_buckets, uint32_t &probes) {
+  if (tn < SET_MIN_DEG) {  // short list: read it
+    bool found = false;
+#pragma unroll
+    for (int k = 0; k < SET_MIN_DEG - 1; k++) {
+      const int32_t e = k < tn ? ld_graph<STREAM>(g.col + ts + k) : -1;
+      found |= e == v;
+    }
+    probes += tn;
+    return found;
+  }
+  const int4 *region = reinterpret_cast<const int4 *>(adjset) + 2 * (size_t)((uint32_t)ts >> 2);
+  for (uint32_t it = 0; it < n_buckets; it++) {  // the home bucket was full: walk on
+    bucket = bucket + 1 < n_buckets ? bucket + 1 : 0;
+    const int4 a = ld_graph<STREAM>(region + 2 * (size_t)bucket), b = ld_graph<STREAM>(region + 2 * (size_t)bucket + 1);
+    probes += 8;
+    if (a.x == v || a.y == v || a.z == v || a.w == v || b.x == v || b.y == v || b.z == v || b.w == v) return true;
+    if (b.w == SET_EMPTY) return false;  // slots fill front to back inside a bucket
+  }
+  return false;
+}
+
+constexpr int TRY_BATCH = 4;    // node2vec tries whose gathers are issued together
+// Weighted tries per round.  Every try of a round is gathered, so a larger batch buys latency with
+// gathers that a 60 % acceptance rate wastes: two per round, except PPR in the sample-parallel
+// kernel (walks die young there, the kernel is short of loads in flight; four measured faster).
+template <int APP, bool STREAM>
+__host__ __device__ constexpr int weight_batch() { return APP == ND_APP_PPR && !STREAM ? 4 : 2; }
+
+// One next() of the app on a transit with n > 0 neighbours; -1 = no vertex.
+//
+// The rejection loops of DeepWalk / PPR / node2vec draw their tries from the keyed stream in
+// order, so try k of an invocation is a pure function of (sample, step, k).  The loops below
+// evaluate TRY_BATCH tries per round: the gathers of the whole round are issued together (one
+// memory latency instead of one per try) and the first try that accepts, in draw order, wins --
+// the same vertex the one-try-at-a-time loop returns.  Only the tries up to the winner are counted.
 template <int APP, bool STREAM = true>
 __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkParams &wp, int step,
                                             int32_t transit, int32_t rs, int32_t n, int32_t &state_t,
@@ -93,77 +131,97 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
       if (pr < wp.stop_prob) return -1;
     }
     if (n == 1) return ld_graph<STREAM>(edges);
-    const float *__restrict__ weights = g.w + rs;
+    const int2 *__restrict__ recs = wp.colw + rs;
     const float max_w = __ldg(g.max_w + transit);
-    int32_t x = rng.rand_int(n);
-    float y = __fmul_rn(rng.uniform(), max_w);
-    int it = 0;
-    ev.weight_tries++;
-    while (y > ld_graph<STREAM>(weights + x)) {
-      if (++it > RETRY_CAP) { atomicOr(status, ND_DEV_RETRY_LIMIT); break; }
-      x = rng.rand_int(n);
-      y = __fmul_rn(rng.uniform(), max_w);
-      ev.weight_tries++;
+    constexpr int WEIGHT_BATCH = weight_batch<APP, STREAM>();
+    for (int it = 0;; it += WEIGHT_BATCH) {
+      float y[WEIGHT_BATCH];
+      int2 rec[WEIGHT_BATCH];
+#pragma unroll
+      for (int k = 0; k < WEIGHT_BATCH; k++) {
+        const int32_t x = rng.rand_int(n);
+        y[k] = __fmul_rn(rng.uniform(), max_w);
+        rec[k] = ld_graph<STREAM>(recs + x);
+      }
+#pragma unroll
+      for (int k = 0; k < WEIGHT_BATCH; k++) {
+        ev.weight_tries++;
+        if (!(y[k] > __int_as_float(rec[k].y))) return rec[k].x;
+      }
+      if (it > RETRY_CAP) { atomicOr(status, ND_DEV_RETRY_LIMIT); return rec[WEIGHT_BATCH - 1].x; }
     }
-    return ld_graph<STREAM>(edges + x);
   }
   if (APP == ND_APP_NODE2VEC) {  // randomWalks.cu:141-172
     if (n == 1 || step == 0) { state_t = transit; return ld_graph<STREAM>(edges); }
     const float inv_q = __fdiv_rn(1.0f, wp.q);
     float bound = wp.p > inv_q ? wp.p : inv_q;
     if (bound < 1.0f) bound = 1.0f;
+    // a candidate that is not the previous vertex is accepted when y < 1/q (neighbour of t) or
+    // y < 1 (not a neighbour): below `lo` the membership does not matter, at or above `hi` neither;
+    // below `sure` nothing about the candidate matters
+    const float lo = inv_q < 1.0f ? inv_q : 1.0f, hi = inv_q < 1.0f ? 1.0f : inv_q;
+    const float sure = lo < wp.p ? lo : wp.p;
     const int32_t t = state_t;
     const int32_t ts = __ldg(g.row_ptr + t);
     const int32_t tn = __ldg(g.row_ptr + t + 1) - ts;
-    const int32_t *__restrict__ tedges = g.col + ts;
-    for (int it = 0;; it++) {
-      const int32_t x = rng.rand_int(n);
-      const int32_t v = ld_graph<STREAM>(edges + x);
-      const float y = __fmul_rn(rng.uniform(), bound);
-      float h;
-      ev.n2v_tries++;
-      const bool is_ret = wp.n2v_compat ? (x == t) : (v == t);  // randomWalks.cu:159 compares the index
-      if (is_ret) {
-        h = wp.p;
-      } else {
-        // membership of v in the sorted list of t: the answer of utils::binarySearch
-        // (src/utils.hpp:30-48), found with fewer dependent loads
-        int32_t l = 0, r = tn;  // candidates in [l, r)
-        bool found = false;
-        if (wp.filter && tn >= FILTER_MIN_DEG) {
-          uint32_t word;
-          unsigned long long mask;
-          filter_slot(v, (uint32_t)tn >> 2, word, mask);
-          ev.n2v_probes += 2;  // one 8-byte load
-          if ((ld_graph<STREAM>(wp.filter + ((uint32_t)ts >> 2) + word) & mask) != mask) r = 0;  // certainly not a neighbour
-        }
-        // 5-ary search: the four pivots of a level are loaded together, so a level costs one
-        // memory latency and a 138K-entry list is searched in 8 levels instead of 17
-        while (r - l > 4 && !found) {
-          const int32_t q5 = (r - l) / 5;
-          const int32_t p1 = l + q5, p2 = p1 + q5, p3 = p2 + q5, p4 = p3 + q5;
-          const int32_t e1 = ld_graph<STREAM>(tedges + p1), e2 = ld_graph<STREAM>(tedges + p2), e3 = ld_graph<STREAM>(tedges + p3), e4 = ld_graph<STREAM>(tedges + p4);
-          ev.n2v_probes += 4;
-          if (v == e1 || v == e2 || v == e3 || v == e4) found = true;
-          else if (v < e1) r = p1;
-          else if (v < e2) { l = p1 + 1; r = p2; }
-          else if (v < e3) { l = p2 + 1; r = p3; }
-          else if (v < e4) { l = p3 + 1; r = p4; }
-          else l = p4 + 1;
-        }
-        if (!found && r > l) {  // at most four left: load them together
-          int32_t e[4];
+    const uint32_t n_buckets = ((uint32_t)(ts + tn) >> 2) - ((uint32_t)ts >> 2);
+    const int4 *__restrict__ region = reinterpret_cast<const int4 *>(wp.adjset) + 2 * (size_t)((uint32_t)ts >> 2);
+    const bool use_set = tn >= SET_MIN_DEG;
+    for (int it = 0;; it += TRY_BATCH) {
+      int32_t x[TRY_BATCH], v[TRY_BATCH];
+      float y[TRY_BATCH];
+      int n_try = TRY_BATCH;  // the round ends at the first try that is sure to accept
 #pragma unroll
-          for (int k = 0; k < 4; k++) e[k] = l + k < r ? ld_graph<STREAM>(tedges + l + k) : -1;
-          ev.n2v_probes += r - l;
-          found = v == e[0] || v == e[1] || v == e[2] || v == e[3];
+      for (int k = 0; k < TRY_BATCH; k++) {
+        if (k < n_try) {
+          x[k] = rng.rand_int(n);
+          y[k] = __fmul_rn(rng.uniform(), bound);
+          if (y[k] < sure) n_try = k + 1;
         }
-        h = found ? inv_q : 1.0f;
       }
-      if (y < h || it >= RETRY_CAP) {
-        if (it >= RETRY_CAP) atomicOr(status, ND_DEV_RETRY_LIMIT);
+#pragma unroll
+      for (int k = 0; k < TRY_BATCH; k++) v[k] = k < n_try ? ld_graph<STREAM>(edges + x[k]) : -1;
+      // membership gathers of the tries that need one, issued together
+      bool is_ret[TRY_BATCH], need[TRY_BATCH];
+      uint32_t bucket[TRY_BATCH];
+      int4 ba[TRY_BATCH], bb[TRY_BATCH];
+#pragma unroll
+      for (int k = 0; k < TRY_BATCH; k++) {
+        is_ret[k] = wp.n2v_compat ? (x[k] == t) : (v[k] == t);  // randomWalks.cu:159 compares the index
+        need[k] = k < n_try && !is_ret[k] && y[k] >= lo && y[k] < hi;
+        bucket[k] = set_bucket(v[k], n_buckets);
+        if (need[k] && use_set) {
+          ba[k] = ld_graph<STREAM>(region + 2 * (size_t)bucket[k]);
+          bb[k] = ld_graph<STREAM>(region + 2 * (size_t)bucket[k] + 1);
+        } else {
+          ba[k] = make_int4(SET_EMPTY, SET_EMPTY, SET_EMPTY, SET_EMPTY);
+          bb[k] = ba[k];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < TRY_BATCH; k++) {
+        if (k < n_try) {
+          ev.n2v_tries++;
+          bool accept;
+          if (is_ret[k]) {
+            accept = y[k] < wp.p;
+          } else if (!need[k]) {
+            accept = y[k] < lo;
+          } else {
+            bool found = ba[k].x == v[k] || ba[k].y == v[k] || ba[k].z == v[k] || ba[k].w == v[k] ||
+                         bb[k].x == v[k] || bb[k].y == v[k] || bb[k].z == v[k] || bb[k].w == v[k];
+            if (use_set) ev.n2v_probes += 8;
+            if (!found && (!use_set || bb[k].w != SET_EMPTY))
+              found = n2v_member_slow<STREAM>(g, wp.adjset, ts, tn, v[k], bucket[k], n_buckets, ev.n2v_probes);
+            accept = y[k] < (found ? inv_q : 1.0f);
+          }
+          if (accept) { state_t = transit; return v[k]; }
+        }
+      }
+      if (it > RETRY_CAP) {
+        atomicOr(status, ND_DEV_RETRY_LIMIT);
         state_t = transit;
-        return v;
+        return v[n_try - 1 < 0 ? 0 : n_try - 1];
       }
     }
   }
@@ -172,22 +230,39 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
 
 // ---------------------------------------------------------------- set-up kernels
 
-// one warp per vertex: set the two bits of every neighbour in the vertex's filter region
-__global__ void filter_build_kernel(NdGraphView g, unsigned long long *__restrict__ filter) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp_id = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
-  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t t = warp_id; t < g.V; t += n_warps) {
-    const int32_t rs = g.row_ptr[t], deg = g.row_ptr[t + 1] - rs;
-    if (deg < FILTER_MIN_DEG) continue;
-    unsigned long long *region = filter + ((uint32_t)rs >> 2);
-    for (int e = lane; e < deg; e += 32) {
-      uint32_t word;
-      unsigned long long mask;
-      filter_slot(g.col[rs + e], (uint32_t)deg >> 2, word, mask);
-      atomicOr(region + word, mask);
+// thread per CSR entry: find the entry's source vertex by bisection of the row offsets and insert
+// the neighbour id into the source's set (first free slot at or after the home bucket)
+__global__ void adjset_build_kernel(NdGraphView g, int64_t E, int32_t *__restrict__ adjset, int *__restrict__ status) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+    int32_t lo = 0, hi = g.V;  // last vertex with row_ptr[v] <= e
+    while (hi - lo > 1) {
+      const int32_t mid = lo + ((hi - lo) >> 1);
+      if ((int64_t)g.row_ptr[mid] <= e) lo = mid; else hi = mid;
     }
+    const int32_t rs = g.row_ptr[lo], deg = g.row_ptr[lo + 1] - rs;
+    if (deg < SET_MIN_DEG) continue;
+    const uint32_t n_buckets = ((uint32_t)(rs + deg) >> 2) - ((uint32_t)rs >> 2);
+    int32_t *region = adjset + 8 * (size_t)((uint32_t)rs >> 2);
+    const int32_t v = g.col[e];
+    uint32_t b = set_bucket(v, n_buckets);
+    bool done = false;
+    for (uint32_t it = 0; it < n_buckets && !done; it++) {
+      for (int i = 0; i < 8 && !done; i++) {
+        int32_t *slot = region + 8 * (size_t)b + i;
+        int32_t cur = *(volatile int32_t *)slot;
+        if (cur == SET_EMPTY) cur = atomicCAS(slot, SET_EMPTY, v);
+        done = cur == SET_EMPTY || cur == v;  // placed, or the id is in the set already (repeated edge)
+      }
+      b = b + 1 < n_buckets ? b + 1 : 0;
+    }
+    if (!done) atomicOr(status, ND_DEV_RETRY_LIMIT);  // cannot happen: a region has at least deg slots
   }
+}
+
+__global__ void colw_build_kernel(const int32_t *__restrict__ col, const float *__restrict__ w, int64_t E,
+                                  int2 *__restrict__ colw) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x)
+    colw[e] = make_int2(col[e], __float_as_int(w[e]));
 }
 
 __global__ void walk_reset_kernel(const int32_t *__restrict__ initial, int32_t V, int64_t S, int steps,
@@ -277,28 +352,47 @@ walk_next_tp_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample
 //
 // The transit ids are a dense key space (< V) and the map holds at most one pair per walk, so
 // the inversion does not need a multi-pass sort: next() takes a ticket on its new transit
-// (atomicAdd on cnt[transit], the ticket is the pair's rank inside the transit's run), two small
-// kernels turn the counters into run offsets (chunk sums, then per-chunk exclusive scan, which
-// also clears the counters and publishes the live count), and one kernel moves every pair to
-// offs[transit] + rank.  16 B read + 8 B written per pair beside 12 B per vertex of counter
-// traffic, against 2-3 radix passes.  The order of the pairs inside one transit's run depends on
-// the order the tickets were drawn; results do not, because every draw is keyed by the sample.
+// (atomicAdd on cnt[transit], the ticket is the pair's rank inside the transit's run) and counts
+// the pair in a coarse histogram (one bin per CNT_SUPER vertices, kept in shared memory and
+// flushed once per CTA); one kernel turns the counters into run offsets (a CTA per bin: the bins
+// before it give its base, then an exclusive scan of its own counters, which also clears them and
+// publishes the live count); one kernel moves every pair to offs[transit] + rank.  Three launches
+// and 16 B read + 8 B written per pair beside the counter traffic, against 2-3 radix passes of
+// three launches each.  The order of the pairs inside one transit's run depends on the order the
+// tickets were drawn; results do not, because every draw is keyed by the sample.
+// node2vec: the previous vertex of a walk travels with the sorted map (the scatter copies the
+// transit the pair was read under), so next() reads it with a coalesced load instead of a gather
+// by sample id.
 
-constexpr int CNT_THREADS = 256;
-constexpr int CNT_PER_THREAD = 8;
-constexpr int CNT_CHUNK = CNT_THREADS * CNT_PER_THREAD;  // counters per CTA
+constexpr int CNT_SUPER = 4096;                             // counters per scan CTA = vertices per coarse bin
+constexpr int CNT_SUPER_SHIFT = 12;
+constexpr int SCAN_THREADS = 512;
+constexpr int SCAN_PER_THREAD = CNT_SUPER / SCAN_THREADS;   // 32 consecutive counters per thread
+constexpr int MAX_SMEM_BINS = 8192;                         // coarse bins kept in shared memory (V <= 2^25)
+
+// node2vec keeps a round of candidates and set buckets in registers: three CTAs per SM (80
+// registers) measured faster than two (116) or four (64, spilling)
+template <int APP>
+constexpr int walk_min_ctas() { return APP == ND_APP_NODE2VEC ? 3 : 1; }
 
 template <int APP, bool COUNT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, walk_min_ctas<APP>())
 walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample,
                        const int32_t *__restrict__ in_key, const int32_t *__restrict__ in_val,
-                       const int32_t *__restrict__ d_n, int32_t *__restrict__ out_key,
-                       int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
-                       uint32_t *__restrict__ cnt, uint8_t *__restrict__ dirty, int32_t *__restrict__ tmp_step,
-                       int32_t *__restrict__ len, int32_t *__restrict__ state, int *__restrict__ status,
-                       unsigned long long *__restrict__ stats) {
+                       const int32_t *__restrict__ in_prev, const int32_t *__restrict__ d_n,
+                       int32_t *__restrict__ out_key, int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
+                       uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum, int bins, int32_t *__restrict__ tmp_step,
+                       int32_t *__restrict__ len, int *__restrict__ status, unsigned long long *__restrict__ stats) {
+  extern __shared__ uint32_t sh_bins[];
   Events ev;
   const int n = *d_n;
+  if ((int64_t)blockIdx.x * blockDim.x >= n) return;  // no pair for this CTA
+  const bool smem_bins = COUNT && bins <= MAX_SMEM_BINS;
+  if (smem_bins) {
+#pragma unroll 1
+    for (int b = threadIdx.x; b < bins; b += blockDim.x) sh_bins[b] = 0u;
+    __syncthreads();
+  }
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int32_t t = in_key[i];
     const int32_t s = in_val[i];
@@ -308,12 +402,11 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
     } else {
       const int32_t rs = __ldg(g.row_ptr + t);
       const int32_t deg = __ldg(g.row_ptr + t + 1) - rs;
-      if (deg > 0) {
+      if (deg > 0) {  // next() runs only on transits with edges (src/nextdoor.cu:255,412)
         Rng rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
         int32_t st = 0;
-        if (APP == ND_APP_NODE2VEC && step > 0) st = state[s];
+        if (APP == ND_APP_NODE2VEC && step > 0) st = in_prev[i];
         nbr = app_next<APP>(g, wp, step, t, rs, deg, st, rng, status, ev);
-        if (APP == ND_APP_NODE2VEC && nbr >= 0) state[s] = st;
       }
     }
     if (nbr >= 0) tmp_step[s] = nbr; else len[s] = step;
@@ -322,77 +415,60 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
       if (nbr >= 0) {
         out_val[i] = s;
         out_rank[i] = (int32_t)atomicAdd(&cnt[nbr], 1u);
-        if (dirty) {  // this chunk of counters has work for the scan (test first: hub chunks are hit by everyone)
-          uint8_t *d = dirty + nbr / CNT_CHUNK;
-          if (__ldcg(d) == 0) *d = 1;
-        }
+        if (smem_bins) atomicAdd(&sh_bins[nbr >> CNT_SUPER_SHIFT], 1u);
+        else atomicAdd(&bsum[nbr >> CNT_SUPER_SHIFT], 1u);
       }
+    }
+  }
+  if (smem_bins) {
+    __syncthreads();
+#pragma unroll 1
+    for (int b = threadIdx.x; b < bins; b += blockDim.x) {
+      const uint32_t c = sh_bins[b];
+      if (c) atomicAdd(&bsum[b], c);
     }
   }
   if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
 }
 
-__global__ void __launch_bounds__(CNT_THREADS)
-cnt_chunk_sum_kernel(const uint32_t *__restrict__ cnt, int32_t V, const uint8_t *__restrict__ dirty,
-                     uint32_t *__restrict__ bsum) {
-  __shared__ uint32_t wsum[CNT_THREADS / 32];
-  if (dirty && !dirty[blockIdx.x]) {  // no ticket was drawn in this chunk: its counters are all zero
-    if (threadIdx.x == 0) bsum[blockIdx.x] = 0u;
-    return;
-  }
-  const uint4 *src = reinterpret_cast<const uint4 *>(cnt + (size_t)blockIdx.x * CNT_CHUNK);
-  uint32_t part = 0;
-#pragma unroll
-  for (int r = 0; r < CNT_PER_THREAD / 4; r++) {
-    const uint4 a = src[r * CNT_THREADS + threadIdx.x];
-    part += a.x + a.y + a.z + a.w;
-  }
-  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = part;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t t = 0;
-    for (int w = 0; w < CNT_THREADS / 32; w++) t += wsum[w];
-    bsum[blockIdx.x] = t;
-  }
-}
-
-// CTA b: start of its chunk = sum of the chunk sums before it; exclusive scan of its counters into
-// offs; counters cleared for the next step; the last CTA publishes the number of live pairs.
-__global__ void __launch_bounds__(CNT_THREADS)
-cnt_scan_kernel(uint32_t *__restrict__ cnt, int32_t V, const uint32_t *__restrict__ bsum,
-                uint8_t *__restrict__ dirty, uint32_t *__restrict__ offs, int32_t *__restrict__ d_n_out) {
-  __shared__ uint32_t wsum[CNT_THREADS / 32];
+// CTA b owns the counters of coarse bin b: its base is the sum of the bins before it; exclusive
+// scan of its counters into offs; counters cleared for the next step; the last CTA publishes the
+// number of live pairs.  A bin nobody drew a ticket in holds no transit of the next step: its
+// offsets are never read and its counters are zero already.
+__global__ void __launch_bounds__(SCAN_THREADS)
+cnt_scan_kernel(uint32_t *__restrict__ cnt, const uint32_t *__restrict__ bsum, uint32_t *__restrict__ offs,
+                int32_t *__restrict__ d_n_out) {
+  __shared__ uint32_t wsum[SCAN_THREADS / 32];
   __shared__ uint32_t base_sh;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool is_dirty = !dirty || dirty[blockIdx.x] != 0;
   const bool is_last = blockIdx.x == gridDim.x - 1;
-  // a chunk nobody drew a ticket in holds no transit of the next step: its offsets are never
-  // read, so the CTA has nothing to do (the last CTA still publishes the live count)
-  if (!is_dirty && !is_last) return;
+  const uint32_t own = bsum[blockIdx.x];
+  if (own == 0u && !is_last) return;
   uint32_t part = 0;
-  for (int i = threadIdx.x; i < (int)blockIdx.x; i += CNT_THREADS) part += bsum[i];
+  for (int i = threadIdx.x; i < (int)blockIdx.x; i += SCAN_THREADS) part += bsum[i];
   for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
   if (lane == 0) wsum[warp] = part;
   __syncthreads();
   if (threadIdx.x == 0) {
     uint32_t t = 0;
-    for (int w = 0; w < CNT_THREADS / 32; w++) t += wsum[w];
+    for (int w = 0; w < SCAN_THREADS / 32; w++) t += wsum[w];
     base_sh = t;
   }
   __syncthreads();
-  // each thread owns 8 consecutive counters (one 32-byte sector)
-  // (the arrays are padded to whole chunks, so the two 16-byte accesses never leave them)
-  const int first = blockIdx.x * CNT_CHUNK + threadIdx.x * CNT_PER_THREAD;
-  uint32_t c[CNT_PER_THREAD];
-  uint32_t tsum = 0;
-  {
-    const uint4 a = *reinterpret_cast<const uint4 *>(cnt + first);
-    const uint4 b = *reinterpret_cast<const uint4 *>(cnt + first + 4);
-    c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+  if (own == 0u) {  // last CTA, empty bin
+    if (threadIdx.x == 0) *d_n_out = (int32_t)base_sh;
+    return;
   }
+  // each thread owns SCAN_PER_THREAD consecutive counters (the arrays are padded to whole bins)
+  const size_t first = (size_t)blockIdx.x * CNT_SUPER + (size_t)threadIdx.x * SCAN_PER_THREAD;
+  uint32_t c[SCAN_PER_THREAD];
+  uint32_t tsum = 0;
 #pragma unroll
-  for (int r = 0; r < CNT_PER_THREAD; r++) tsum += c[r];
+  for (int r = 0; r < SCAN_PER_THREAD / 4; r++) {
+    const uint4 a = *reinterpret_cast<const uint4 *>(cnt + first + 4 * r);
+    c[4 * r] = a.x; c[4 * r + 1] = a.y; c[4 * r + 2] = a.z; c[4 * r + 3] = a.w;
+    tsum += a.x + a.y + a.z + a.w;
+  }
   uint32_t inc = tsum;
   for (int o = 1; o < 32; o <<= 1) {
     const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
@@ -403,35 +479,45 @@ cnt_scan_kernel(uint32_t *__restrict__ cnt, int32_t V, const uint32_t *__restric
   __syncthreads();
   uint32_t run = base_sh + inc - tsum;
   for (int w = 0; w < warp; w++) run += wsum[w];
-  uint32_t o[CNT_PER_THREAD];
+  if (tsum != 0u) {  // a thread without tickets has nothing to publish or clear
 #pragma unroll
-  for (int r = 0; r < CNT_PER_THREAD; r++) { o[r] = run; run += c[r]; }
-  *reinterpret_cast<uint4 *>(offs + first) = make_uint4(o[0], o[1], o[2], o[3]);
-  *reinterpret_cast<uint4 *>(offs + first + 4) = make_uint4(o[4], o[5], o[6], o[7]);
-  *reinterpret_cast<uint4 *>(cnt + first) = make_uint4(0u, 0u, 0u, 0u);
-  *reinterpret_cast<uint4 *>(cnt + first + 4) = make_uint4(0u, 0u, 0u, 0u);
-  if (is_last && threadIdx.x == CNT_THREADS - 1) *d_n_out = (int32_t)run;
-  if (dirty && threadIdx.x == 0) dirty[blockIdx.x] = 0;
+    for (int r = 0; r < SCAN_PER_THREAD / 4; r++) {
+      uint4 o;
+      o.x = run; run += c[4 * r];
+      o.y = run; run += c[4 * r + 1];
+      o.z = run; run += c[4 * r + 2];
+      o.w = run; run += c[4 * r + 3];
+      *reinterpret_cast<uint4 *>(offs + first + 4 * r) = o;
+      *reinterpret_cast<uint4 *>(cnt + first + 4 * r) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  if (is_last && threadIdx.x == SCAN_THREADS - 1) *d_n_out = (int32_t)run;
 }
 
+// Moves every live pair to its place in the sorted map of the next step; clears the coarse bins
+// (the scan before it was their last reader).
 __global__ void __launch_bounds__(256)
 walk_scatter_kernel(const int32_t *__restrict__ d_n, int32_t V, const int32_t *__restrict__ ukey,
                     const int32_t *__restrict__ uval, const int32_t *__restrict__ urank,
-                    const uint32_t *__restrict__ offs, int32_t *__restrict__ okey, int32_t *__restrict__ oval) {
+                    const int32_t *__restrict__ cur_transit, const uint32_t *__restrict__ offs,
+                    int32_t *__restrict__ okey, int32_t *__restrict__ oval, int32_t *__restrict__ oprev,
+                    uint32_t *__restrict__ bsum, int bins) {
   const int n = *d_n;
+  for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < bins; b += gridDim.x * blockDim.x) bsum[b] = 0u;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int32_t k = ukey[i];
     if (k == V) continue;
     const uint32_t pos = __ldg(offs + k) + (uint32_t)urank[i];
     okey[pos] = k;
     oval[pos] = uval[i];
+    if (oprev) oprev[pos] = cur_transit[i];
   }
 }
 
 // ---------------------------------------------------------------- sample-parallel: a thread owns a walk
 
 template <int APP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, walk_min_ctas<APP>())
 walk_sp_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_t S,
                const int32_t *__restrict__ initial, int32_t *__restrict__ tmp,
                int32_t *__restrict__ len, int *__restrict__ status, unsigned long long *__restrict__ stats) {
@@ -557,12 +643,25 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_CUDA(cudaMalloc(&s->d_len, sizeof(int32_t) * (size_t)S));
   if (s->p.app == ND_APP_NODE2VEC) {
     ND_CUDA(cudaMalloc(&s->d_state, sizeof(int32_t) * (size_t)S));
-    // adjacency pre-filter: 2 bytes per CSR entry, built once per sampler
-    const size_t words = (size_t)(s->g->E / 4) + 2;
-    ND_CUDA(cudaMalloc(&s->d_filter, sizeof(unsigned long long) * words));
-    ND_CUDA(cudaMemset(s->d_filter, 0, sizeof(unsigned long long) * words));
-    filter_build_kernel<<<s->dev.sms * 16, 256>>>(nd_view(s->g), s->d_filter);
-    ND_CUDA(cudaGetLastError());
+    if (!s->g->adjset) {  // 8 bytes per CSR entry, built once per graph
+      const size_t slots = 8 * ((size_t)(s->g->E / 4) + 2);
+      int32_t *set = nullptr;
+      ND_CUDA(cudaMalloc(&set, sizeof(int32_t) * slots));
+      ND_CUDA(cudaMemset(set, 0xff, sizeof(int32_t) * slots));
+      ND_CUDA(cudaMemset(s->d_status, 0, sizeof(int)));
+      adjset_build_kernel<<<s->dev.sms * 16, 256>>>(nd_view(s->g), s->g->E, set, s->d_status);
+      int st = 0;
+      ND_CUDA(cudaMemcpy(&st, s->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+      if (st) { cudaFree(set); ND_REQUIRE(false, ND_ERR_DEVICE, "neighbour-set construction failed (status %d)", st); }
+      s->g->adjset = set;
+    }
+  }
+  if ((s->p.app == ND_APP_DEEPWALK || s->p.app == ND_APP_PPR) && !s->g->colw && s->g->E > 0) {
+    int2 *cw = nullptr;
+    ND_CUDA(cudaMalloc(&cw, sizeof(int2) * (size_t)s->g->E));
+    colw_build_kernel<<<s->dev.sms * 16, 256>>>(s->g->col, s->g->w, s->g->E, cw);
+    ND_CUDA(cudaDeviceSynchronize());
+    s->g->colw = cw;
   }
   s->map_cap = S;
   for (int i = 0; i < 2; i++) {
@@ -576,14 +675,17 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_TRY(nd_radix_scratch_alloc(&s->radix, key_bits, S));
   // counting inversion (load-balanced mode)
   const size_t V = (size_t)s->g->V;
-  const size_t chunks = (V + CNT_CHUNK - 1) / CNT_CHUNK;
-  ND_CUDA(cudaMalloc(&s->d_cnt, sizeof(uint32_t) * chunks * CNT_CHUNK));   // padded to whole chunks
-  ND_CUDA(cudaMalloc(&s->d_offs, sizeof(uint32_t) * chunks * CNT_CHUNK));
-  ND_CUDA(cudaMalloc(&s->d_bsum, sizeof(uint32_t) * chunks));
-  ND_CUDA(cudaMalloc(&s->d_dirty, chunks));
-  ND_CUDA(cudaMemset(s->d_dirty, 0, chunks));
+  const size_t bins = (V + CNT_SUPER - 1) / CNT_SUPER;
+  ND_CUDA(cudaMalloc(&s->d_cnt, sizeof(uint32_t) * bins * CNT_SUPER));   // padded to whole bins
+  ND_CUDA(cudaMalloc(&s->d_offs, sizeof(uint32_t) * bins * CNT_SUPER));
+  ND_CUDA(cudaMalloc(&s->d_bsum, sizeof(uint32_t) * bins));
   ND_CUDA(cudaMalloc(&s->d_rank, sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
-  ND_CUDA(cudaMemset(s->d_cnt, 0, sizeof(uint32_t) * chunks * CNT_CHUNK));
+  ND_CUDA(cudaMemset(s->d_cnt, 0, sizeof(uint32_t) * bins * CNT_SUPER));
+  ND_CUDA(cudaMemset(s->d_bsum, 0, sizeof(uint32_t) * bins));
+  for (int i = 0; i < 2; i++) {
+    ND_CUDA(cudaMalloc(&s->d_lb_key[i], sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
+    if (s->p.app == ND_APP_NODE2VEC) ND_CUDA(cudaMalloc(&s->d_prev[i], sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
+  }
   return ND_OK;
 }
 
@@ -617,7 +719,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
   const int steps = s->p.steps;
   const int app = s->p.app;
   cudaStream_t st = s->stream;
-  WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps, s->d_filter};
+  WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps, s->g->adjset, s->g->colw};
   const int rblocks = (int)((S + 255) / 256);
   walk_reset_kernel<<<rblocks > 1 ? rblocks : 1, 256, 0, st>>>(s->d_initial, s->g->V, S, steps, s->d_len, s->d_state, s->d_stats);
   nd_count_launches(1);
@@ -669,25 +771,27 @@ static int walk_enqueue(nd_sampler *s, int mode) {
   } else {
     // load-balanced transit-parallel: next() draws tickets, counting inversion
     const int V = s->g->V;
-    const int chunks = (V + CNT_CHUNK - 1) / CNT_CHUNK;
-    // Tracking which counter chunks were touched lets the scan skip the others; it pays when the
-    // counter array is large against the live pairs (late PPR steps on 2^24 vertices).  On small
-    // graphs every chunk is touched every step and the flag traffic would only add contention.
-    uint8_t *dirty = chunks >= 2048 ? s->d_dirty : nullptr;
+    const int bins = (V + CNT_SUPER - 1) / CNT_SUPER;
+    const size_t smem = bins <= MAX_SMEM_BINS ? sizeof(uint32_t) * (size_t)bins : 0;
     const int64_t blocks = (S + 255) / 256;
-    const int grid = (int)(blocks < (int64_t)s->dev.sms * 64 ? blocks : (int64_t)s->dev.sms * 64);
+    const int grid = (int)(blocks < (int64_t)s->dev.sms * 16 ? blocks : (int64_t)s->dev.sms * 16);
     NdGraphView gv = nd_view(s->g);
-    const int32_t *in_key = s->d_init_key, *in_val = s->d_init_val;
-    int32_t *ukey = s->d_map_key[0], *uval = s->d_map_val[0];   // unsorted pairs written by next()
-    int32_t *skey = s->d_map_key[1], *sval = s->d_map_val[1];   // sorted map of the following step
+    const bool n2v = app == ND_APP_NODE2VEC;
+    // unsorted pairs written by next(): key/val in d_map_*[0]; sorted maps ping-pong between
+    // (d_map_key[1], d_map_val[1], d_prev[0]) and (d_lb_key[0], d_lb_key[1], d_prev[1])
+    int32_t *ukey = s->d_map_key[0], *uval = s->d_map_val[0];
+    int32_t *skey[2] = {s->d_map_key[1], s->d_lb_key[0]};
+    int32_t *sval[2] = {s->d_map_val[1], s->d_lb_key[1]};
+    const int32_t *in_key = s->d_init_key, *in_val = s->d_init_val, *in_prev = nullptr;
+    int cur = 0;  // sorted map the scatter of this step writes
     for (int step = 0; step < steps; step++) {
       const bool last = step == steps - 1;
       const int32_t *d_n = s->d_nlive + step;
       int32_t *tmp_step = s->d_tmp + (int64_t)step * S;
       nd_phase_begin(s, ND_PHASE_NEXT);
 #define ND_LAUNCH_COUNT(APPID)                                                                                         \
-  if (last) walk_next_count_kernel<APPID, false><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, dirty, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats); \
-  else walk_next_count_kernel<APPID, true><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, d_n, ukey, uval, s->d_rank, s->d_cnt, dirty, tmp_step, s->d_len, s->d_state, s->d_status, s->d_stats);
+  if (last) walk_next_count_kernel<APPID, false><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, in_prev, d_n, ukey, uval, s->d_rank, s->d_cnt, s->d_bsum, bins, tmp_step, s->d_len, s->d_status, s->d_stats); \
+  else walk_next_count_kernel<APPID, true><<<grid, 256, smem, st>>>(gv, wp, step, s->first, in_key, in_val, in_prev, d_n, ukey, uval, s->d_rank, s->d_cnt, s->d_bsum, bins, tmp_step, s->d_len, s->d_status, s->d_stats);
       switch (app) {
         case ND_APP_UNIFORM_WALK: ND_LAUNCH_COUNT(ND_APP_UNIFORM_WALK) break;
         case ND_APP_DEEPWALK: ND_LAUNCH_COUNT(ND_APP_DEEPWALK) break;
@@ -699,13 +803,15 @@ static int walk_enqueue(nd_sampler *s, int mode) {
       nd_count_launches(1);
       if (last) break;
       nd_phase_begin(s, ND_PHASE_INVERT);
-      cnt_chunk_sum_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, dirty, s->d_bsum);
-      cnt_scan_kernel<<<chunks, CNT_THREADS, 0, st>>>(s->d_cnt, V, s->d_bsum, dirty, s->d_offs, s->d_nlive + step + 1);
-      walk_scatter_kernel<<<grid, 256, 0, st>>>(d_n, V, ukey, uval, s->d_rank, s->d_offs, skey, sval);
+      cnt_scan_kernel<<<bins, SCAN_THREADS, 0, st>>>(s->d_cnt, s->d_bsum, s->d_offs, s->d_nlive + step + 1);
+      walk_scatter_kernel<<<grid, 256, 0, st>>>(d_n, V, ukey, uval, s->d_rank, in_key, s->d_offs, skey[cur], sval[cur],
+                                                n2v ? s->d_prev[cur] : nullptr, s->d_bsum, bins);
       nd_phase_end(s);
-      nd_count_launches(3);
-      in_key = skey;
-      in_val = sval;
+      nd_count_launches(2);
+      in_key = skey[cur];
+      in_val = sval[cur];
+      in_prev = n2v ? s->d_prev[cur] : nullptr;
+      cur ^= 1;
     }
   }
   nd_phase_begin(s, ND_PHASE_FINALIZE);
