@@ -78,7 +78,7 @@ void free_sampler(nd_sampler *s) {
   for (int i = 0; i < 2; i++) { cudaFree(s->d_map_key[i]); cudaFree(s->d_map_val[i]); }
   cudaFree(s->d_init_key); cudaFree(s->d_init_val); cudaFree(s->d_nlive); cudaFree(s->d_stats); cudaFree(s->d_status);
   cudaFree(s->d_runs); cudaFree(s->d_bin_counts); cudaFree(s->d_hop_counts);
-  cudaFree(s->d_adj_row); cudaFree(s->d_adj_col); cudaFree(s->d_prob); cudaFree(s->d_cand); cudaFree(s->d_cand_w);
+  cudaFree(s->d_adj_row); cudaFree(s->d_adj_col); cudaFree(s->d_prob); cudaFree(s->d_cand); cudaFree(s->d_cand_w); cudaFree(s->d_acc);
   cudaFree(s->d_cnt); cudaFree(s->d_offs); cudaFree(s->d_bsum); cudaFree(s->d_rank);
   for (int i = 0; i < 2; i++) { cudaFree(s->d_lb_key[i]); cudaFree(s->d_prev[i]); }
   for (int i = 0; i < 3; i++) if (s->graph_exec[i]) cudaGraphExecDestroy(s->graph_exec[i]);

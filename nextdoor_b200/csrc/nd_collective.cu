@@ -24,6 +24,7 @@
 // per-step cudaMalloc, src/nextdoor.cu:2413-2429) so that samples can be processed in chunks that
 // fit the candidate buffers whatever the hub sizes are.
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 #include "nd_common.cuh"
@@ -59,7 +60,7 @@ __device__ __forceinline__ bool has_edge_logn(const NdGraphView &g, int32_t src,
 // adjacency entries of one layer of one sample: (row,col) = (i,j) where transit i -- vertex j is an edge
 __device__ __forceinline__ void emit_adjacency(const NdGraphView &g, const CollParams &cp, const int32_t *tr,
                                                const int32_t *layer, int32_t *arow, int32_t *acol) {
-  for (int e = threadIdx.x; e < cp.stride; e += CTHREADS) {
+  for (int e = threadIdx.x; e < cp.stride; e += blockDim.x) {
     const int i = e / cp.L, j = e - i * cp.L;
     int32_t ri = -1, cj = -1;
     if (i < cp.ntr) {
@@ -261,6 +262,279 @@ coll_sample_kernel(NdGraphView g, CollParams cp, int steps, int64_t s0, int64_t 
   }
 }
 
+// ---------------------------------------------------------------- importance sampling, bitmap path
+//
+// When a bit per vertex fits the CTA's shared memory (V up to about 1.4 M with 227 KB), the union
+// of a sample's neighbour lists needs no sort: one CTA per sample streams the transits' lists and
+// sets the neighbours' bits; a popcount scan over groups of BM_GROUP_WORDS words ranks every set
+// bit, which is the candidate's index in the sorted unique union; the candidates' weights are
+// summed per group and scanned in fp64, and a draw bisects the group sums and then walks the one
+// group its target falls into.  FastGCN weights are recomputed from the row offsets where they are
+// needed; LADIES accumulates its terms per candidate rank in a global fp64 array (one V-entry
+// region per CTA) during a second pass over the lists.  No host round trip, no chunking: one
+// launch per layer for all samples.  Sums are fp64, so they agree with the sorted sequential
+// order to ~1e-16 (FastGCN's integer weights sum exactly).
+constexpr int BM_THREADS = 1024;
+constexpr int BM_GROUP_WORDS = 16;   // 512 candidates per group
+constexpr int BM_BIG_LIST = 4096;    // lists at least this long are streamed by the whole CTA
+
+struct BmLayout {
+  int words, groups;
+  uint32_t off_gcdf, off_gpref, off_tr, off_layer, off_rowsum, off_red, bytes;
+};
+
+__device__ __forceinline__ void bm_mark(uint32_t *bm, int32_t v) {
+  const uint32_t bit = 1u << (v & 31);
+  uint32_t *wp = bm + ((uint32_t)v >> 5);
+  if (!(*(volatile uint32_t *)wp & bit)) atomicOr(wp, bit);  // hub lists overlap: most bits are set already
+}
+
+__device__ __forceinline__ uint32_t bm_rank(const uint32_t *bm, const uint32_t *gpref, int32_t v) {
+  const uint32_t word = (uint32_t)v >> 5, grp = word / BM_GROUP_WORDS;
+  uint32_t r = gpref[grp];
+  for (uint32_t k = grp * BM_GROUP_WORDS; k < word; k++) r += __popc(bm[k]);
+  return r + __popc(bm[word] & ((1u << (v & 31)) - 1u));
+}
+
+template <bool LADIES>
+__device__ __forceinline__ float bm_weight(const NdGraphView &g, const double *acc, int32_t v, uint32_t rank) {
+  if (LADIES) return (float)acc[rank];
+  const float d = __int2float_rn(__ldg(g.row_ptr + v + 1) - __ldg(g.row_ptr + v));
+  return __fmul_rn(d, d);
+}
+
+// exclusive (uint32) or inclusive (double) scan of a shared array by the whole CTA: every thread
+// owns a contiguous chunk, the chunk totals are scanned through warp shuffles
+__device__ __forceinline__ uint32_t bm_scan_u32(uint32_t *a, int n, uint32_t *red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per = (n + BM_THREADS - 1) / BM_THREADS;
+  const int b = threadIdx.x * per, e = b + per < n ? b + per : n;
+  uint32_t sum = 0;
+  for (int i = b; i < e; i++) sum += a[i];
+  uint32_t inc = sum;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) red[warp] = inc;
+  __syncthreads();
+  uint32_t base = inc - sum;
+  for (int w = 0; w < warp; w++) base += red[w];
+  uint32_t total = 0;
+  for (int w = 0; w < BM_THREADS / 32; w++) total += red[w];
+  for (int i = b; i < e; i++) { const uint32_t c = a[i]; a[i] = base; base += c; }
+  __syncthreads();
+  return total;
+}
+
+__device__ __forceinline__ void bm_scan_f64(double *a, int n, double *red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per = (n + BM_THREADS - 1) / BM_THREADS;
+  const int b = threadIdx.x * per, e = b + per < n ? b + per : n;
+  double sum = 0.0;
+  for (int i = b; i < e; i++) sum += a[i];
+  double inc = sum;
+  for (int o = 1; o < 32; o <<= 1) {
+    const double t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) red[warp] = inc;
+  __syncthreads();
+  double base = inc - sum;
+  for (int w = 0; w < warp; w++) base += red[w];
+  for (int i = b; i < e; i++) { base += a[i]; a[i] = base; }
+  __syncthreads();
+}
+
+template <bool LADIES>
+__global__ void __launch_bounds__(BM_THREADS, 1)
+coll_bitmap_kernel(NdGraphView g, CollParams cp, int steps, int64_t S, BmLayout lay, const int32_t *__restrict__ initial,
+                   int32_t *out, double *__restrict__ acc_all, int32_t *__restrict__ adj_row,
+                   int32_t *__restrict__ adj_col, float *__restrict__ prob, unsigned long long *__restrict__ stats) {
+  extern __shared__ __align__(16) unsigned char bm_smem[];
+  uint32_t *bm = reinterpret_cast<uint32_t *>(bm_smem);
+  double *gcdf = reinterpret_cast<double *>(bm_smem + lay.off_gcdf);
+  uint32_t *gpref = reinterpret_cast<uint32_t *>(bm_smem + lay.off_gpref);
+  int32_t *sh_tr = reinterpret_cast<int32_t *>(bm_smem + lay.off_tr);
+  int32_t *sh_layer = reinterpret_cast<int32_t *>(bm_smem + lay.off_layer);
+  float *sh_rowsum = reinterpret_cast<float *>(bm_smem + lay.off_rowsum);
+  double *red = reinterpret_cast<double *>(bm_smem + lay.off_red);   // 32 doubles
+  uint32_t *red_u = reinterpret_cast<uint32_t *>(red + 32);           // 32 words
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  double *acc = LADIES ? acc_all + (size_t)blockIdx.x * (size_t)cp.V : nullptr;
+  unsigned long long ids_sum = 0, uniq_sum = 0;  // thread 0
+  uint32_t valid = 0;
+  for (int64_t s = blockIdx.x; s < S; s += gridDim.x) {
+    const int32_t *tr = transits_of(cp, initial, out, s);
+    for (int i = tid; i < cp.ntr; i += BM_THREADS) sh_tr[i] = tr[i];
+    for (int w = tid * 4; w < lay.words; w += BM_THREADS * 4) *reinterpret_cast<uint4 *>(bm + w) = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    // ---- pass 1: the union as a bitmap (and the LADIES row sums)
+    for (int i = warp; i < cp.ntr; i += BM_THREADS / 32) {  // short lists: a warp each
+      const int32_t t = sh_tr[i];
+      if (t < 0 || t >= cp.V) { if (LADIES && lane == 0) sh_rowsum[i] = 0.f; continue; }
+      const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
+      if (deg >= BM_BIG_LIST) continue;
+      double part = 0.0;
+      for (int e = lane; e < deg; e += 32) {
+        bm_mark(bm, __ldg(g.col + rs + e));
+        if (LADIES) part += (double)__ldg(g.w + rs + e);
+      }
+      if (LADIES) {
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) sh_rowsum[i] = (float)part;
+      }
+    }
+    for (int i = 0; i < cp.ntr; i++) {  // long lists: the whole CTA
+      const int32_t t = sh_tr[i];
+      if (t < 0 || t >= cp.V) continue;
+      const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
+      if (tid == 0) ids_sum += (unsigned long long)deg;
+      if (deg < BM_BIG_LIST) continue;
+      double part = 0.0;
+      for (int e = tid; e < deg; e += BM_THREADS) {
+        bm_mark(bm, __ldg(g.col + rs + e));
+        if (LADIES) part += (double)__ldg(g.w + rs + e);
+      }
+      if (LADIES) {
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        if (tid == 0) {
+          double tot = 0.0;
+          for (int w = 0; w < BM_THREADS / 32; w++) tot += red[w];
+          sh_rowsum[i] = (float)tot;
+        }
+        __syncthreads();
+      }
+    }
+    __syncthreads();
+    // ---- candidates per group, ranks
+    for (int gi = tid; gi < lay.groups; gi += BM_THREADS) {
+      uint32_t c = 0;
+#pragma unroll
+      for (int k = 0; k < BM_GROUP_WORDS; k += 4) {
+        const uint4 q = *reinterpret_cast<const uint4 *>(bm + gi * BM_GROUP_WORDS + k);
+        c += __popc(q.x) + __popc(q.y) + __popc(q.z) + __popc(q.w);
+      }
+      gpref[gi] = c;
+    }
+    __syncthreads();
+    const uint32_t U = bm_scan_u32(gpref, lay.groups, red_u);
+    if (tid == 0) uniq_sum += U;
+    // ---- LADIES pass 2: the terms of every list entry, added to the candidate's accumulator
+    if (LADIES) {
+      for (uint32_t u = tid; u < U; u += BM_THREADS) acc[u] = 0.0;
+      __syncthreads();
+      for (int i = warp; i < cp.ntr; i += BM_THREADS / 32) {
+        const int32_t t = sh_tr[i];
+        if (t < 0 || t >= cp.V) continue;
+        const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
+        if (deg >= BM_BIG_LIST) continue;
+        const float rowsum = sh_rowsum[i];
+        for (int e = lane; e < deg; e += 32) {
+          const float r = __fdiv_rn(__ldg(g.w + rs + e), rowsum);
+          atomicAdd(acc + bm_rank(bm, gpref, __ldg(g.col + rs + e)), (double)__fmul_rn(r, r));
+        }
+      }
+      for (int i = 0; i < cp.ntr; i++) {
+        const int32_t t = sh_tr[i];
+        if (t < 0 || t >= cp.V) continue;
+        const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
+        if (deg < BM_BIG_LIST) continue;
+        const float rowsum = sh_rowsum[i];
+        for (int e = tid; e < deg; e += BM_THREADS) {
+          const float r = __fdiv_rn(__ldg(g.w + rs + e), rowsum);
+          atomicAdd(acc + bm_rank(bm, gpref, __ldg(g.col + rs + e)), (double)__fmul_rn(r, r));
+        }
+      }
+      __syncthreads();
+    }
+    // ---- weight of every group, in candidate order; inclusive scan over the groups
+    for (int gi = tid; gi < lay.groups; gi += BM_THREADS) {
+      double sum = 0.0;
+      uint32_t r = gpref[gi];
+      for (int k = 0; k < BM_GROUP_WORDS; k++) {
+        uint32_t bits = bm[gi * BM_GROUP_WORDS + k];
+        while (bits) {
+          const int b = __ffs(bits) - 1;
+          bits &= bits - 1;
+          sum += (double)bm_weight<LADIES>(g, acc, (int32_t)(((gi * BM_GROUP_WORDS + k) << 5) + b), r);
+          r++;
+        }
+      }
+      gcdf[gi] = sum;
+    }
+    __syncthreads();
+    bm_scan_f64(gcdf, lay.groups, red);
+    const double total = gcdf[lay.groups - 1];
+    // ---- the layer's draws
+    for (int j = tid; j < cp.L; j += BM_THREADS) {
+      int32_t pick = cp.V;
+      float pr = 0.f;
+      if (U > 0 && total > 0.0) {
+        Rng rng(cp.seed, (uint32_t)(cp.first_sample + s), (uint32_t)cp.step, (uint32_t)j);
+        const double target = (double)rng.uniform() * total;
+        int lo = 0, hi = lay.groups - 1;  // first group whose prefix reaches the target
+        while (lo < hi) {
+          const int mid = lo + (hi - lo) / 2;
+          if (gcdf[mid] >= target) hi = mid; else lo = mid + 1;
+        }
+        double run = lo > 0 ? gcdf[lo - 1] : 0.0;
+        uint32_t r = gpref[lo];
+        int32_t last_v = cp.V;
+        float pw = 0.f;
+        bool found = false;
+        for (int gi = lo; gi < lay.groups && !found; gi++) {
+          for (int k = 0; k < BM_GROUP_WORDS && !found; k++) {
+            uint32_t bits = bm[gi * BM_GROUP_WORDS + k];
+            while (bits && !found) {
+              const int b = __ffs(bits) - 1;
+              bits &= bits - 1;
+              last_v = (int32_t)(((gi * BM_GROUP_WORDS + k) << 5) + b);
+              pw = bm_weight<LADIES>(g, acc, last_v, r);
+              run += (double)pw;
+              r++;
+              found = run >= target;
+            }
+          }
+        }
+        pick = last_v;  // not found: rounding left the target above the last prefix, the last candidate takes it
+        pr = (float)((double)pw / total);
+        valid++;
+      }
+      sh_layer[j] = pick;
+      out[s * cp.fs + (int64_t)cp.step * cp.L + j] = pick;
+      prob[s * cp.fs + (int64_t)cp.step * cp.L + j] = pr;
+    }
+    __syncthreads();
+    const int64_t a = (s * steps + cp.step) * (int64_t)cp.stride;
+    emit_adjacency(g, cp, sh_tr, sh_layer, adj_row + a, adj_col + a);
+    __syncthreads();
+  }
+  for (int o = 16; o > 0; o >>= 1) valid += __shfl_xor_sync(0xffffffffu, valid, o);
+  if (lane == 0 && valid) atomicAdd(&stats[0], (unsigned long long)valid);
+  if (tid == 0) {
+    if (ids_sum) atomicAdd(&stats[5], ids_sum);
+    if (uniq_sum) atomicAdd(&stats[6], uniq_sum);
+  }
+}
+
+static BmLayout bm_layout(int32_t V, int ntr_max, int L) {
+  BmLayout l;
+  l.words = (int)((((int64_t)V + 31) / 32 + BM_GROUP_WORDS - 1) / BM_GROUP_WORDS * BM_GROUP_WORDS);
+  l.groups = l.words / BM_GROUP_WORDS;
+  uint32_t off = 4u * (uint32_t)l.words;       // a multiple of 64
+  l.off_gcdf = off; off += 8u * (uint32_t)l.groups;
+  l.off_red = off; off += 8u * 32u + 4u * 32u;
+  l.off_gpref = off; off += 4u * (uint32_t)(l.groups + 1);
+  l.off_tr = off; off += 4u * (uint32_t)ntr_max;
+  l.off_layer = off; off += 4u * (uint32_t)L;
+  l.off_rowsum = off; off += 4u * (uint32_t)ntr_max;
+  l.bytes = off;
+  return l;
+}
+
 __global__ void coll_reset_kernel(unsigned long long *stats) { if (threadIdx.x < 8) stats[threadIdx.x] = 0ull; }
 
 }  // namespace
@@ -292,7 +566,27 @@ int nd_collective_alloc(nd_sampler *s) {
   ND_CUDA(cudaMalloc(&s->d_len, sizeof(int32_t) * (S1 + 1)));        // per-sample sizes of the layer
   ND_CUDA(cudaMalloc(&s->d_tmp, sizeof(int64_t) * (S1 + 1)));        // per-sample region offsets
   ND_CUDA(cudaMalloc(&s->d_nlive, sizeof(int32_t) * 4));
-  if (p.app == ND_APP_FASTGCN_IS || p.app == ND_APP_LADIES_IS) ND_TRY(ensure_cand(s, (int64_t)1 << 22));
+  if (p.app == ND_APP_FASTGCN_IS || p.app == ND_APP_LADIES_IS) {
+    // bitmap path when a bit per vertex (plus the group arrays) fits the opt-in shared memory of a CTA;
+    // ND_COLLECTIVE_SORT=1 forces the sort pipeline (used by the tests to keep it covered)
+    int optin = 0;
+    ND_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, s->g->device));
+    const BmLayout lay = bm_layout(s->g->V, B > L ? B : L, L);
+    const char *force = getenv("ND_COLLECTIVE_SORT");
+    const bool ladies = p.app == ND_APP_LADIES_IS;
+    if ((int64_t)lay.bytes <= (int64_t)optin && B <= 1024 && L <= 1024 && !(force && force[0] == '1')) {
+      s->coll_bitmap = true;
+      s->coll_grid = (int)std::min<int64_t>(S1, (int64_t)s->dev.sms);
+      if (ladies) {
+        ND_CUDA(cudaFuncSetAttribute(coll_bitmap_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.bytes));
+        ND_CUDA(cudaMalloc(&s->d_acc, sizeof(double) * (size_t)s->coll_grid * (size_t)s->g->V));
+      } else {
+        ND_CUDA(cudaFuncSetAttribute(coll_bitmap_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.bytes));
+      }
+    } else {
+      ND_TRY(ensure_cand(s, (int64_t)1 << 22));
+    }
+  }
   return ND_OK;
 }
 
@@ -313,6 +607,27 @@ int nd_collective_sample(nd_sampler *s, int mode) {
     coll_ref_kernel<<<grid, CTHREADS, 0, st>>>(gv, cp, p.steps, S, s->d_initial, s->d_out, s->d_adj_row, s->d_adj_col, s->d_stats);
     nd_phase_end(s);
     nd_count_launches(1);
+    ND_CUDA(cudaGetLastError());
+    return ND_OK;
+  }
+  if (s->coll_bitmap) {
+    const BmLayout lay = bm_layout(cp.V, cp.B > cp.L ? cp.B : cp.L, cp.L);
+    for (int step = 0; step < p.steps; step++) {
+      cp.step = step;
+      cp.ntr = step == 0 ? cp.B : cp.L;
+      nd_phase_begin(s, ND_PHASE_NEXT);
+      if (p.app == ND_APP_LADIES_IS)
+        coll_bitmap_kernel<true><<<s->coll_grid, BM_THREADS, lay.bytes, st>>>(gv, cp, p.steps, S, lay, s->d_initial, s->d_out, s->d_acc,
+                                                                             s->d_adj_row, s->d_adj_col, s->d_prob, s->d_stats);
+      else
+        coll_bitmap_kernel<false><<<s->coll_grid, BM_THREADS, lay.bytes, st>>>(gv, cp, p.steps, S, lay, s->d_initial, s->d_out, nullptr,
+                                                                              s->d_adj_row, s->d_adj_col, s->d_prob, s->d_stats);
+      nd_phase_end(s);
+      nd_count_launches(1);
+    }
+    const unsigned long long pairs = (unsigned long long)(S * (cp.B + (int64_t)(p.steps - 1) * cp.L));
+    ND_CUDA(cudaMemcpyAsync(s->d_stats + 1, &pairs, sizeof(unsigned long long), cudaMemcpyHostToDevice, st));
+    ND_CUDA(cudaStreamSynchronize(st));
     ND_CUDA(cudaGetLastError());
     return ND_OK;
   }

@@ -188,6 +188,9 @@ struct nd_sampler {
   int32_t *d_cand = nullptr;
   float *d_cand_w = nullptr;
   int64_t cand_cap = 0;
+  bool coll_bitmap = false;       // importance sampling through the shared-memory bitmap kernel
+  int coll_grid = 0;
+  double *d_acc = nullptr;        // LADIES: per-CTA accumulators of the candidates' weights
 
   NdPhaseTimer timer;
   int64_t host_stats[8] = {0};

@@ -92,9 +92,17 @@ def _compare_importance(ndo, hg, opr, S, init, got, gprob, exp):
     return flips
 
 
+@pytest.fixture(params=["bitmap", "sort"])
+def union_path(request, monkeypatch):
+    """The importance samplers build the union either in a shared-memory bitmap (graphs whose
+    vertex count fits) or with the radix-sort pipeline; ND_COLLECTIVE_SORT=1 selects the latter."""
+    monkeypatch.setenv("ND_COLLECTIVE_SORT", "1" if request.param == "sort" else "0")
+    return request.param
+
+
 @pytest.mark.parametrize("app", [8, 9])
 @pytest.mark.parametrize("L,B,steps", [(64, 64, 2), (16, 8, 3)])
-def test_importance_apps_match_oracle(nd, ndo, small_graph, app, L, B, steps):
+def test_importance_apps_match_oracle(nd, ndo, small_graph, union_path, app, L, B, steps):
     g = _graph(nd, small_graph)
     S, first = 300, 17
     pr = nd.app_params(app, steps=steps, fanout=L, batch=B, seed=6)
@@ -121,7 +129,7 @@ def test_importance_apps_match_oracle(nd, ndo, small_graph, app, L, B, steps):
 
 
 @pytest.mark.parametrize("app", [8, 9])
-def test_importance_apps_benchmark_shape(nd, ndo, app):
+def test_importance_apps_benchmark_shape(nd, ndo, union_path, app):
     """2 layers x 64, batches of 64 uniform seeds on a graph with hubs: chunked candidate buffers,
     every sampled vertex is in the union of the previous layer's neighbours."""
     hg = ndo.rmat_graph(1 << 16, 1 << 20, seed=5)
