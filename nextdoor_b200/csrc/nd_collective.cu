@@ -296,6 +296,51 @@ __device__ __forceinline__ uint32_t bm_rank(const uint32_t *bm, const uint32_t *
   return r + __popc(bm[word] & ((1u << (v & 31)) - 1u));
 }
 
+// Streams one neighbour list with STRIDE cooperating threads, BM_UNROLL loads in flight per thread:
+// sets the neighbours' bits and, for LADIES, adds the weights to the caller's partial row sum.
+constexpr int BM_UNROLL = 8;
+template <bool LADIES, int STRIDE>
+__device__ __forceinline__ void bm_stream(const NdGraphView &g, uint32_t *bm, int32_t rs, int32_t deg, int me, double &part) {
+  for (int e0 = me; e0 < deg; e0 += STRIDE * BM_UNROLL) {
+    int32_t v[BM_UNROLL];
+    float w[BM_UNROLL];
+#pragma unroll
+    for (int k = 0; k < BM_UNROLL; k++) {
+      const int e = e0 + k * STRIDE;
+      v[k] = e < deg ? __ldg(g.col + rs + e) : -1;
+      if (LADIES) w[k] = e < deg ? __ldg(g.w + rs + e) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < BM_UNROLL; k++) {
+      if (v[k] >= 0) bm_mark(bm, v[k]);
+      if (LADIES) part += (double)w[k];
+    }
+  }
+}
+
+// LADIES second pass over one list: (w / rowsum)^2 of every entry added to its candidate's accumulator
+template <int STRIDE>
+__device__ __forceinline__ void bm_accumulate(const NdGraphView &g, const uint32_t *bm, const uint32_t *gpref, double *acc,
+                                              int32_t rs, int32_t deg, int me, float rowsum) {
+  for (int e0 = me; e0 < deg; e0 += STRIDE * BM_UNROLL) {
+    int32_t v[BM_UNROLL];
+    float w[BM_UNROLL];
+#pragma unroll
+    for (int k = 0; k < BM_UNROLL; k++) {
+      const int e = e0 + k * STRIDE;
+      v[k] = e < deg ? __ldg(g.col + rs + e) : -1;
+      w[k] = e < deg ? __ldg(g.w + rs + e) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < BM_UNROLL; k++) {
+      if (v[k] >= 0) {
+        const float r = __fdiv_rn(w[k], rowsum);
+        atomicAdd(acc + bm_rank(bm, gpref, v[k]), (double)__fmul_rn(r, r));
+      }
+    }
+  }
+}
+
 template <bool LADIES>
 __device__ __forceinline__ float bm_weight(const NdGraphView &g, const double *acc, int32_t v, uint32_t rank) {
   if (LADIES) return (float)acc[rank];
@@ -376,10 +421,7 @@ coll_bitmap_kernel(NdGraphView g, CollParams cp, int steps, int64_t S, BmLayout 
       const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
       if (deg >= BM_BIG_LIST) continue;
       double part = 0.0;
-      for (int e = lane; e < deg; e += 32) {
-        bm_mark(bm, __ldg(g.col + rs + e));
-        if (LADIES) part += (double)__ldg(g.w + rs + e);
-      }
+      bm_stream<LADIES, 32>(g, bm, rs, deg, lane, part);
       if (LADIES) {
         for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
         if (lane == 0) sh_rowsum[i] = (float)part;
@@ -392,10 +434,7 @@ coll_bitmap_kernel(NdGraphView g, CollParams cp, int steps, int64_t S, BmLayout 
       if (tid == 0) ids_sum += (unsigned long long)deg;
       if (deg < BM_BIG_LIST) continue;
       double part = 0.0;
-      for (int e = tid; e < deg; e += BM_THREADS) {
-        bm_mark(bm, __ldg(g.col + rs + e));
-        if (LADIES) part += (double)__ldg(g.w + rs + e);
-      }
+      bm_stream<LADIES, BM_THREADS>(g, bm, rs, deg, tid, part);
       if (LADIES) {
         for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
         if (lane == 0) red[warp] = part;
@@ -431,22 +470,14 @@ coll_bitmap_kernel(NdGraphView g, CollParams cp, int steps, int64_t S, BmLayout 
         if (t < 0 || t >= cp.V) continue;
         const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
         if (deg >= BM_BIG_LIST) continue;
-        const float rowsum = sh_rowsum[i];
-        for (int e = lane; e < deg; e += 32) {
-          const float r = __fdiv_rn(__ldg(g.w + rs + e), rowsum);
-          atomicAdd(acc + bm_rank(bm, gpref, __ldg(g.col + rs + e)), (double)__fmul_rn(r, r));
-        }
+        bm_accumulate<32>(g, bm, gpref, acc, rs, deg, lane, sh_rowsum[i]);
       }
       for (int i = 0; i < cp.ntr; i++) {
         const int32_t t = sh_tr[i];
         if (t < 0 || t >= cp.V) continue;
         const int32_t rs = __ldg(g.row_ptr + t), deg = __ldg(g.row_ptr + t + 1) - rs;
         if (deg < BM_BIG_LIST) continue;
-        const float rowsum = sh_rowsum[i];
-        for (int e = tid; e < deg; e += BM_THREADS) {
-          const float r = __fdiv_rn(__ldg(g.w + rs + e), rowsum);
-          atomicAdd(acc + bm_rank(bm, gpref, __ldg(g.col + rs + e)), (double)__fmul_rn(r, r));
-        }
+        bm_accumulate<BM_THREADS>(g, bm, gpref, acc, rs, deg, tid, sh_rowsum[i]);
       }
       __syncthreads();
     }
