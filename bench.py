@@ -144,6 +144,34 @@ def next_bytes(wl, st, mode):
     return (8 if app == 9 else 4) * st["union_ids"] + 8 * st["union_unique"] + 8 * edges
 
 
+def gather_ceiling(wl, st, g, next_ms, next_launches, device):
+    """The second ceiling of the walk kernels, measured live: next() is a few independent random
+    4-byte gathers into the graph arrays per pair, and a GPU serves those at a rate set by the
+    arrays' footprint against the L2 (nd_probe_random_gather), far below the copy bandwidth that
+    `peak` is.  graph_gathers = the gathers into graph-sized arrays one pass needs (uniform walk:
+    one neighbour id per edge; weighted: one (id, weight) record per try; node2vec: one candidate
+    per try + one set bucket per membership test), floor = graph_gathers / rate."""
+    import ctypes as C
+    from nextdoor_b200._lib import lib, check
+    app = wl["app"]
+    if app == 0:
+        gathers, footprint = st["sampled_edges"], 4 * g.E
+    elif app in (1, 2):
+        gathers, footprint = st["weight_tries"], 8 * g.E
+    else:
+        gathers, footprint = st["n2v_tries"] + st["n2v_probes"] // 8, 12 * g.E
+    per_launch = max(int(gathers / max(next_launches, 1)), 1)
+    rate = C.c_double(0.0)
+    check(lib.nd_probe_random_gather(device, int(footprint), 1 << 24, 3, C.byref(rate)))
+    small = C.c_double(0.0)   # the same at the size of one launch: fixed launch and ramp costs included
+    check(lib.nd_probe_random_gather(device, int(footprint), per_launch, 20, C.byref(small)))
+    floor_ms = gathers / rate.value * 1e3
+    return {"footprint_bytes": int(footprint), "rate_gathers_per_s": rate.value,
+            "rate_at_launch_size": small.value, "graph_gathers_per_pass": int(gathers),
+            "floor_ms_per_pass": floor_ms, "frac": floor_ms / next_ms if next_ms > 0 else None,
+            "note": "frac = time the pass's graph gathers take at the measured random-gather rate / next() time"}
+
+
 def cpu_baseline(hg, wl, seed, budget_s=12.0):
     """The reference's own next() bodies (oracle/_ref) where they exist for the workload, else the
     oracle port, on all host threads, on a bounded prefix of the workload's samples."""
@@ -341,6 +369,8 @@ def main():
         kernel = {WALK: {0: "walk_next_tp_kernel", 1: "walk_next_count_kernel", 2: "walk_sp_kernel"}[mode],
                   KHOP: "khop_pairs_kernel + khop_staged_kernel" if mode == 1 else "khop_pairs_kernel",
                   COLL: "coll_gather/sort/weigh/sample kernels"}[wl["kind"]]
+        kernel = kernel if wl["kind"] != COLL else "coll_bitmap_kernel"
+        gather = gather_ceiling(wl, st, g, next_ms, next_launches, torch.cuda.current_device()) if wl["kind"] == WALK else None
         cb = None
         if world == 1 and not a.no_cpu_baseline:
             from oracle import ndo
@@ -367,7 +397,7 @@ def main():
             "roofline": {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
                          "launches": next_launches, "avg_launch_us": 1e3 * next_ms / max(next_launches, 1),
-                         "algorithmic_bytes_per_pass": nb},
+                         "algorithmic_bytes_per_pass": nb, "random_gather": gather},
             "phases_ms": {k: round(v[0], 4) for k, v in ph.items()},
             "counters": st,
             "cpu_baseline": cb,

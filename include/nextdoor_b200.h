@@ -188,6 +188,13 @@ int nd_distinct_segments(int device, int32_t *data, int64_t n_segments, int32_t 
                          int32_t invalid, int32_t *counts);
 /* the keyed draw the kernels use, evaluated on the device for n (sample, step, slot, draw) tuples */
 int nd_philox_uniform(int device, uint64_t seed, int64_t n, const uint32_t *tuples4, float *out);
+/* Measurement aid, no counterpart in the reference: the rate (gathers per second) at which this
+ * GPU serves independent random 4-byte gathers from an array of footprint_bytes, n_gathers per
+ * launch, averaged over `repeats` launches after two warm-up launches.  A walk step is a few such
+ * gathers per (transit, sample) pair, so this rate -- not the copy bandwidth -- is the ceiling of
+ * the next() kernels on graphs that do not fit the L2.  Allocates and frees its own array. */
+int nd_probe_random_gather(int device, int64_t footprint_bytes, int64_t n_gathers, int repeats,
+                           double *gathers_per_second);
 
 #ifdef __cplusplus
 }

@@ -53,6 +53,19 @@ void nd_phase_end(nd_sampler *s) {
 
 namespace {
 
+// independent random 4-byte gathers, one per thread and loop trip: the access pattern of a walk step
+__global__ void random_gather_kernel(const int32_t *__restrict__ a, uint64_t words, int64_t total, int32_t *sink, uint32_t salt) {
+  int32_t acc = 0;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t x = (uint32_t)i ^ (salt * 0x9e3779b9u), y = (uint32_t)(i >> 32) + salt;
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    y = (y ^ x) * 0x85ebca6bu; y ^= y >> 13;
+    const uint64_t idx = (((uint64_t)y << 32) | x) % words;
+    acc ^= __ldg(a + idx);
+  }
+  if (acc == 0x5a5a5a5a) *sink = acc;  // never true for the fill pattern: keeps the loads alive
+}
+
 __global__ void philox_uniform_kernel(uint64_t seed, int64_t n, const uint32_t *__restrict__ t4, float *__restrict__ out) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -367,6 +380,39 @@ int nd_distinct_segments(int device, int32_t *data, int64_t n_segments, int32_t 
   if (n_segments == 0) return ND_OK;
   ND_TRY(nd_distinct_launch(nullptr, data, n_segments, seg_len, seg_len, invalid, counts, 1));
   ND_CUDA(cudaDeviceSynchronize());
+  return ND_OK;
+}
+
+int nd_probe_random_gather(int device, int64_t footprint_bytes, int64_t n_gathers, int repeats,
+                           double *gathers_per_second) {
+  ND_REQUIRE(footprint_bytes >= 4 && n_gathers > 0 && repeats > 0 && gathers_per_second, ND_ERR_ARG,
+             "nd_probe_random_gather: bad argument");
+  ND_CUDA(cudaSetDevice(device));
+  NdDeviceInfo dev;
+  ND_TRY(nd_device_info(device, &dev));
+  const uint64_t words = (uint64_t)footprint_bytes / 4;
+  int32_t *a = nullptr, *sink = nullptr;
+  ND_CUDA(cudaMalloc(&a, words * 4));
+  ND_CUDA(cudaMalloc(&sink, 4));
+  ND_CUDA(cudaMemset(a, 1, words * 4));
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  const int64_t blocks = (n_gathers + 255) / 256;
+  const int grid = (int)(blocks < (int64_t)dev.sms * 8 ? blocks : (int64_t)dev.sms * 8);
+  for (int r = 0; r < 2; r++) random_gather_kernel<<<grid, 256>>>(a, words, n_gathers, sink, (uint32_t)r);
+  cudaEventRecord(e0);
+  for (int r = 0; r < repeats; r++) random_gather_kernel<<<grid, 256>>>(a, words, n_gathers, sink, (uint32_t)(r + 2));
+  cudaEventRecord(e1);
+  const cudaError_t err = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(a);
+  cudaFree(sink);
+  ND_REQUIRE(err == cudaSuccess && ms > 0.f, ND_ERR_CUDA, "nd_probe_random_gather: %s", cudaGetErrorString(err));
+  *gathers_per_second = (double)n_gathers * repeats / ((double)ms * 1e-3);
   return ND_OK;
 }
 

@@ -287,12 +287,17 @@ __global__ void init_map_kernel(const int32_t *__restrict__ initial, int32_t V, 
 
 // ---------------------------------------------------------------- transit-parallel next()
 
-constexpr int NEXT_THREADS = 512;
+// node2vec keeps a round of candidates and set buckets in registers: three CTAs per SM (80
+// registers) measured faster than two (116) or four (64, spilling)
+template <int APP>
+constexpr int walk_min_ctas() { return APP == ND_APP_NODE2VEC ? 3 : 1; }
+
+constexpr int NEXT_THREADS = 256;
 
 // One CTA per radix tile of the transit->sample map.  HIST: also count the first radix digit of the
 // new keys (layout and digit as the radix scatter of pass 0 expects them).
 template <int APP, bool HIST>
-__global__ void __launch_bounds__(NEXT_THREADS)
+__global__ void __launch_bounds__(NEXT_THREADS, walk_min_ctas<APP>())
 walk_next_tp_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample, int tile_size,
                     const int32_t *__restrict__ in_key, const int32_t *__restrict__ in_val,
                     const int32_t *__restrict__ d_n, int32_t *__restrict__ out_key,
@@ -369,11 +374,6 @@ constexpr int CNT_SUPER_SHIFT = 12;
 constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_PER_THREAD = CNT_SUPER / SCAN_THREADS;   // 32 consecutive counters per thread
 constexpr int MAX_SMEM_BINS = 8192;                         // coarse bins kept in shared memory (V <= 2^25)
-
-// node2vec keeps a round of candidates and set buckets in registers: three CTAs per SM (80
-// registers) measured faster than two (116) or four (64, spilling)
-template <int APP>
-constexpr int walk_min_ctas() { return APP == ND_APP_NODE2VEC ? 3 : 1; }
 
 template <int APP, bool COUNT>
 __global__ void __launch_bounds__(256, walk_min_ctas<APP>())
@@ -737,7 +737,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     // plain transit-parallel: sort-based inversion, first digit histogram fused into next()
     const NdRadixPlan &pl = s->radix.plan;
     const int64_t tiles = pl.max_tiles;
-    const int grid = (int)(tiles < (int64_t)s->dev.sms * 4 ? tiles : (int64_t)s->dev.sms * 4);
+    const int grid = (int)(tiles < (int64_t)s->dev.sms * 8 ? tiles : (int64_t)s->dev.sms * 8);
     const int32_t *in_key = s->d_init_key, *in_val = s->d_init_val;
     int cur = 0;  // buffer the next kernel writes into
     for (int step = 0; step < steps; step++) {
