@@ -144,6 +144,11 @@ def next_bytes(wl, st, mode):
     return (8 if app == 9 else 4) * st["union_ids"] + 8 * st["union_unique"] + 8 * edges
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the next() kernel, from the ncu captures
+# summarised under profiles/ (bytes; same workload and mode, warm caches)
+NCU_TRAFFIC = {("c2", "tp_lb"): 165.2e6}
+
+
 def gather_ceiling(wl, st, g, next_ms, next_launches, device):
     """The second ceiling of the walk kernels, measured live: next() is a few independent random
     4-byte gathers into the graph arrays per pair, and a GPU serves those at a rate set by the
@@ -199,7 +204,7 @@ def cpu_baseline(hg, wl, seed, budget_s=12.0):
         n = n2
         e, t = run(n)
     return {"value": e / t, "unit": "sampled edges/s", "cores": int(threads), "kind": "reference" if use_ref else "port",
-            "sample": f"first {n} of {S_all} samples, {t:.2f} s"}
+            "sample": f"first {n} of {S_all} samples, {t:.2f} s", "seconds": t}
 
 
 def main():
@@ -239,7 +244,8 @@ def main():
         cb = dict(vals[-1], value=v)
         print(json.dumps({
             "impl": "reference", "metric": "sampled edges/sec", "value": v, "unit": "sampled edges/s", "n_gpus": a.gpus,
-            "steps": a.steps, "warmup": a.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 * float(np.mean([c["seconds"] for c in vals])),
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int32", "data": "synthetic",
             "config": {"workload": f"{a.workload}: {wl['desc']}", "host_graph_build_s": round(t_graph, 2)},
             "cpu_baseline": cb, "e2e": {"value": v, "unit": "sampled edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
@@ -395,7 +401,8 @@ def main():
                 "value": total_edges * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",
                 "collective": "ncclAllGather of the final samples", "bytes_per_rank_per_step": int(S * fs * 4)},
             "roofline": {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
+                         "traffic": NCU_TRAFFIC.get((a.workload, a.mode)),
                          "launches": next_launches, "avg_launch_us": 1e3 * next_ms / max(next_launches, 1),
                          "algorithmic_bytes_per_pass": nb, "random_gather": gather},
             "phases_ms": {k: round(v[0], 4) for k, v in ph.items()},
