@@ -48,7 +48,8 @@ WORKLOADS = {
 }
 APP_NAMES = {0: "uniform_walk", 1: "deepwalk", 2: "ppr", 3: "node2vec", 4: "khop", 5: "khop_distinct", 8: "fastgcn_is", 9: "ladies_is"}
 MODES = {"tp": 0, "tp_lb": 1, "sp": 2}
-E2E_CHUNKS = 2   # the per-step kernels are latency-bound at these sizes: finer chunks cost more than the overlap gains
+E2E_CHUNKS = 1   # the per-step kernels are latency-bound at these sizes: cutting a job costs more than it gains;
+E2E_DEPTH = 2    # instead two sampler sets alternate, so a job's result copy runs under the next job's sampling
 
 
 def peaks():
@@ -312,23 +313,27 @@ def main():
         ms_sp = s0.elapsed_time(s1)
 
     # ---- end to end through the public API with host buffers: seeds H2D from pinned memory,
-    # sample, result D2H into pinned memory.  The job runs as E2E_CHUNKS seed-range chunks
-    # (nextdoor_b200.api.PipelinedSampler): a finished chunk is copied on a second stream while the next one is sampled.
+    # sample, result D2H into pinned memory, through nextdoor_b200.api.PipelinedSampler: the result of a
+    # step is copied on a second stream while the next step is sampled (two sampler sets alternate).
     init_host = torch.from_numpy(init_np).pin_memory()
     out_host = torch.empty(S * fs, dtype=torch.int32).pin_memory()
-    init_pin, out_pin = init_host.numpy(), out_host.numpy()
+    out_host2 = torch.empty(S * fs, dtype=torch.int32).pin_memory()   # consecutive steps land in alternating buffers
+    init_pin, out_pin, out_pin2 = init_host.numpy(), out_host.numpy(), out_host2.numpy()
     copy_stream = torch.cuda.Stream()
-    pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init_np, chunks=E2E_CHUNKS,
+    pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init_np, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
                                stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream)
     for _ in range(2):
         pipe.run(init_pin, out_pin, mode)
     barrier()
     x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     x0.record(stream)
-    for _ in range(a.steps):
-        pipe.run(init_pin, out_pin, mode)     # returns when every chunk has landed in out_pin
+    for i in range(a.steps):                  # step i+1 starts sampling while the tail of step i is being copied
+        pipe.run_async(init_pin, out_pin if i % 2 == 0 else out_pin2, mode)
+    pipe.wait()                               # every step's result has landed on the host
     x1.record(stream)
     barrier()
+    if a.steps % 2 == 0:
+        out_pin = out_pin2                    # the buffer the last step wrote
     clocks.stop_flag = True
     ms_e2e = x0.elapsed_time(x1)
     e2e_check = int((out_pin != V).sum()) if wl["kind"] != COLL else None
@@ -393,7 +398,7 @@ def main():
                        "sampled_edges_per_step_per_gpu": edges_step},
             "e2e": {"value": total_edges * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
                     "h2d_bytes_per_step": int(init_np.nbytes), "d2h_bytes_per_step": int(S * fs * 4),
-                    "chunks": E2E_CHUNKS, "valid_vertices_in_host_result": e2e_check},
+                    "chunks": E2E_CHUNKS, "depth": E2E_DEPTH, "valid_vertices_in_host_result": e2e_check},
             "gpu_launches": int(launches),
             "sample_parallel": None if mode == 2 else {"value": total_edges * a.steps / (ms_sp * 1e-3), "unit": "sampled edges/s",
                                                        "note": "same sampler, same samples, nd_mode SampleParallel"},

@@ -248,27 +248,47 @@ class PipelinedSampler:
     replay its CUDA graph)."""
 
     def __init__(self, graph: Graph, params: AppParams, num_samples, first_sample=0, initial=None, chunks=4,
-                 stream=None, copy_stream=None):
+                 stream=None, copy_stream=None, depth=1):
+        """depth > 1 keeps that many independent sets of samplers (own result buffers) and rotates
+        through them job by job, so with run_async() a whole job's copy overlaps the next job's
+        sampling even with chunks=1 (no small-launch penalty from cutting the job)."""
         self.S, self.fs, self.isz = int(num_samples), final_sample_size(params), initial_sample_size(params)
         self.device, self.copy_stream = graph.device, copy_stream
-        self.parts = []
-        for c in range(chunks):
-            f, n = shard_range(self.S, c, chunks)
-            init = None if initial is None else np.ascontiguousarray(initial[f * self.isz:(f + n) * self.isz], np.int32)
-            smp = Sampler(graph, params, num_samples=n, first_sample=first_sample + f, initial=init)
-            if stream is not None:
-                smp.set_stream(stream)
-            self.parts.append((f, n, smp))
+        self.sets, self._job = [], 0
+        for _ in range(max(1, depth)):
+            parts = []
+            for c in range(chunks):
+                f, n = shard_range(self.S, c, chunks)
+                init = None if initial is None else np.ascontiguousarray(initial[f * self.isz:(f + n) * self.isz], np.int32)
+                smp = Sampler(graph, params, num_samples=n, first_sample=first_sample + f, initial=init)
+                if stream is not None:
+                    smp.set_stream(stream)
+                parts.append((f, n, smp))
+            self.sets.append(parts)
+        self.parts = self.sets[0]
 
     def run(self, initial_host, out_host, mode=MODE_TRANSIT_PARALLEL_LB):
         """initial_host / out_host: (pinned) numpy int32 arrays of the whole job; returns after everything landed."""
+        self.run_async(initial_host, out_host, mode)
+        self.wait()
+
+    def run_async(self, initial_host, out_host, mode=MODE_TRANSIT_PARALLEL_LB):
+        """Enqueue one job and return.  Jobs enqueued back to back overlap: a chunk of the next
+        job is sampled while the last chunk of this one is still on its way to the host (the
+        library orders a chunk's next sampling after its own pending copy).  Give consecutive
+        jobs different `out_host` buffers and call wait() before reading them."""
+        self.parts = self.sets[self._job % len(self.sets)]
+        self._job += 1
         for f, n, smp in self.parts:
             if initial_host is not None:
                 smp.set_initial(initial_host[f * self.isz:(f + n) * self.isz])
             smp.sample(mode, sync=False)
             smp.final_samples_async(out_host[f * self.fs:(f + n) * self.fs], self.copy_stream)
-        for _, _, smp in self.parts:
-            smp.sync()
+
+    def wait(self):
+        for parts in self.sets:
+            for _, _, smp in parts:
+                smp.sync()
         if self.copy_stream:
             check(lib.nd_stream_sync(self.device, C.c_void_p(self.copy_stream)))
 
@@ -280,8 +300,9 @@ class PipelinedSampler:
         return tot
 
     def free(self):
-        for _, _, smp in self.parts:
-            smp.free()
+        for parts in self.sets:
+            for _, _, smp in parts:
+                smp.free()
 
 
 class SamplingModule:

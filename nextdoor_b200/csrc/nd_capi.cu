@@ -96,6 +96,7 @@ void free_sampler(nd_sampler *s) {
   for (int i = 0; i < 2; i++) { cudaFree(s->d_lb_key[i]); cudaFree(s->d_prev[i]); }
   for (int i = 0; i < 3; i++) if (s->graph_exec[i]) cudaGraphExecDestroy(s->graph_exec[i]);
   if (s->copy_event) cudaEventDestroy(s->copy_event);
+  if (s->copy_done) cudaEventDestroy(s->copy_done);
   nd_radix_scratch_free(&s->radix);
   for (cudaEvent_t e : s->timer.ev) cudaEventDestroy(e);
   delete s;
@@ -228,6 +229,10 @@ int nd_sampler_sample(nd_sampler *s, int mode) {
   }
   s->sampled = true;
   if (s->S == 0) return ND_OK;
+  if (s->copy_pending) {  // a result copy on another stream still reads the buffers this job overwrites
+    ND_CUDA(cudaStreamWaitEvent(s->stream, s->copy_done, 0));
+    s->copy_pending = false;
+  }
   if (nd_is_walk(s->p.app)) return nd_walk_sample(s, mode);
   if (nd_is_khop(s->p.app)) return nd_khop_sample(s, mode);
   return nd_collective_sample(s, mode);
@@ -268,6 +273,11 @@ int nd_sampler_final_samples_async(nd_sampler *s, int32_t *out, void *copy_strea
     ND_CUDA(cudaStreamWaitEvent(cs, s->copy_event, 0));
   }
   if (s->S > 0) ND_CUDA(cudaMemcpyAsync(out, s->d_out, sizeof(int32_t) * (size_t)s->S * s->fs, cudaMemcpyDeviceToHost, cs));
+  if (cs != s->stream) {
+    if (!s->copy_done) ND_CUDA(cudaEventCreateWithFlags(&s->copy_done, cudaEventDisableTiming));
+    ND_CUDA(cudaEventRecord(s->copy_done, cs));
+    s->copy_pending = true;
+  }
   return ND_OK;
 }
 

@@ -177,6 +177,8 @@ struct nd_sampler {
   int graph_launches[3] = {0, 0, 0};
   bool graph_off = false;
   cudaEvent_t copy_event = nullptr;  // orders a result copy on another stream after the sampling
+  cudaEvent_t copy_done = nullptr;   // ... and the next sampling (which overwrites the result) after that copy
+  bool copy_pending = false;
   // k-hop LB bins
   int32_t *d_runs = nullptr;      // work lists
   int64_t runs_cap = 0;

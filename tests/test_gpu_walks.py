@@ -169,3 +169,25 @@ def test_pipelined_sampler_equals_single_sampler(nd, ndo, small_graph):
         pipe.run(init_pin, out_pin, mode)
         assert np.array_equal(out_pin.reshape(S, 40), exp["out"])
     assert pipe.stats()["sampled_edges"] == exp["counters"]["sampled_edges"]
+
+
+def test_pipelined_jobs_back_to_back(nd, ndo, small_graph):
+    """Jobs enqueued without waiting in between (the next job samples while the previous one's
+    last chunk is still copied) land complete and unmixed in their own host buffers."""
+    import torch
+    g = _graph(nd, small_graph)
+    pr = nd.app_params(3, steps=40, seed=12, p=2.0, q=0.5)
+    opr = ndo.make_params(3, steps=40, seed=12, p=2.0, q=0.5)
+    S, first = 20_001, 5
+    st, cst = torch.cuda.Stream(), torch.cuda.Stream()
+    inits = [((np.arange(first, first + S) * k) % small_graph.V).astype(np.int32) for k in (1, 3, 7, 11)]
+    pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=inits[0], chunks=2, stream=st.cuda_stream,
+                               copy_stream=cst.cuda_stream)
+    pins = [torch.from_numpy(i).pin_memory().numpy() for i in inits]
+    outs = [torch.full((S * 40,), -7, dtype=torch.int32).pin_memory().numpy() for _ in inits]
+    for ip, op in zip(pins, outs):
+        pipe.run_async(ip, op, 1)
+    pipe.wait()
+    for i, op in zip(inits, outs):
+        exp = ndo.sample(small_graph, opr, S, first=first, initial=i)
+        assert np.array_equal(op.reshape(S, 40), exp["out"])
