@@ -29,6 +29,7 @@
 #include <sstream>
 #include <string>
 #include <vector>
+#include <assert.h>
 
 #include "nextdoor_b200.h"
 
@@ -101,7 +102,27 @@ __host__ __device__ inline bool binarySearch(F &array, T x, int size) {
   }
   return false;
 }
+// is_cuda_error / printCudaMemInfo (src/utils.hpp:16-30, 352-357)
+inline bool is_cuda_error(cudaError_t status, int line) {
+  if (status != cudaSuccess) {
+    printf("CUDA error at line %d: %s\n", line, cudaGetErrorString(status));
+    return true;
+  }
+  return false;
+}
+inline void printCudaMemInfo() {
+  size_t free_b = 0, total_b = 0;
+  if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) printf("free memory %ld\n", (long)free_b);
+}
 }  // namespace utils
+using namespace utils;  // src/nextdoor.cu:40
+
+#ifndef DIVUP
+#define DIVUP(x, y) (((x) + ((y) - 1)) / (y))  // src/utils.hpp:12
+#endif
+#ifndef CHK_CU
+#define CHK_CU(x) if (utils::is_cuda_error((x), __LINE__) == true) { assert(false); }  // src/utils.hpp:16
+#endif
 
 // ------------------------------------------------------------------ graph types the App bodies see
 
@@ -240,10 +261,16 @@ int getFinalSampleSize() {
 namespace ndc {
 
 template <typename App>
-__host__ __device__ inline int pairs_per_sample(int step) {  // transits of a sample entering `step`
+__host__ __device__ inline int pairs_per_sample(int step, int isz = 1) {  // transits of a sample entering `step`
   if (App().samplingType() == CollectiveNeighborhood) return 1;
-  int n = 1;
+  int n = isz;  // individual-neighbourhood apps may start from several vertices (MVS, ClusterGCN: 32)
   for (int k = 0; k < step; k++) n *= App().stepSize(k);
+  return n;
+}
+template <typename App>
+__host__ __device__ inline int hop_size(int step) {  // slots hop `step` has in a sample's row (getFinalSampleSize)
+  int n = 1;
+  for (int k = 0; k <= step; k++) n *= App().stepSize(k);
   return n;
 }
 template <typename App>
@@ -262,14 +289,14 @@ template <class SampleType, typename App, bool FROM_MAP>
 __global__ void step_kernel(CSRPartition part, int step, uint64_t seed, int64_t first_sample, int64_t n_pairs,
                             const VertexID_t *in_key, const VertexID_t *in_val, const VertexID_t *initial,
                             SampleType *samples, VertexID_t *out, int fs, VertexID_t *mkey, VertexID_t *mval,
-                            bool write_map, const VertexID_t *explicit_prev) {
+                            bool write_map, const VertexID_t *explicit_prev, int isz) {
   const int f = App().stepSize(step);
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (tid >= n_pairs * f) return;
   const int64_t i = tid / f;
   const int j = (int)(tid - i * f);
   const int32_t INV = part.get_n_vertices();
-  const int n_prev = pairs_per_sample<App>(step);
+  const int n_prev = pairs_per_sample<App>(step, isz);
   VertexID_t q, transit;
   if (FROM_MAP) { transit = in_key[i]; q = in_val[i]; }
   else {
@@ -277,7 +304,7 @@ __global__ void step_kernel(CSRPartition part, int step, uint64_t seed, int64_t 
     const int64_t s = q / n_prev;
     // apps with explicit transits walk from what stepTransits returned at the previous step
     // (kept per pair id), the others from the vertex sampled at the previous hop
-    if (step == 0) transit = initial[s];
+    if (step == 0) transit = initial[q];  // q = s * isz + index inside the initial sample
     else if (explicit_prev) transit = explicit_prev[q];
     else transit = out[s * fs + prefix_of<App>(step - 1) + (q - s * n_prev)];
   }
@@ -296,15 +323,35 @@ __global__ void step_kernel(CSRPartition part, int step, uint64_t seed, int64_t 
           step, &part, &transit, (VertexID)(first_sample + s), &samples[s], part.get_max_weight(transit), edges, weights, n, j, &rng);
     }
   }
-  out[s * fs + prefix_of<App>(step) + slot] = nbr != -1 ? nbr : INV;
-  if (write_map) {
-    VertexID_t key = nbr;
-    if (App().hasExplicitTransits())
-      key = App().template stepTransits<SampleType>(step + 1, (VertexID_t)(first_sample + s), samples[s], slot, &rng);
+  // with several initial vertices a hop has more (pair, slot) combinations than slots in the row
+  // (the reference sizes the row without them, src/nextdoor.cu:1914-1929): those are not stored
+  if (slot < hop_size<App>(step)) out[s * fs + prefix_of<App>(step) + slot] = nbr != -1 ? nbr : INV;
+  if (write_map) {  // apps with explicit transits get their keys from transits_kernel instead
     const int64_t c = (int64_t)q * f + j;
-    mkey[c] = key != -1 ? key : INV;
+    mkey[c] = nbr != -1 ? nbr : INV;
     mval[c] = (VertexID_t)c;
   }
+}
+
+// Explicit transits (hasExplicitTransits / stepTransits, src/nextdoor.cu:1285-1323): the transit of
+// every (sample, index) pair of the next step, computed by a kernel of its own AFTER the step's
+// next() calls have all finished -- apps such as ClusterGCN read in stepTransits() what next()
+// accumulated in the sample.  The draws of stepTransits come from the pair's keyed stream at an
+// offset no next() reaches.
+constexpr uint32_t NDC_TRANSIT_DRAW_BASE = 1u << 16;
+template <class SampleType, typename App>
+__global__ void transits_kernel(int next_step, uint64_t seed, int64_t first_sample, int64_t total, int per_sample,
+                                SampleType *samples, VertexID_t *mkey, VertexID_t *mval, VertexID_t INV) {
+  const int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (c >= total) return;
+  const int64_t s = c / per_sample;
+  const int slot = (int)(c - s * per_sample);
+  nd_rng rng;
+  rng.seed = seed; rng.sample = (uint32_t)(first_sample + s); rng.step = (uint32_t)(next_step - 1); rng.slot = (uint32_t)slot;
+  rng.draw = NDC_TRANSIT_DRAW_BASE;
+  const VertexID_t key = App().template stepTransits<SampleType>(next_step, (VertexID_t)(first_sample + s), samples[s], slot, &rng);
+  mkey[c] = key != -1 ? key : INV;
+  mval[c] = (VertexID_t)c;
 }
 
 // Collective apps: one thread per (sample, slot); the transits are the sample's previous layer
@@ -391,8 +438,8 @@ bool allocNextDoorDataOnGPU(CSR *csr, NextDoorData<SampleType, App> &data) {
   data.samples.clear(); data.initialContents.clear(); data.initialTransitToSampleValues.clear();
   const EdgePos_t isz = App().initialSampleSize(csr);
   const int64_t S = App().numSamples(csr);
-  if (App().samplingType() == IndividualNeighborhood && isz != 1) {
-    printf("initialSampleSize '%d' > 1 is only supported for CollectiveNeighborhood apps\n", isz);
+  if (App().samplingType() == IndividualNeighborhood && isz != 1 && App().steps() > 1 && !App().hasExplicitTransits()) {
+    printf("initialSampleSize '%d' > 1 with several steps needs hasExplicitTransits() for IndividualNeighborhood apps\n", isz);
     return false;
   }
   for (int step = 0; step < App().steps(); step++)
@@ -411,7 +458,7 @@ bool allocNextDoorDataOnGPU(CSR *csr, NextDoorData<SampleType, App> &data) {
   data.maxBits = 0;
   while ((data.INVALID_VERTEX >> data.maxBits) != 0) data.maxBits++;
   data.hFinalSamples.assign((size_t)fs * S, data.INVALID_VERTEX);
-  size_t max_pairs = 1;  // pairs per sample at the widest step that still feeds a map
+  size_t max_pairs = App().samplingType() == IndividualNeighborhood ? (size_t)isz : 1;  // pairs per sample at the widest step that still feeds a map
   for (int step = 0; step + 1 < App().steps(); step++) max_pairs *= App().stepSize(step);
   const int P = (int)data.devices.size();
   data.dOutputSamples.assign(P, nullptr); data.dFinalSamples.assign(P, nullptr); data.dInitialSamples.assign(P, nullptr);
@@ -483,23 +530,24 @@ bool run(CSR *csr, NextDoorData<SampleType, App> &data, bool transit_parallel) {
       NDC_CHECK(cudaDeviceSynchronize());
       continue;
     }
-    int64_t n_pairs = n;       // live pairs of the current step (transit-parallel) / all pairs (sample-parallel)
+    const int64_t n0 = n * isz;   // initial pairs: every vertex of every initial sample
+    int64_t n_pairs = n0;      // live pairs of the current step (transit-parallel) / all pairs (sample-parallel)
     int cur = 0;
     const VertexID_t *in_key = nullptr, *in_val = nullptr;
     if (transit_parallel) {   // initial transit -> sample map, sorted by transit
       VertexID_t *k0 = data.dMapKeys[0][d], *v0 = data.dMapVals[0][d];
-      NDC_CHECK(cudaMemcpy(k0, data.initialContents.data() + first, sizeof(VertexID_t) * (size_t)n, cudaMemcpyHostToDevice));
-      std::vector<VertexID_t> ids((size_t)n);
-      for (int64_t i = 0; i < n; i++) ids[(size_t)i] = (VertexID_t)i;
-      NDC_CHECK(cudaMemcpy(v0, ids.data(), sizeof(VertexID_t) * (size_t)n, cudaMemcpyHostToDevice));
-      if (nd_invert_map(data.devices[d], n, k0, v0, INV, data.dMapKeys[1][d], data.dMapVals[1][d], &n_pairs) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }
+      NDC_CHECK(cudaMemcpy(k0, data.initialContents.data() + first * isz, sizeof(VertexID_t) * (size_t)n0, cudaMemcpyHostToDevice));
+      std::vector<VertexID_t> ids((size_t)n0);
+      for (int64_t i = 0; i < n0; i++) ids[(size_t)i] = (VertexID_t)i;
+      NDC_CHECK(cudaMemcpy(v0, ids.data(), sizeof(VertexID_t) * (size_t)n0, cudaMemcpyHostToDevice));
+      if (nd_invert_map(data.devices[d], n0, k0, v0, INV, data.dMapKeys[1][d], data.dMapVals[1][d], &n_pairs) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }
       in_key = data.dMapKeys[1][d]; in_val = data.dMapVals[1][d];
       cur = 0;
     }
     for (int step = 0; step < App().steps(); step++) {
       const bool last = step == App().steps() - 1;
       const int f = App().stepSize(step);
-      const int64_t full_pairs = n * pairs_per_sample<App>(step);
+      const int64_t full_pairs = n * pairs_per_sample<App>(step, isz);
       const int64_t pairs = transit_parallel ? n_pairs : full_pairs;
       const bool explicit_tr = App().hasExplicitTransits();
       const bool write_map = (transit_parallel || explicit_tr) && !last;
@@ -510,8 +558,13 @@ bool run(CSR *csr, NextDoorData<SampleType, App> &data, bool transit_parallel) {
       if (write_map) fill_kernel<VertexID_t><<<(unsigned)((full_pairs * f + 255) / 256), 256>>>(mk, full_pairs * f, INV);
       const int64_t threads = pairs * f;
       if (threads > 0) {
-        if (transit_parallel) step_kernel<SampleType, App, true><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, in_key, in_val, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, nullptr);
-        else step_kernel<SampleType, App, false><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, nullptr, nullptr, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, explicit_prev);
+        if (transit_parallel) step_kernel<SampleType, App, true><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, in_key, in_val, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, nullptr, isz);
+        else step_kernel<SampleType, App, false><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, nullptr, nullptr, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, explicit_prev, isz);
+      }
+      if (write_map && explicit_tr) {
+        const int64_t total = full_pairs * f;
+        transits_kernel<SampleType, App><<<(unsigned)((total + 255) / 256), 256>>>(step + 1, nextdoor_seed(), first, total, (int)(total / n),
+                                                                                  data.dOutputSamples[d], mk, mv, INV);
       }
       NDC_CHECK(cudaGetLastError());
       if (write_map && transit_parallel) {  // the map inversion of the step loop (src/nextdoor.cu:2924-2939)

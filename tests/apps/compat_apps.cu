@@ -173,6 +173,17 @@ struct OwnTeleportWalk : WalkBase {
 #include "apps/multiRW/multiRW.cu"
 #undef VERTICES_PER_SAMPLE
 #include "apps/layer/layerSampling.cu"
+// The two subgraph apps keep file-scope globals with the same names (dRowStorage, dColStorage, foo):
+// each gets a namespace of its own.
+#undef VERTICES_PER_SAMPLE
+namespace ref_mvs {
+#include "apps/mvs/mvsSampling.cu"
+}
+#undef VERTICES_PER_SAMPLE
+namespace ref_cluster {
+#include "apps/clustergcn/clusterGCNSampling.cu"
+}
+#undef VERTICES_PER_SAMPLE
 #endif
 
 // ---------------------------------------------------------------- runners
@@ -231,6 +242,92 @@ extern "C" int ndc_run(int which, const char *file, const char *kernel, int lb, 
     default: return -1;
   }
 }
+
+#ifdef NDC_WITH_REFERENCE
+// The reference's MVS app (src/apps/mvs/mvsSampling.cu) driven as its own test does
+// (src/tests/multiGPU/mvs.cu:116-167): COO side buffers allocated by the caller, every sample
+// appends the edges of its 32 batch vertices.  Returns the buffers and the per-sample records.
+extern "C" int ndc_run_mvs(const char *file, const char *kernel, int lb, int64_t cap, int32_t *rows, int32_t *cols,
+                           int64_t max_samples, int32_t *pos, int32_t *len, int32_t *vertices, int64_t *n_samples) {
+  using namespace ref_mvs;
+  Graph graph;
+  CSR *csr = loadGraph(graph, (char *)file, (char *)"edge-list", (char *)"binary");
+  if (!csr) return 1;
+  const int64_t S = MVSSamplingApp().numSamples(csr);
+  const int64_t storage = (int64_t)graph.get_n_edges() * DIVUP(S * 32, csr->get_n_vertices());
+  if (storage > cap || S > max_samples) return 4;
+  storagePosition = 0;
+  cudaMalloc(&dRowStorage, sizeof(VertexID_t) * storage);
+  cudaMalloc(&dColStorage, sizeof(VertexID_t) * storage);
+  NextDoorData<MVSSample, MVSSamplingApp> data;
+  data.csr = csr;
+  data.gpuCSRPartitions = transferCSRToGPUs(data, csr);
+  if (!allocNextDoorDataOnGPU<MVSSample, MVSSamplingApp>(csr, data)) return 2;
+  if (data.gpuCSRPartitions.empty()) data.gpuCSRPartitions = transferCSRToGPUs(data, csr);
+  bool ok = strcmp(kernel, "SampleParallel") == 0 ? doSampleParallelSampling<MVSSample, MVSSamplingApp>(csr, data)
+                                                  : doTransitParallelSampling<MVSSample, MVSSamplingApp>(csr, data, lb != 0);
+  if (!ok) return 3;
+  getFinalSamples(data);
+  cudaMemcpy(rows, dRowStorage, sizeof(int32_t) * storage, cudaMemcpyDeviceToHost);
+  cudaMemcpy(cols, dColStorage, sizeof(int32_t) * storage, cudaMemcpyDeviceToHost);
+  *n_samples = (int64_t)data.samples.size();
+  for (size_t i = 0; i < data.samples.size(); i++) {
+    pos[i] = data.samples[i].posInStorage;
+    len[i] = data.samples[i].length;
+    memcpy(vertices + i * 32, data.samples[i].vertices, sizeof(int32_t) * 32);
+  }
+  cudaFree(dRowStorage);
+  cudaFree(dColStorage);
+  freeDeviceData(data);
+  delete csr;
+  return 0;
+}
+
+// The reference's ClusterGCN app (src/apps/clustergcn/clusterGCNSampling.cu), set up as its foo()
+// does (:141-208): clusters of 16 consecutive vertices, two clusters per sample, the induced
+// subgraph of a sample appended to the COO buffers at a position claimed in stepTransits().
+extern "C" int ndc_run_cluster(const char *file, const char *kernel, int lb, int64_t cap, int32_t *rows, int32_t *cols,
+                               int64_t max_samples, int32_t *pos, int32_t *len, int32_t *vertices, int64_t *n_samples) {
+  using namespace ref_cluster;
+  Graph graph;
+  CSR *csr = loadGraph(graph, (char *)file, (char *)"edge-list", (char *)"binary");
+  if (!csr) return 1;
+  clusters = std::vector<std::vector<VertexID_t>>(csr->get_n_vertices() / VERTICES_IN_CLUSTERS);
+  for (int c = 0; c < (int)clusters.size(); c++)
+    for (int v = 0; v < VERTICES_IN_CLUSTERS; v++) clusters[c].push_back(c * VERTICES_IN_CLUSTERS + v);
+  const int64_t S = SubGraphSamplingAppI().numSamples(csr);
+  const int64_t storage = (int64_t)graph.get_n_edges() * DIVUP(S * 32, csr->get_n_vertices());
+  if (storage > cap || S > max_samples) return 4;
+  NextDoorData<SubGraphSample, SubGraphSamplingAppI> data;
+  data.devices = {0};
+  data.csr = csr;
+  data.gpuCSRPartitions = transferCSRToGPUs(data, csr);
+  cudaMalloc(&dAdjMatrixTotalLen, sizeof(int));
+  cudaMemset(dAdjMatrixTotalLen, 0, sizeof(int));
+  cudaMalloc(&dRowStorage, sizeof(VertexID_t) * storage);
+  cudaMalloc(&dColStorage, sizeof(VertexID_t) * storage);
+  if (!allocNextDoorDataOnGPU<SubGraphSample, SubGraphSamplingAppI>(csr, data)) return 2;
+  if (data.gpuCSRPartitions.empty()) data.gpuCSRPartitions = transferCSRToGPUs(data, csr);
+  bool ok = strcmp(kernel, "SampleParallel") == 0 ? doSampleParallelSampling<SubGraphSample, SubGraphSamplingAppI>(csr, data)
+                                                  : doTransitParallelSampling<SubGraphSample, SubGraphSamplingAppI>(csr, data, lb != 0);
+  if (!ok) return 3;
+  getFinalSamples(data);
+  cudaMemcpy(rows, dRowStorage, sizeof(int32_t) * storage, cudaMemcpyDeviceToHost);
+  cudaMemcpy(cols, dColStorage, sizeof(int32_t) * storage, cudaMemcpyDeviceToHost);
+  *n_samples = (int64_t)data.samples.size();
+  for (size_t i = 0; i < data.samples.size(); i++) {
+    pos[i] = data.samples[i].adjMatrixPos;
+    len[i] = data.samples[i].adjacencyMatrixLen;
+    memcpy(vertices + i * 32, data.samples[i].vertices, sizeof(int32_t) * 32);
+  }
+  cudaFree(dRowStorage);
+  cudaFree(dColStorage);
+  cudaFree(dAdjMatrixTotalLen);
+  freeDeviceData(data);
+  delete csr;
+  return 0;
+}
+#endif
 
 extern "C" int ndc_has_reference_apps(void) {
 #ifdef NDC_WITH_REFERENCE

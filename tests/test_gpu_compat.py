@@ -89,8 +89,8 @@ def test_explicit_transits_app(ndo, world, kernel, lb):
                 if step > 0:
                     roots[last] = v
                 exp[s, step] = v
-            if step < steps - 1:
-                last = ri(u(0, s, step, 0, draw), 4)
+            if step < steps - 1:   # stepTransits draws from the pair's stream at a fixed offset (1 << 16)
+                last = ri(u(0, s, step, 0, 1 << 16), 4)
                 transit = roots[last]
     assert np.array_equal(got, exp)
 
@@ -150,3 +150,59 @@ def test_app_main_command_line(ndo, world, capfd):
     bad = [b"app", b"-g", b"/nonexistent.bin", b"-t", b"edge-list", b"-f", b"binary"]
     assert L.ndc_app_main(len(bad), (C.c_char_p * len(bad))(*bad)) == 0
     assert "not found" in capfd.readouterr().out
+
+
+def _run_subgraph(L, fn, path, kernel, lb, hg):
+    """Runs one of the reference's two subgraph apps and returns, per sample, its 32 vertices and
+    the (row, col) pairs it appended to the COO side buffers."""
+    f = getattr(L, fn)
+    f.restype = C.c_int
+    f.argtypes = [C.c_char_p, C.c_char_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                  C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+    max_s = hg.V  # both apps take about V/4 samples
+    cap = int(hg.E) * 9
+    rows, cols = np.full(cap, -1, np.int32), np.full(cap, -1, np.int32)
+    pos, ln, verts = np.zeros(max_s, np.int32), np.zeros(max_s, np.int32), np.zeros(max_s * 32, np.int32)
+    n = C.c_int64(0)
+    rc = f(path.encode(), kernel.encode(), lb, cap, rows.ctypes.data, cols.ctypes.data, max_s, pos.ctypes.data,
+           ln.ctypes.data, verts.ctypes.data, C.byref(n))
+    assert rc == 0, f"{fn} failed with {rc}"
+    S = n.value
+    return S, verts[:S * 32].reshape(S, 32), [(rows[pos[i]:pos[i] + ln[i]], cols[pos[i]:pos[i] + ln[i]]) for i in range(S)]
+
+
+@pytest.mark.skipif(not os.path.exists(WITH_REF), reason="built without the reference tree")
+@pytest.mark.parametrize("kernel,lb", KERNELS)
+def test_reference_mvs_app(world, kernel, lb):
+    """src/apps/mvs/mvsSampling.cu compiled unchanged: every sample collects exactly the edges of
+    its 32 batch vertices (what the reference's own checker, src/tests/multiGPU/mvs.cu:11-110, asks)."""
+    path, hg = world
+    L = C.CDLL(WITH_REF)
+    S, verts, coo = _run_subgraph(L, "ndc_run_mvs", path, kernel, lb, hg)
+    assert S == min(1500000, (hg.V * 8 + 31) // 32)
+    for s in range(S):
+        assert np.array_equal(verts[s], (s * 32 + np.arange(32)) % hg.V)
+        exp = sorted((int(v), int(c)) for v in verts[s] for c in hg.col[hg.row_ptr[v]:hg.row_ptr[v + 1]])
+        got = sorted(zip(coo[s][0].tolist(), coo[s][1].tolist()))
+        assert got == exp, f"sample {s}"
+
+
+@pytest.mark.skipif(not os.path.exists(WITH_REF), reason="built without the reference tree")
+@pytest.mark.parametrize("kernel,lb", KERNELS)
+def test_reference_clustergcn_app(world, kernel, lb):
+    """src/apps/clustergcn/clusterGCNSampling.cu compiled unchanged (explicit transits, positions
+    claimed with atomics in stepTransits): every sample holds the subgraph induced by its two
+    clusters of 16 vertices, one entry per (v1, v2) pair that is an edge."""
+    path, hg = world
+    L = C.CDLL(WITH_REF)
+    S, verts, coo = _run_subgraph(L, "ndc_run_cluster", path, kernel, lb, hg)
+    n_clusters = hg.V // 16
+    assert S == min(2000000, (hg.V * 8 + 31) // 32)
+    spans = []
+    for s in range(S):
+        cl = [(s * 2 + i) % n_clusters for i in range(2)]
+        assert np.array_equal(verts[s], np.concatenate([c * 16 + np.arange(16) for c in cl]))
+        exp = sorted((int(v1), int(v2)) for v1 in verts[s] for v2 in verts[s]
+                     if v2 in set(hg.col[hg.row_ptr[v1]:hg.row_ptr[v1 + 1]].tolist()))
+        got = sorted(zip(coo[s][0].tolist(), coo[s][1].tolist()))
+        assert got == exp, f"sample {s}"
