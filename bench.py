@@ -186,16 +186,18 @@ def cpu_baseline(hg, wl, seed, budget_s=12.0):
     use_ref = ndo.ref_available() and wl["kind"] == WALK and not (app == 2 and abs(wl.get("stop_prob", 0.01) - 0.01) > 1e-9)
     use_ref = use_ref or (ndo.ref_available() and app == 4 and wl["fanout"] == [25, 10])
     pr = params_for(ndo, wl, seed)
-    threads = ndo.ref().ref_max_threads() if use_ref else ndo.lib().ndo_max_threads()
+    # all host cores this process may run on, set explicitly: launchers such as torchrun export
+    # OMP_NUM_THREADS=1 to their ranks, which would silently make this a one-thread baseline
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     S_all = wl.get("S", wl["V"])
 
     def run(n):
         init = seeds_for(wl, 0, n)
         t0 = time.perf_counter()
         if use_ref:
-            e = ndo.ref_sample(hg, app, pr.steps, n, seed=seed, initial=init)["sampled_edges"]
+            e = ndo.ref_sample(hg, app, pr.steps, n, seed=seed, initial=init, threads=threads)["sampled_edges"]
         else:
-            e = ndo.sample(hg, pr, n, initial=init, want_adj=False)["counters"]["sampled_edges"]
+            e = ndo.sample(hg, pr, n, initial=init, want_adj=False, threads=threads)["counters"]["sampled_edges"]
         return e, time.perf_counter() - t0
 
     n = max(1, min(S_all, 20000 if wl["kind"] == WALK else (2000 if wl["kind"] == KHOP else 8)))
