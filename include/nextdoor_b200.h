@@ -188,6 +188,17 @@ int nd_distinct_segments(int device, int32_t *data, int64_t n_segments, int32_t 
                          int32_t invalid, int32_t *counts);
 /* the keyed draw the kernels use, evaluated on the device for n (sample, step, slot, draw) tuples */
 int nd_philox_uniform(int device, uint64_t seed, int64_t n, const uint32_t *tuples4, float *out);
+/* One next() of a walk application (uniform walk, DeepWalk, PPR) for n explicit (transit, sample)
+ * pairs: the transit-parallel next() kernel (samplingKernel, src/nextdoor.cu:212-336) as an
+ * operator.  d_transits[n] int32, d_samples[n] int64 (GLOBAL sample ids: the draws are keyed by
+ * them) and d_next[n] int32 are DEVICE pointers; d_next[i] = the sampled neighbour, or -1 (no
+ * edges, walk ended, transit outside [0, V)).  Enqueued on `stream`, no synchronisation.  With a
+ * graph that holds only the rows of one vertex range (other rows empty) this is the per-step
+ * building block of sampling over a graph partitioned across GPUs -- the use the reference's
+ * CSR partitioner was written for (src/graph_partitioner.cuh:1-173; the multi-GPU partitioned
+ * path itself is a stub there, ENABLE_GRAPH_PARTITION_FOR_GLOBAL_MEM, src/csr.hpp:371-374). */
+int nd_walk_step(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const int32_t *d_transits,
+                 const int64_t *d_samples, int32_t *d_next, void *stream);
 /* Measurement aid, no counterpart in the reference: the rate (gathers per second) at which this
  * GPU serves independent random 4-byte gathers from an array of footprint_bytes, n_gathers per
  * launch, averaged over `repeats` launches after two warm-up launches.  A walk step is a few such

@@ -85,6 +85,7 @@ _SIGS = {
     "nd_static_max_pairs": (C.c_int64, []),
     "nd_distinct_segments":(C.c_int, [C.c_int, VP, C.c_int64, C.c_int32, C.c_int32, VP]),
     "nd_philox_uniform": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, VP, VP]),
+    "nd_walk_step": (C.c_int, [VP, C.POINTER(AppParams), C.c_int, C.c_int64, VP, VP, VP, VP]),
     "nd_probe_random_gather": (C.c_int, [C.c_int, C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_double)]),
 }
 

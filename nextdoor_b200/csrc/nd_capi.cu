@@ -393,6 +393,16 @@ int nd_distinct_segments(int device, int32_t *data, int64_t n_segments, int32_t 
   return ND_OK;
 }
 
+int nd_walk_step(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const int32_t *d_transits,
+                 const int64_t *d_samples, int32_t *d_next, void *stream) {
+  ND_REQUIRE(g && p && n >= 0 && step >= 0 && (n == 0 || (d_transits && d_samples && d_next)), ND_ERR_ARG, "nd_walk_step: bad argument");
+  ND_REQUIRE(p->app == ND_APP_UNIFORM_WALK || p->app == ND_APP_DEEPWALK || p->app == ND_APP_PPR, ND_ERR_ARG,
+             "nd_walk_step: app %d needs the adjacency of another vertex than the transit (node2vec) or is not a walk", p->app);
+  ND_CUDA(cudaSetDevice(g->device));
+  if (n == 0) return ND_OK;
+  return nd_walk_step_launch(g, p, step, n, d_transits, d_samples, d_next, (cudaStream_t)stream);
+}
+
 int nd_probe_random_gather(int device, int64_t footprint_bytes, int64_t n_gathers, int repeats,
                            double *gathers_per_second) {
   ND_REQUIRE(footprint_bytes >= 4 && n_gathers > 0 && repeats > 0 && gathers_per_second, ND_ERR_ARG,

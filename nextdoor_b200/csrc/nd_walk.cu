@@ -635,6 +635,63 @@ int launch_sp(nd_sampler *s, const WalkParams &wp) {
 
 }  // namespace
 
+// interleaved (neighbour id, weight) records of a graph, built on first use
+int nd_graph_ensure_colw(const nd_graph *g, int sms) {
+  if (g->colw || g->E == 0) return ND_OK;
+  int2 *cw = nullptr;
+  ND_CUDA(cudaMalloc(&cw, sizeof(int2) * (size_t)g->E));
+  colw_build_kernel<<<sms * 16, 256>>>(g->col, g->w, g->E, cw);
+  ND_CUDA(cudaDeviceSynchronize());
+  g->colw = cw;
+  return ND_OK;
+}
+
+namespace {
+__device__ int g_step_status;                       // device status word of nd_walk_step
+__device__ unsigned long long g_step_stats[8];      // its event counters (not reported)
+
+// One next() per explicit (transit, sample) pair; the sample id is the global one the draws are keyed by.
+template <int APP>
+__global__ void __launch_bounds__(256)
+walk_step_kernel(NdGraphView g, WalkParams wp, int step, int64_t n, const int32_t *__restrict__ transit,
+                 const int64_t *__restrict__ sample, int32_t *__restrict__ next) {
+  Events ev;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t t = transit[i];
+    int32_t nbr = -1;
+    if (t >= 0 && t < g.V) {
+      const int32_t rs = __ldg(g.row_ptr + t);
+      const int32_t deg = __ldg(g.row_ptr + t + 1) - rs;
+      if (deg > 0) {
+        Rng rng(wp.seed, (uint32_t)sample[i], (uint32_t)step, 0u);
+        int32_t st = 0;
+        nbr = app_next<APP, false>(g, wp, step, t, rs, deg, st, rng, &g_step_status, ev);
+      }
+    }
+    next[i] = nbr;
+  }
+}
+}  // namespace
+
+int nd_walk_step_launch(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const int32_t *d_transits,
+                        const int64_t *d_samples, int32_t *d_next, cudaStream_t st) {
+  NdDeviceInfo dev;
+  ND_TRY(nd_device_info(g->device, &dev));
+  if (p->app == ND_APP_DEEPWALK || p->app == ND_APP_PPR) ND_TRY(nd_graph_ensure_colw(g, dev.sms));
+  WalkParams wp{p->seed, p->p, p->q, p->stop_prob, p->n2v_ref_compat, p->steps, nullptr, g->colw};
+  const int64_t blocks = (n + 255) / 256;
+  const int grid = (int)(blocks < (int64_t)dev.sms * 16 ? blocks : (int64_t)dev.sms * 16);
+  NdGraphView gv = nd_view(g);
+  switch (p->app) {
+    case ND_APP_UNIFORM_WALK: walk_step_kernel<ND_APP_UNIFORM_WALK><<<grid, 256, 0, st>>>(gv, wp, step, n, d_transits, d_samples, d_next); break;
+    case ND_APP_DEEPWALK: walk_step_kernel<ND_APP_DEEPWALK><<<grid, 256, 0, st>>>(gv, wp, step, n, d_transits, d_samples, d_next); break;
+    default: walk_step_kernel<ND_APP_PPR><<<grid, 256, 0, st>>>(gv, wp, step, n, d_transits, d_samples, d_next); break;
+  }
+  nd_count_launches(1);
+  ND_CUDA(cudaGetLastError());
+  return ND_OK;
+}
+
 int nd_walk_alloc(nd_sampler *s) {
   const int64_t S = s->S;
   const int steps = s->p.steps;
@@ -656,13 +713,7 @@ int nd_walk_alloc(nd_sampler *s) {
       s->g->adjset = set;
     }
   }
-  if ((s->p.app == ND_APP_DEEPWALK || s->p.app == ND_APP_PPR) && !s->g->colw && s->g->E > 0) {
-    int2 *cw = nullptr;
-    ND_CUDA(cudaMalloc(&cw, sizeof(int2) * (size_t)s->g->E));
-    colw_build_kernel<<<s->dev.sms * 16, 256>>>(s->g->col, s->g->w, s->g->E, cw);
-    ND_CUDA(cudaDeviceSynchronize());
-    s->g->colw = cw;
-  }
+  if (s->p.app == ND_APP_DEEPWALK || s->p.app == ND_APP_PPR) ND_TRY(nd_graph_ensure_colw(s->g, s->dev.sms));
   s->map_cap = S;
   for (int i = 0; i < 2; i++) {
     ND_CUDA(cudaMalloc(&s->d_map_key[i], sizeof(int32_t) * (size_t)S));

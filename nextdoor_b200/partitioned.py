@@ -1,0 +1,162 @@
+"""Random walks over a graph that is PARTITIONED across the GPUs of a process group instead of
+replicated: rank r holds the CSR rows of one contiguous vertex range, every step runs next() on
+the walkers that currently stand on the rank's vertices (`nd_walk_step`), and the survivors are
+routed to the owners of their new vertices with one all-to-all.  At the end every (sample, step,
+vertex) record travels to the sample's home rank (the reference's seed shards, src/utils.hpp:26-27)
+with one more all-to-all.
+
+This is the path the reference's CSR partitioner was written for (src/graph_partitioner.cuh:1-173)
+but never got: its multi-GPU code replicates the graph (src/nextdoor.cu:1893-1911) and the
+partitioned variant is a stub (ENABLE_GRAPH_PARTITION_FOR_GLOBAL_MEM, src/csr.hpp:371-374).  Because
+every draw is keyed by (global sample, step), the result is bit-identical to the replicated
+sampler's, whatever the number of ranks.
+
+Supported applications: uniform walk, DeepWalk, PPR (a step needs only the transit's own row).
+node2vec reads the adjacency of the PREVIOUS vertex, which lives on another rank, and is refused.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import api
+from ._lib import APP_DEEPWALK, APP_PPR, APP_UNIFORM_WALK, check, lib
+
+
+def split_bounds(row_ptr, parts: int) -> np.ndarray:
+    """Vertex boundaries b[0..parts] of `parts` contiguous ranges holding about E/parts CSR entries
+    each (the reference's partitioner also cuts by size, src/graph_partitioner.cuh:40-110)."""
+    row_ptr = np.asarray(row_ptr, np.int64)
+    V, E = row_ptr.shape[0] - 1, int(row_ptr[-1])
+    b = np.zeros(parts + 1, np.int64)
+    for k in range(1, parts):
+        b[k] = min(max(int(np.searchsorted(row_ptr, (E * k) // parts, side="left")), int(b[k - 1])), V)
+    b[parts] = V
+    return b
+
+
+def local_rows(row_ptr, col, w, lo: int, hi: int):
+    """The CSR of the vertex range [lo, hi) with GLOBAL vertex ids: a row-offset array of full
+    length whose rows outside the range are empty, and only the range's entries of col / w."""
+    row_ptr = np.asarray(row_ptr, np.int64)
+    V = row_ptr.shape[0] - 1
+    e0, e1 = int(row_ptr[lo]), int(row_ptr[hi])
+    rp = np.zeros(V + 1, np.int32)
+    rp[lo:hi + 1] = (row_ptr[lo:hi + 1] - e0).astype(np.int32)
+    rp[hi + 1:] = e1 - e0
+    return rp, np.ascontiguousarray(col[e0:e1], np.int32), np.ascontiguousarray(w[e0:e1], np.float32)
+
+
+class PartitionedWalker:
+    """One rank of a partitioned walk job.
+
+    row_ptr_local / col_local / w_local: this rank's rows as returned by local_rows().
+    bounds: the vertex boundaries of ALL ranks (split_bounds), identical on every rank.
+    step_fn(cur, sid, step) -> next: replaces the library's kernel (tests of the routing logic on
+    CPU use it); tensors live on `device`.
+    """
+
+    def __init__(self, row_ptr_local, col_local, w_local, bounds, params, group=None, device=None, step_fn=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.params = params
+        if params.app not in (APP_UNIFORM_WALK, APP_DEEPWALK, APP_PPR):
+            raise ValueError("partitioned sampling supports the uniform walk, DeepWalk and PPR (a step of node2vec "
+                             "needs the previous vertex's adjacency, which lives on another rank)")
+        self.V = int(np.asarray(row_ptr_local).shape[0] - 1)
+        self.bounds = np.asarray(bounds, np.int64)
+        assert self.bounds.shape[0] == self.world + 1 and self.bounds[-1] == self.V
+        self.step_fn = step_fn
+        if step_fn is None:
+            dev_index = torch.cuda.current_device() if device is None else torch.device(device).index
+            self.device = torch.device("cuda", dev_index)
+            self.graph = api.Graph.from_csr(row_ptr_local, col_local, w_local, device=dev_index)
+        else:
+            self.device = torch.device(device or "cpu")
+            self.graph = None
+        self._inner = torch.as_tensor(self.bounds[1:-1], dtype=torch.int64, device=self.device)
+        # collectives run on the tensors' own device unless the backend cannot (gloo with CUDA tensors)
+        self._comm_cpu = dist.is_initialized() and dist.get_backend(group) == "gloo" and self.device.type == "cuda"
+        self.bytes_sent = 0
+
+    # ------------------------------------------------------------------ one step of next()
+    def _next(self, cur, sid, step):
+        if self.step_fn is not None:
+            return self.step_fn(cur, sid, step)
+        n = int(cur.shape[0])
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if n:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            check(lib.nd_walk_step(self.graph._h, C.byref(self.params), step, n, C.c_void_p(cur.data_ptr()),
+                                   C.c_void_p(sid.data_ptr()), C.c_void_p(out.data_ptr()), C.c_void_p(stream)))
+        return out
+
+    # ------------------------------------------------------------------ all-to-all of ragged rows
+    def _exchange(self, dest, columns):
+        """Sends row i of every tensor in `columns` to rank dest[i]; returns the received columns."""
+        if self.world == 1:
+            return columns
+        order = torch.argsort(dest, stable=True)
+        counts = torch.bincount(dest, minlength=self.world)
+        send_counts = counts.cpu()
+        recv_counts = torch.empty_like(send_counts)
+        cdev = torch.device("cpu") if (self._comm_cpu or self.device.type == "cpu") else self.device
+        sc, rc = send_counts.to(cdev), recv_counts.to(cdev)
+        dist.all_to_all_single(rc, sc, group=self.group)
+        recv_counts = rc.cpu()
+        in_split, out_split = send_counts.tolist(), recv_counts.tolist()
+        received = []
+        for col in columns:
+            src = col[order].contiguous()
+            if self._comm_cpu:
+                src = src.cpu()
+            dst = torch.empty(int(sum(out_split)), dtype=src.dtype, device=src.device)
+            dist.all_to_all_single(dst, src, output_split_sizes=out_split, input_split_sizes=in_split, group=self.group)
+            self.bytes_sent += src.element_size() * (int(sum(in_split)) - in_split[self.rank])
+            received.append(dst.to(self.device))
+        return received
+
+    def _owner(self, v):
+        return torch.bucketize(v.to(torch.int64), self._inner, right=True)
+
+    # ------------------------------------------------------------------ the job
+    def run(self, total_samples: int, initial=None):
+        """Walks samples [0, total_samples); returns this rank's home shard [count, steps] (int32 on
+        `device`, invalid = V) and the shard's first sample.  `initial`: the initial vertex of every
+        sample (array of total_samples), default sample s starts at vertex s mod V."""
+        steps = int(self.params.steps)
+        first, count = api.shard_range(total_samples, self.rank, self.world)
+        sid = torch.arange(first, first + count, dtype=torch.int64, device=self.device)
+        if initial is None:
+            cur = (sid % self.V).to(torch.int32)
+        else:
+            cur = torch.as_tensor(np.ascontiguousarray(initial[first:first + count], np.int32), device=self.device)
+        ok = (cur >= 0) & (cur < self.V)
+        cur, sid = self._exchange(self._owner(cur[ok]), [cur[ok], sid[ok]])
+        rec_sid, rec_step, rec_v = [], [], []
+        for step in range(steps):
+            nxt = self._next(cur.contiguous(), sid.contiguous(), step)
+            alive = nxt >= 0
+            sid, nxt = sid[alive], nxt[alive]
+            rec_sid.append(sid)
+            rec_step.append(torch.full_like(sid, step, dtype=torch.int32))
+            rec_v.append(nxt)
+            left = torch.tensor([int(sid.shape[0])], dtype=torch.int64,
+                                device="cpu" if (self._comm_cpu or self.device.type == "cpu") else self.device)
+            if self.world > 1:
+                dist.all_reduce(left, group=self.group)
+            if int(left.item()) == 0 or step == steps - 1:
+                break
+            cur, sid = self._exchange(self._owner(nxt), [nxt, sid])
+        # every record goes home
+        r_sid, r_step, r_v = torch.cat(rec_sid), torch.cat(rec_step), torch.cat(rec_v)
+        per = total_samples // self.world
+        home = torch.clamp(r_sid // per, max=self.world - 1) if per > 0 else torch.full_like(r_sid, self.world - 1)
+        r_sid, r_step, r_v = self._exchange(home, [r_sid, r_step, r_v])
+        out = torch.full((count, steps), self.V, dtype=torch.int32, device=self.device)
+        out[(r_sid - first), r_step.to(torch.int64)] = r_v
+        return out, first

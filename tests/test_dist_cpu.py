@@ -48,3 +48,53 @@ def test_two_ranks_gather_equals_single_job():
         assert ret["ok"]
         (f0, c0), (f1, c1) = ret["ranges"]
         assert (f0, c0) == (0, total // 2) and (f1, c1) == (total // 2, total - total // 2)
+
+
+def _partitioned_worker(rank, world, port, total, steps, ret):
+    """The routing and bookkeeping of the partitioned walker over gloo, with next() restated in
+    Python from the keyed draws (uniform walk) so that no GPU is needed."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from nextdoor_b200 import api as nd
+    from nextdoor_b200 import partitioned as ndp
+    from oracle import ndo
+    g = ndo.rmat_graph(300, 1500, seed=4)
+    seed = 9
+    bounds = ndp.split_bounds(g.row_ptr, world)
+    rp, col, w = ndp.local_rows(g.row_ptr, g.col, g.w, int(bounds[rank]), int(bounds[rank + 1]))
+    u, ri = ndo.lib().ndo_uniform, ndo.lib().ndo_rand_int
+
+    def step_fn(cur, sid, step):
+        out = torch.empty_like(cur)
+        for i, (t, s) in enumerate(zip(cur.tolist(), sid.tolist())):
+            assert bounds[rank] <= t < bounds[rank + 1], "a walker was routed to a rank that does not own its vertex"
+            deg = int(rp[t + 1] - rp[t])
+            out[i] = int(col[rp[t] + ri(u(seed, s, step, 0, 0), deg)]) if deg > 0 else -1
+        return out
+
+    pr = nd.app_params(nd.APP_UNIFORM_WALK, steps=steps, seed=seed)
+    walker = ndp.PartitionedWalker(rp, col, w, bounds, pr, device="cpu", step_fn=step_fn)
+    init = (np.arange(total) * 7 % g.V).astype(np.int32)
+    init[5] = g.V          # an invalid seed: its row stays invalid
+    out, first = walker.run(total, initial=init)
+    exp = ndo.sample(g, ndo.make_params(ndo.APP_UNIFORM_WALK, steps=steps, seed=seed), total, initial=init)["out"]
+    ok = np.array_equal(out.numpy(), exp[first:first + out.shape[0]])
+    oks = [None] * world
+    dist.all_gather_object(oks, bool(ok))
+    if rank == 0:
+        ret["ok"] = all(oks)
+        ret["sent"] = walker.bytes_sent
+    dist.destroy_process_group()
+
+
+def test_partitioned_walk_two_ranks_equals_replicated_job():
+    from nextdoor_b200 import build
+    build.build()
+    for world in (2, 3):
+        mgr = mp.Manager()
+        ret = mgr.dict()
+        mp.spawn(_partitioned_worker, args=(world, _free_port(), 257, 15, ret), nprocs=world, join=True)
+        assert ret["ok"]
+        assert ret["sent"] > 0
