@@ -210,6 +210,53 @@ def cpu_baseline(hg, wl, seed, budget_s=12.0):
             "sample": f"first {n} of {S_all} samples, {t:.2f} s", "seconds": t}
 
 
+def partitioned_bench(a, wl, nd, torch, rank, world, local, seed):
+    """Strong-scaling figure of the partitioned path: the workload's walks over a graph whose rows
+    are split across the ranks (each GPU holds 1/N of the CSR entries), walkers routed by
+    all-to-all every step.  Device-timed, max over ranks."""
+    import torch.distributed as dist
+    from nextdoor_b200 import partitioned as ndp
+    V, S = wl["V"], wl.get("S", wl["V"])
+    g = nd.Graph.rmat(V, wl["M"], seed, device=local)
+    row_ptr, col, w, _ = g.to_host()
+    E = int(g.E)
+    del g
+    bounds = ndp.split_bounds(row_ptr, world)
+    rp, lc, lw = ndp.local_rows(row_ptr, col, w, int(bounds[rank]), int(bounds[rank + 1]))
+    pr = params_for(nd, wl, seed)
+    walker = ndp.PartitionedWalker(rp, lc, lw, bounds, pr, device=f"cuda:{local}")
+    for _ in range(max(a.warmup, 2)):
+        out, _ = walker.run(S)
+        edges = int((out != V).sum())
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    walker.bytes_sent = 0
+    e0.record()
+    for _ in range(a.steps):
+        out, _ = walker.run(S)
+    e1.record()
+    torch.cuda.synchronize()
+    edges = int((out != V).sum())
+    t = torch.tensor([e0.elapsed_time(e1), float(edges), float(walker.bytes_sent)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        tm = t.clone()
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        t[0] = tm[0]
+    if rank == 0:
+        ms = float(t[0]) / a.steps
+        print(json.dumps({"metric": "sampled edges/sec", "path": "partitioned graph", "value": float(t[1]) / (ms * 1e-3),
+                          "unit": "sampled edges/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
+                          "scaling": "strong", "config": {"workload": f"{a.workload}: {wl['desc']}",
+                                                          "csr_entries_per_gpu": [int(row_ptr[bounds[r + 1]] - row_ptr[bounds[r]]) for r in range(world)],
+                                                          "csr_entries": E},
+                          "all_to_all_bytes_per_step": float(t[2]) / a.steps}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -219,6 +266,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=list(WORKLOADS))
     ap.add_argument("--mode", default="tp_lb", choices=list(MODES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--partitioned", action="store_true",
+                    help="walk over the graph PARTITIONED across the ranks (nextdoor_b200.partitioned) instead of replicated; "
+                         "walk workloads without node2vec; prints its own JSON line")
     ap.add_argument("--profile-only", action="store_true",
                     help="build the graph, run warmup+steps passes of sample() and exit (short launch list for ncu)")
     a = ap.parse_args()
@@ -260,6 +310,8 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if a.partitioned:
+        return partitioned_bench(a, wl, nd, torch, rank, world, local, seed)
     mode = MODES[a.mode]
     g = nd.Graph.rmat(V, M, seed, device=local)
     pr = params_for(nd, wl, seed)

@@ -199,6 +199,26 @@ int nd_philox_uniform(int device, uint64_t seed, int64_t n, const uint32_t *tupl
  * path itself is a stub there, ENABLE_GRAPH_PARTITION_FOR_GLOBAL_MEM, src/csr.hpp:371-374). */
 int nd_walk_step(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const int32_t *d_transits,
                  const int64_t *d_samples, int32_t *d_next, void *stream);
+/* nd_walk_step for walkers packed into one 64-bit word each, (global sample id << 32) | vertex;
+ * a walk that ended comes back as all ones.  Device pointers, enqueued on `stream`. */
+int nd_walk_step_packed(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const uint64_t *d_walkers_in,
+                        uint64_t *d_walkers_out, void *stream);
+/* Routing of packed walkers between the ranks of a partitioned job (no counterpart in the
+ * reference, whose multi-GPU path replicates the graph, src/nextdoor.cu:1893-1911).  `d_bounds`
+ * (device, parts + 1 int64) are the contiguous key ranges of the parts; the key of a walker is its
+ * vertex, or its sample id when by_sample != 0 (records going to the samples' home ranks).
+ * nd_route_count: d_counts[parts] = live walkers per destination (ended walkers are skipped).
+ * nd_route_scatter: d_out = the live walkers grouped by destination, segment p starting at
+ * sum(d_counts[0..p)); d_cursor[parts] is scratch.  Device pointers, enqueued on `stream`. */
+int nd_route_count(int device, int64_t n, const uint64_t *d_walkers, int by_sample, const int64_t *d_bounds, int parts,
+                   uint64_t *d_counts, void *stream);
+int nd_route_scatter(int device, int64_t n, const uint64_t *d_walkers, int by_sample, const int64_t *d_bounds, int parts,
+                     const uint64_t *d_counts, uint64_t *d_cursor, uint64_t *d_out, void *stream);
+/* d_records[n] = (sample << 32 | vertex) words of ONE step that arrived at their home rank:
+ * d_out[(sample - first_sample) * steps + step] = vertex for the samples in [first_sample,
+ * first_sample + count); d_out is the rank's [count, steps] result array. */
+int nd_records_store(int device, int64_t n, const uint64_t *d_records, int step, int64_t first_sample, int64_t count,
+                     int steps, int32_t *d_out, void *stream);
 /* Measurement aid, no counterpart in the reference: the rate (gathers per second) at which this
  * GPU serves independent random 4-byte gathers from an array of footprint_bytes, n_gathers per
  * launch, averaged over `repeats` launches after two warm-up launches.  A walk step is a few such

@@ -86,6 +86,10 @@ _SIGS = {
     "nd_distinct_segments":(C.c_int, [C.c_int, VP, C.c_int64, C.c_int32, C.c_int32, VP]),
     "nd_philox_uniform": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, VP, VP]),
     "nd_walk_step": (C.c_int, [VP, C.POINTER(AppParams), C.c_int, C.c_int64, VP, VP, VP, VP]),
+    "nd_walk_step_packed": (C.c_int, [VP, C.POINTER(AppParams), C.c_int, C.c_int64, VP, VP, VP]),
+    "nd_route_count": (C.c_int, [C.c_int, C.c_int64, VP, C.c_int, VP, C.c_int, VP, VP]),
+    "nd_route_scatter": (C.c_int, [C.c_int, C.c_int64, VP, C.c_int, VP, C.c_int, VP, VP, VP, VP]),
+    "nd_records_store": (C.c_int, [C.c_int, C.c_int64, VP, C.c_int, C.c_int64, C.c_int64, C.c_int, VP, VP]),
     "nd_probe_random_gather": (C.c_int, [C.c_int, C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_double)]),
 }
 

@@ -403,6 +403,16 @@ int nd_walk_step(const nd_graph *g, const nd_app_params *p, int step, int64_t n,
   return nd_walk_step_launch(g, p, step, n, d_transits, d_samples, d_next, (cudaStream_t)stream);
 }
 
+int nd_walk_step_packed(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const uint64_t *d_walkers_in,
+                        uint64_t *d_walkers_out, void *stream) {
+  ND_REQUIRE(g && p && n >= 0 && step >= 0 && (n == 0 || (d_walkers_in && d_walkers_out)), ND_ERR_ARG, "nd_walk_step_packed: bad argument");
+  ND_REQUIRE(p->app == ND_APP_UNIFORM_WALK || p->app == ND_APP_DEEPWALK || p->app == ND_APP_PPR, ND_ERR_ARG,
+             "nd_walk_step_packed: app %d needs the adjacency of another vertex than the transit (node2vec) or is not a walk", p->app);
+  ND_CUDA(cudaSetDevice(g->device));
+  if (n == 0) return ND_OK;
+  return nd_walk_step_packed_launch(g, p, step, n, d_walkers_in, d_walkers_out, (cudaStream_t)stream);
+}
+
 int nd_probe_random_gather(int device, int64_t footprint_bytes, int64_t n_gathers, int repeats,
                            double *gathers_per_second) {
   ND_REQUIRE(footprint_bytes >= 4 && n_gathers > 0 && repeats > 0 && gathers_per_second, ND_ERR_ARG,

@@ -204,6 +204,8 @@ void nd_phase_end(nd_sampler *s);
 
 // ---------------------------------------------------------------- per-family entry points
 int nd_graph_ensure_colw(const nd_graph *g, int sms);
+int nd_walk_step_packed_launch(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const uint64_t *d_in,
+                               uint64_t *d_out, cudaStream_t st);
 int nd_walk_step_launch(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const int32_t *d_transits,
                         const int64_t *d_samples, int32_t *d_next, cudaStream_t st);
 

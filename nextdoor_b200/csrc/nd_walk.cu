@@ -671,7 +671,51 @@ walk_step_kernel(NdGraphView g, WalkParams wp, int step, int64_t n, const int32_
     next[i] = nbr;
   }
 }
+// The same for walkers packed as (global sample id << 32) | vertex; an ended walk becomes all ones.
+template <int APP>
+__global__ void __launch_bounds__(256)
+walk_step_packed_kernel(NdGraphView g, WalkParams wp, int step, int64_t n, const unsigned long long *__restrict__ in,
+                        unsigned long long *__restrict__ out) {
+  Events ev;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const unsigned long long x = in[i];
+    const int32_t t = (int32_t)(uint32_t)x;
+    const uint32_t sample = (uint32_t)(x >> 32);
+    int32_t nbr = -1;
+    if (x != ~0ull && t >= 0 && t < g.V) {
+      const int32_t rs = __ldg(g.row_ptr + t);
+      const int32_t deg = __ldg(g.row_ptr + t + 1) - rs;
+      if (deg > 0) {
+        Rng rng(wp.seed, sample, (uint32_t)step, 0u);
+        int32_t st = 0;
+        nbr = app_next<APP, false>(g, wp, step, t, rs, deg, st, rng, &g_step_status, ev);
+      }
+    }
+    out[i] = nbr >= 0 ? (((unsigned long long)sample << 32) | (uint32_t)nbr) : ~0ull;
+  }
+}
 }  // namespace
+
+int nd_walk_step_packed_launch(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const uint64_t *d_in,
+                               uint64_t *d_out, cudaStream_t st) {
+  NdDeviceInfo dev;
+  ND_TRY(nd_device_info(g->device, &dev));
+  if (p->app == ND_APP_DEEPWALK || p->app == ND_APP_PPR) ND_TRY(nd_graph_ensure_colw(g, dev.sms));
+  WalkParams wp{p->seed, p->p, p->q, p->stop_prob, p->n2v_ref_compat, p->steps, nullptr, g->colw};
+  const int64_t blocks = (n + 255) / 256;
+  const int grid = (int)(blocks < (int64_t)dev.sms * 16 ? blocks : (int64_t)dev.sms * 16);
+  NdGraphView gv = nd_view(g);
+  const unsigned long long *in = (const unsigned long long *)d_in;
+  unsigned long long *out = (unsigned long long *)d_out;
+  switch (p->app) {
+    case ND_APP_UNIFORM_WALK: walk_step_packed_kernel<ND_APP_UNIFORM_WALK><<<grid, 256, 0, st>>>(gv, wp, step, n, in, out); break;
+    case ND_APP_DEEPWALK: walk_step_packed_kernel<ND_APP_DEEPWALK><<<grid, 256, 0, st>>>(gv, wp, step, n, in, out); break;
+    default: walk_step_packed_kernel<ND_APP_PPR><<<grid, 256, 0, st>>>(gv, wp, step, n, in, out); break;
+  }
+  nd_count_launches(1);
+  ND_CUDA(cudaGetLastError());
+  return ND_OK;
+}
 
 int nd_walk_step_launch(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const int32_t *d_transits,
                         const int64_t *d_samples, int32_t *d_next, cudaStream_t st) {

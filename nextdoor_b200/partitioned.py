@@ -128,6 +128,8 @@ class PartitionedWalker:
         """Walks samples [0, total_samples); returns this rank's home shard [count, steps] (int32 on
         `device`, invalid = V) and the shard's first sample.  `initial`: the initial vertex of every
         sample (array of total_samples), default sample s starts at vertex s mod V."""
+        if self.step_fn is None:
+            return self._run_packed(total_samples, initial)
         steps = int(self.params.steps)
         first, count = api.shard_range(total_samples, self.rank, self.world)
         sid = torch.arange(first, first + count, dtype=torch.int64, device=self.device)
@@ -159,4 +161,94 @@ class PartitionedWalker:
         r_sid, r_step, r_v = self._exchange(home, [r_sid, r_step, r_v])
         out = torch.full((count, steps), self.V, dtype=torch.int32, device=self.device)
         out[(r_sid - first), r_step.to(torch.int64)] = r_v
+        return out, first
+
+    # ------------------------------------------------------------------ the CUDA path: packed walkers, routing kernels
+    def _count(self, wk, by_sample, bounds, counts):
+        check(lib.nd_route_count(self.device.index, int(wk.shape[0]), C.c_void_p(wk.data_ptr()), by_sample,
+                                 C.c_void_p(bounds.data_ptr()), self.world, C.c_void_p(counts.data_ptr()), self._stream()))
+
+    def _scatter(self, wk, by_sample, bounds, counts, n_out):
+        out = torch.empty(n_out, dtype=torch.int64, device=self.device)
+        check(lib.nd_route_scatter(self.device.index, int(wk.shape[0]), C.c_void_p(wk.data_ptr()), by_sample,
+                                   C.c_void_p(bounds.data_ptr()), self.world, C.c_void_p(counts.data_ptr()),
+                                   C.c_void_p(self._cursor.data_ptr()), C.c_void_p(out.data_ptr()), self._stream()))
+        return out
+
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _gather_counts(self, counts):
+        """Every rank's count rows (k rows of P destinations) -> [P ranks, k, P] on the host: the
+        one host synchronisation of a step."""
+        P = self.world
+        k = int(counts.numel()) // P
+        if P == 1:
+            return counts.cpu().view(1, k, 1)
+        if self._comm_cpu:
+            allc = torch.empty(P * k * P, dtype=torch.int64)
+            dist.all_gather_into_tensor(allc, counts.cpu().reshape(-1), group=self.group)
+        else:
+            allc = torch.empty(P * k * P, dtype=torch.int64, device=self.device)
+            dist.all_gather_into_tensor(allc, counts.reshape(-1), group=self.group)
+        return allc.cpu().view(P, k, P)
+
+    def _all_to_all(self, src, send, recv):
+        if self.world == 1:
+            return src
+        if self._comm_cpu:
+            dst = torch.empty(int(sum(recv)), dtype=torch.int64)
+            dist.all_to_all_single(dst, src.cpu(), output_split_sizes=recv, input_split_sizes=send, group=self.group)
+            dst = dst.to(self.device)
+        else:
+            dst = torch.empty(int(sum(recv)), dtype=torch.int64, device=self.device)
+            dist.all_to_all_single(dst, src, output_split_sizes=recv, input_split_sizes=send, group=self.group)
+        self.bytes_sent += 8 * (int(sum(send)) - send[self.rank])
+        return dst
+
+    def _run_packed(self, total_samples, initial):
+        steps, P, r = int(self.params.steps), self.world, self.rank
+        first, count = api.shard_range(total_samples, r, P)
+        dev = self.device
+        if not hasattr(self, "_counts"):
+            self._counts = torch.zeros(P, dtype=torch.int64, device=dev)
+            self._cursor = torch.zeros(P, dtype=torch.int64, device=dev)
+            self._vbounds = torch.as_tensor(self.bounds, dtype=torch.int64, device=dev)
+        sid = torch.arange(first, first + count, dtype=torch.int64, device=dev)
+        if initial is None:
+            cur = sid % self.V
+        else:
+            cur = torch.as_tensor(np.ascontiguousarray(initial[first:first + count], np.int32), device=dev).to(torch.int64)
+        nxt = torch.where((cur >= 0) & (cur < self.V), (sid << 32) | cur, torch.full_like(sid, -1))
+        records = []   # per step: this rank's (sample, new vertex) words, grouped by the owner of the vertex
+        for step in range(-1, steps):
+            # route the live walkers to the owners of their vertices (step -1: the initial vertices)
+            if step >= 0:
+                nxt = torch.empty_like(wk)
+                check(lib.nd_walk_step_packed(self.graph._h, C.byref(self.params), step, int(wk.shape[0]),
+                                              C.c_void_p(wk.data_ptr()), C.c_void_p(nxt.data_ptr()), self._stream()))
+            self._count(nxt, 0, self._vbounds, self._counts)
+            mat = self._gather_counts(self._counts)[:, 0, :]            # [sender, destination]
+            send, recv = mat[r].tolist(), mat[:, r].tolist()
+            live = self._scatter(nxt, 0, self._vbounds, self._counts, int(sum(send)))
+            if step >= 0:
+                records.append(live)
+            if int(mat.sum()) == 0 or step + 1 == steps:
+                break
+            wk = self._all_to_all(live, send, recv)
+        # every step's records go to the samples' home ranks: all counts first (one synchronisation),
+        # then scatter / all-to-all / store per step without touching the host
+        out = torch.full((count, steps), self.V, dtype=torch.int32, device=dev)
+        if records:
+            starts = [api.shard_range(total_samples, k, P)[0] for k in range(P)] + [(1 << 40)]
+            hbounds = torch.as_tensor(starts, dtype=torch.int64, device=dev)
+            hcounts = torch.zeros((len(records), P), dtype=torch.int64, device=dev)
+            for k, rec in enumerate(records):
+                self._count(rec, 1, hbounds, hcounts[k])
+            hmat = self._gather_counts(hcounts)                          # [sender, step, destination]
+            for k, rec in enumerate(records):
+                send, recv = hmat[r, k].tolist(), hmat[:, k, r].tolist()
+                mine = self._all_to_all(self._scatter(rec, 1, hbounds, hcounts[k], int(sum(send))), send, recv)
+                check(lib.nd_records_store(dev.index, int(mine.shape[0]), C.c_void_p(mine.data_ptr()), k, first, count, steps,
+                                           C.c_void_p(out.data_ptr()), self._stream()))
         return out, first
