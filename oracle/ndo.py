@@ -13,6 +13,7 @@ import subprocess
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+REFERENCE_TREE = os.environ.get("NEXTDOOR_REFERENCE", "/root/reference")  # where the upstream sources lie, if present
 ORACLE_SO = os.path.join(HERE, "libnd_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libnd_ref.so")
 
@@ -84,11 +85,11 @@ def build(force=False):
     if force or not os.path.exists(ORACLE_SO) or \
             os.path.getmtime(ORACLE_SO) < os.path.getmtime(os.path.join(HERE, "nd_oracle.c")):
         subprocess.run(["make", "-C", HERE, "libnd_oracle.so"], check=True, capture_output=True)
-    if os.path.isdir("/root/reference/src"):
-        subprocess.run(["make", "-C", HERE, "ref"], check=True, capture_output=True)
+    if os.path.isdir(os.path.join(REFERENCE_TREE, "src")):
+        subprocess.run(["make", "-C", HERE, "ref", "REF=" + REFERENCE_TREE], check=True, capture_output=True)
         # the reference's GPU code for sm_100 (timed beside the library by ref_gpu/run_ref_gpu.py);
         # a measurement leg only, so a compiler failure here does not fail the build
-        subprocess.run(["make", "-C", HERE, "ref_gpu"], check=False, capture_output=True)
+        subprocess.run(["make", "-C", HERE, "ref_gpu", "REF=" + REFERENCE_TREE], check=False, capture_output=True)
 
 
 _lib = None

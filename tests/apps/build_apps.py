@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-REF = "/root/reference"
+REF = os.environ.get("NEXTDOOR_REFERENCE", "/root/reference")
 OWN = os.path.join(HERE, "libnd_compat_apps.so")
 WITH_REF = os.path.join(HERE, "_ref", "libnd_compat_ref.so")
 
