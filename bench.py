@@ -39,6 +39,8 @@ WORKLOADS = {
                desc="GraphSAGE 2-hop, fan-out 25 then 10 without replacement + distinct, 256 batches of 1024 uniform seeds, 2^21 vertices, 32M undirected edges"),
     "c3r": dict(kind=KHOP, app=4, V=1 << 21, M=1 << 25, fanout=[25, 10], S=256 * 1024,
                 desc="k-hop with replacement (the reference's KHopApp) on the c3 graph and seeds"),
+    "c3rv": dict(kind=KHOP, app=4, V=1 << 21, M=1 << 25, fanout=[25, 10], S=1 << 21,
+                 desc="k-hop with replacement, one sample per vertex (the shape of the reference's KHopApp::numSamples) on the c3 graph"),
     "c4f": dict(kind=COLL, app=8, V=1 << 20, M=1 << 24, steps=2, L=64, B=64, S=1024,
                 desc="FastGCN importance sampling (degree^2), 2 layers x 64, 1024 batches of 64 uniform seeds, 2^20 vertices, 16M undirected edges"),
     "c4l": dict(kind=COLL, app=9, V=1 << 20, M=1 << 24, steps=2, L=64, B=64, S=1024,

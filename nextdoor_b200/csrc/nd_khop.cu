@@ -23,6 +23,8 @@
 // its draws are keyed by slot i*stepSize(k) + j.  The reference hands out positions inside
 // [prefix_k, prefix_k + n_k) with an atomic counter (src/nextdoor.cu:295-305), so any order
 // within the hop is a legal outcome of it; this one is deterministic.
+#include <cstdlib>
+
 #include "nd_common.cuh"
 #include "nd_philox.cuh"
 
@@ -420,6 +422,15 @@ int nd_khop_alloc(nd_sampler *s) {
 }
 
 int nd_khop_sample(nd_sampler *s, int mode) {
+  // Load balancing of k-hop = binning by run size + adjacency lists staged in shared memory.  On
+  // B200 it measured slower than the plain pairs kernel in every configuration tried (2^21-vertex
+  // R-MAT graph; 262,144 and 2,097,152 seeds; with and without replacement: 9-25 % slower): the
+  // lists that are short enough to stage and hot enough to pay are served by the 126 MB L2 anyway.
+  // So the load-balanced mode runs the plain transit-parallel kernels unless ND_KHOP_STAGING=1.
+  if (mode == ND_MODE_TRANSIT_PARALLEL_LB) {
+    const char *e = getenv("ND_KHOP_STAGING");
+    if (!(e && e[0] == '1')) mode = ND_MODE_TRANSIT_PARALLEL;
+  }
   const nd_app_params &p = s->p;
   const int64_t S = s->S;
   const bool distinct = p.app == ND_APP_KHOP_DISTINCT;
