@@ -339,6 +339,14 @@ class SamplingModule:
     def finalSamples(self):
         return self.finalSamplesArray().tolist()
 
+    def finalSamplesTensor(self):
+        """The final samples as a CUDA tensor [numSamples, finalSampleSize] that aliases the
+        library's device buffer: no device-to-host copy and no Python list (the reference builds the
+        list element by element, src/nextDoorPythonModule.cu:60-72).  Valid until the next sample()
+        or freeDeviceMemory(); hand it to a loader as is or through DLPack (torch.utils.dlpack)."""
+        from . import dist as _dist
+        return _dist.device_samples(self._sampler)
+
     def finalSampleLength(self):
         return int(self.finalSamplesArray().size)
 

@@ -160,3 +160,13 @@ def test_text_loaders_match_reference_loaders(nd, tmp_path):
     with pytest.raises(nd.NdError) as e:
         nd.Graph.load(str(tmp_path / "edge.txt"), "matrix-market", "text")
     assert "Incorrect graph file type" in str(e.value)
+
+
+def test_random_gather_probe_reports_a_rate(nd):
+    import ctypes as C
+    from nextdoor_b200._lib import lib, check
+    small, large = C.c_double(0), C.c_double(0)
+    check(lib.nd_probe_random_gather(0, 8 << 20, 1 << 22, 3, C.byref(small)))     # L2-resident array
+    check(lib.nd_probe_random_gather(0, 1 << 30, 1 << 22, 3, C.byref(large)))     # 1 GiB: DRAM
+    assert small.value > large.value > 1e9
+    assert lib.nd_probe_random_gather(0, 0, 1, 1, C.byref(small)) != 0            # bad argument is an error, not a crash
