@@ -33,30 +33,38 @@ __global__ void __launch_bounds__(THREADS)
 radix_hist_kernel(const uint32_t *__restrict__ keys, const int32_t *__restrict__ d_n, int shift, int bins,
                   bool drop, uint32_t drop_key, uint32_t *__restrict__ tile_hist, int64_t max_tiles,
                   uint32_t *__restrict__ ghist) {
-  extern __shared__ uint32_t sh[];
+  extern __shared__ uint32_t sh[];   // [bins] counts of the current tile, [bins] counts of all tiles of this CTA
+  uint32_t *acc = sh + bins;
   const int n = *d_n;
   const int tiles = (n + TILE - 1) / TILE;
   const uint32_t mask = bins - 1;
+  for (int b = threadIdx.x; b < bins; b += THREADS) acc[b] = 0;
   for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     for (int b = threadIdx.x; b < bins; b += THREADS) sh[b] = 0;
     __syncthreads();
     const int base = tile * TILE;
+    uint32_t k[IPT];
+#pragma unroll
+    for (int r = 0; r < IPT; r++) {  // all loads of the tile first
+      const int i = base + r * THREADS + threadIdx.x;
+      k[r] = i < n ? keys[i] : drop_key;
+    }
 #pragma unroll
     for (int r = 0; r < IPT; r++) {
       const int i = base + r * THREADS + threadIdx.x;
-      if (i < n) {
-        const uint32_t k = keys[i];
-        if (!(drop && k == drop_key)) atomicAdd(&sh[(k >> shift) & mask], 1u);
-      }
+      if (i < n && !(drop && k[r] == drop_key)) atomicAdd(&sh[(k[r] >> shift) & mask], 1u);
     }
     __syncthreads();
-    for (int b = threadIdx.x; b < bins; b += THREADS) {
+    for (int b = threadIdx.x; b < bins; b += THREADS) {  // a bin is always handled by the same thread
       const uint32_t c = sh[b];
       tile_hist[(int64_t)b * max_tiles + tile] = c;
-      if (c) atomicAdd(&ghist[b], c);
+      acc[b] += c;
     }
     __syncthreads();
   }
+  // one global atomic per bin and CTA instead of one per bin and tile
+  for (int b = threadIdx.x; b < bins; b += THREADS)
+    if (acc[b]) atomicAdd(&ghist[b], acc[b]);
 }
 
 // grid = bins.  CTA b turns row b of tile_hist into global start offsets.
@@ -172,6 +180,113 @@ radix_scatter_kernel(NdSortArrays arr, int key_word, const int32_t *__restrict__
     for (int b = threadIdx.x; b < bins; b += THREADS) ghist_to_clear[b] = 0;
 }
 
+// Scatter for large maps (256 bins): the tile is first permuted into shared memory in its sorted
+// order, then written out, so that consecutive threads store to consecutive addresses inside a
+// bin's run instead of every lane of a warp storing to a different sector.  Same stable order as
+// radix_scatter_kernel.  Shared memory: [WARPS][bins] counters, [bins] tile-local starts, [bins]
+// global starts, [NW][TILE] staged words.
+template <int NW>
+__global__ void __launch_bounds__(THREADS)
+radix_scatter_staged_kernel(NdSortArrays arr, int key_word, const int32_t *__restrict__ d_n, int shift, int bins,
+                            bool drop, uint32_t drop_key, const uint32_t *__restrict__ tile_hist,
+                            int64_t max_tiles, uint32_t *__restrict__ ghist_to_clear) {
+  extern __shared__ uint32_t sm[];
+  uint32_t *cnt = sm;                          // [WARPS][bins]
+  uint32_t *lstart = cnt + WARPS * bins;       // [bins] first slot of the bin inside the staged tile
+  uint32_t *gbase = lstart + bins;             // [bins] first slot of the bin's run of this tile in the output
+  uint32_t *stage = gbase + bins;              // [NW][TILE]
+  __shared__ uint32_t warp_tot[WARPS];
+  const int n = *d_n;
+  const int tiles = (n + TILE - 1) / TILE;
+  const uint32_t mask = bins - 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t lt = (1u << lane) - 1u;
+  uint32_t *my = cnt + warp * bins;
+  const uint32_t *__restrict__ keys = arr.a[key_word];
+
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    for (int i = threadIdx.x; i < WARPS * bins; i += THREADS) cnt[i] = 0;
+    __syncthreads();
+    const int wbase = tile * TILE + warp * (32 * IPT);
+    uint32_t k[IPT], rank[IPT], dig[IPT];
+#pragma unroll
+    for (int r = 0; r < IPT; r++) {
+      const int i = wbase + r * 32 + lane;
+      bool live = i < n;
+      if (live) {
+        k[r] = keys[i];
+        if (drop && k[r] == drop_key) live = false;
+      }
+      dig[r] = live ? ((k[r] >> shift) & mask) : 0xffffffffu;
+    }
+#pragma unroll
+    for (int r = 0; r < IPT; r++) {
+      const uint32_t d = dig[r];
+      const uint32_t peers = __match_any_sync(0xffffffffu, d);
+      const int leader = __ffs(peers) - 1;
+      uint32_t old = 0;
+      if (d != 0xffffffffu && lane == leader) {
+        old = my[d];
+        my[d] = old + __popc(peers);
+      }
+      old = __shfl_sync(0xffffffffu, old, leader);
+      rank[r] = old + __popc(peers & lt);
+      __syncwarp();
+    }
+    __syncthreads();
+    // per bin: exclusive scan over the warps (kept in cnt), tile count of the bin -> lstart (scanned below)
+    for (int b = threadIdx.x; b < bins; b += THREADS) {
+      uint32_t run = 0;
+#pragma unroll
+      for (int w = 0; w < WARPS; w++) {
+        const uint32_t c = cnt[w * bins + b];
+        cnt[w * bins + b] = run;
+        run += c;
+      }
+      lstart[b] = run;
+      gbase[b] = tile_hist[(int64_t)b * max_tiles + tile];
+    }
+    __syncthreads();
+    // exclusive scan of the tile counts over the bins (bins is a multiple of THREADS or smaller)
+    uint32_t carry = 0;
+    for (int b0 = 0; b0 < bins; b0 += THREADS) {
+      const int b = b0 + threadIdx.x;
+      const uint32_t v = b < bins ? lstart[b] : 0u;
+      const uint32_t inc = warp_incl_scan(v);
+      if (lane == 31) warp_tot[warp] = inc;
+      __syncthreads();
+      uint32_t woff = carry;
+      for (int w = 0; w < warp; w++) woff += warp_tot[w];
+      if (b < bins) lstart[b] = woff + inc - v;
+      uint32_t tot = 0;
+      for (int w = 0; w < WARPS; w++) tot += warp_tot[w];
+      carry += tot;
+      __syncthreads();
+    }
+    const uint32_t n_live = carry;
+#pragma unroll
+    for (int r = 0; r < IPT; r++) {
+      if (dig[r] != 0xffffffffu) {
+        const int i = wbase + r * 32 + lane;
+        const uint32_t lp = lstart[dig[r]] + my[dig[r]] + rank[r];
+#pragma unroll
+        for (int w = 0; w < NW; w++) stage[w * TILE + lp] = (w == key_word) ? k[r] : arr.a[w][i];
+      }
+    }
+    __syncthreads();
+    for (uint32_t j = threadIdx.x; j < n_live; j += THREADS) {
+      const uint32_t key = stage[key_word * TILE + j];
+      const uint32_t d = (key >> shift) & mask;
+      const uint32_t pos = gbase[d] + (j - lstart[d]);
+#pragma unroll
+      for (int w = 0; w < NW; w++) arr.b[w][pos] = stage[w * TILE + j];
+    }
+    __syncthreads();
+  }
+  if (ghist_to_clear && blockIdx.x == 0)
+    for (int b = threadIdx.x; b < bins; b += THREADS) ghist_to_clear[b] = 0;
+}
+
 }  // namespace
 
 static int nd_radix_max_digit(int64_t max_n) { return max_n <= ((int64_t)4 << 20) ? 10 : 8; }
@@ -239,11 +354,22 @@ int nd_radix_sort(const NdDeviceInfo &dev, cudaStream_t st, NdRadixScratch *scr,
     NdSortArrays cur = arr;
     if (in_b) for (int w = 0; w < arr.nwords; w++) { cur.a[w] = arr.b[w]; cur.b[w] = arr.a[w]; }
     if (!(p == 0 && first_hist_done)) {
-      radix_hist_kernel<<<grid, THREADS, bins * sizeof(uint32_t), st>>>(
+      radix_hist_kernel<<<grid, THREADS, 2 * bins * sizeof(uint32_t), st>>>(
           cur.a[key_word], n_ptr, pl.shift[p], bins, drop, drop_key, scr->tile_hist, pl.max_tiles, gh);
     }
     radix_scan_kernel<<<bins, THREADS, 0, st>>>(n_ptr, bins, scr->tile_hist, pl.max_tiles, gh,
                                                   p == 0 ? d_n_out : nullptr);
+    if (bins <= 256 && pl.max_n > ((int64_t)4 << 20)) {  // large maps: coalesced stores through a staged tile
+      const size_t sms = sizeof(uint32_t) * ((size_t)WARPS * bins + 2 * (size_t)bins + (size_t)arr.nwords * TILE);
+      switch (arr.nwords) {
+        case 1: radix_scatter_staged_kernel<1><<<grid, THREADS, sms, st>>>(cur, key_word, n_ptr, pl.shift[p], bins, drop, drop_key, scr->tile_hist, pl.max_tiles, gh); break;
+        case 2: radix_scatter_staged_kernel<2><<<grid, THREADS, sms, st>>>(cur, key_word, n_ptr, pl.shift[p], bins, drop, drop_key, scr->tile_hist, pl.max_tiles, gh); break;
+        default: radix_scatter_staged_kernel<3><<<grid, THREADS, sms, st>>>(cur, key_word, n_ptr, pl.shift[p], bins, drop, drop_key, scr->tile_hist, pl.max_tiles, gh); break;
+      }
+      in_b = !in_b;
+      nd_count_launches((p == 0 && first_hist_done) ? 2 : 3);
+      continue;
+    }
     const size_t sm = (size_t)WARPS * bins * sizeof(uint32_t);
     switch (arr.nwords) {
       case 1: radix_scatter_kernel<1><<<grid, THREADS, sm, st>>>(cur, key_word, n_ptr, pl.shift[p], bins, drop, drop_key, scr->tile_hist, pl.max_tiles, gh); break;

@@ -310,6 +310,7 @@ walk_next_tp_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample
   const int n = *d_n;
   const int tiles = (n + tile_size - 1) / tile_size;
   const uint32_t mask = bins - 1;
+  if (HIST) for (int b = threadIdx.x; b < bins; b += NEXT_THREADS) sh_hist[bins + b] = 0;
   for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     if (HIST) {
       for (int b = threadIdx.x; b < bins; b += NEXT_THREADS) sh_hist[b] = 0;
@@ -342,14 +343,17 @@ walk_next_tp_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample
     }
     if (HIST) {
       __syncthreads();
-      for (int b = threadIdx.x; b < bins; b += NEXT_THREADS) {
+      for (int b = threadIdx.x; b < bins; b += NEXT_THREADS) {  // a bin is always handled by the same thread
         const uint32_t c = sh_hist[b];
         tile_hist[(int64_t)b * max_tiles + tile] = c;
-        if (c) atomicAdd(&ghist[b], c);
+        sh_hist[bins + b] += c;
       }
       __syncthreads();
     }
   }
+  if (HIST)  // one global atomic per bin and CTA
+    for (int b = threadIdx.x; b < bins; b += NEXT_THREADS)
+      if (sh_hist[bins + b]) atomicAdd(&ghist[b], sh_hist[bins + b]);
   if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
 }
 
@@ -613,7 +617,7 @@ int launch_next_tp(nd_sampler *s, const WalkParams &wp, int step, bool hist, int
   NdGraphView gv = nd_view(s->g);
   int32_t *tmp_step = s->d_tmp + (int64_t)step * s->S;
   if (hist) {
-    walk_next_tp_kernel<APP, true><<<grid, NEXT_THREADS, bins * sizeof(uint32_t), s->stream>>>(
+    walk_next_tp_kernel<APP, true><<<grid, NEXT_THREADS, 2 * bins * sizeof(uint32_t), s->stream>>>(
         gv, wp, step, s->first, pl.tile, in_key, in_val, d_n, out_key, out_val, tmp_step, s->d_len,
         s->d_state, pl.shift[0], bins, s->radix.tile_hist, pl.max_tiles, s->radix.ghist, s->d_status, s->d_stats);
   } else {
