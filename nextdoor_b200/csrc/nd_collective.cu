@@ -296,25 +296,43 @@ __device__ __forceinline__ uint32_t bm_rank(const uint32_t *bm, const uint32_t *
   return r + __popc(bm[word] & ((1u << (v & 31)) - 1u));
 }
 
-// Streams one neighbour list with STRIDE cooperating threads, BM_UNROLL loads in flight per thread:
-// sets the neighbours' bits and, for LADIES, adds the weights to the caller's partial row sum.
-constexpr int BM_UNROLL = 8;
+// Streams one neighbour list with STRIDE cooperating threads: sets the neighbours' bits and, for
+// LADIES, adds the weights to the caller's partial row sum.  The body of the list is read as
+// 16-byte vectors (the arrays are 256-byte aligned, so entry rs + head is 16-byte aligned for
+// head = (4 - rs % 4) % 4), BM_VEC vectors in flight per thread; head and tail entries one by one.
+constexpr int BM_UNROLL = 8;   // scalar loads in flight per thread (second LADIES pass)
+constexpr int BM_VEC = 4;      // 16-byte loads in flight per thread
 template <bool LADIES, int STRIDE>
 __device__ __forceinline__ void bm_stream(const NdGraphView &g, uint32_t *bm, int32_t rs, int32_t deg, int me, double &part) {
-  for (int e0 = me; e0 < deg; e0 += STRIDE * BM_UNROLL) {
-    int32_t v[BM_UNROLL];
-    float w[BM_UNROLL];
+  const int32_t *__restrict__ col = g.col + rs;
+  const float *__restrict__ wts = g.w + rs;
+  int head = (4 - (rs & 3)) & 3;
+  if (head > deg) head = deg;
+  if (me < head) {
+    bm_mark(bm, __ldg(col + me));
+    if (LADIES) part += (double)__ldg(wts + me);
+  }
+  const int n4 = (deg - head) >> 2;
+  const int4 *__restrict__ col4 = reinterpret_cast<const int4 *>(col + head);
+  const float4 *__restrict__ w4 = reinterpret_cast<const float4 *>(wts + head);
+  for (int e0 = me; e0 < n4; e0 += STRIDE * BM_VEC) {
+    int4 v[BM_VEC];
+    float4 w[BM_VEC];
 #pragma unroll
-    for (int k = 0; k < BM_UNROLL; k++) {
+    for (int k = 0; k < BM_VEC; k++) {
       const int e = e0 + k * STRIDE;
-      v[k] = e < deg ? __ldg(g.col + rs + e) : -1;
-      if (LADIES) w[k] = e < deg ? __ldg(g.w + rs + e) : 0.f;
+      v[k] = e < n4 ? __ldg(col4 + e) : make_int4(-1, -1, -1, -1);
+      if (LADIES) w[k] = e < n4 ? __ldg(w4 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int k = 0; k < BM_UNROLL; k++) {
-      if (v[k] >= 0) bm_mark(bm, v[k]);
-      if (LADIES) part += (double)w[k];
+    for (int k = 0; k < BM_VEC; k++) {
+      if (v[k].x >= 0) { bm_mark(bm, v[k].x); bm_mark(bm, v[k].y); bm_mark(bm, v[k].z); bm_mark(bm, v[k].w); }
+      if (LADIES) part += ((double)w[k].x + (double)w[k].y) + ((double)w[k].z + (double)w[k].w);
     }
+  }
+  for (int e = head + (n4 << 2) + me; e < deg; e += STRIDE) {
+    bm_mark(bm, __ldg(col + e));
+    if (LADIES) part += (double)__ldg(wts + e);
   }
 }
 
