@@ -103,7 +103,10 @@ __device__ __forceinline__ bool n2v_member_slow(const NdGraphView &g, const int3
   return false;
 }
 
-constexpr int TRY_BATCH = 4;    // node2vec tries whose gathers are issued together
+// node2vec tries whose gathers are issued together (template argument of app_next): measured
+// best are 3 in the ticket kernel and 2 in the sample-parallel kernel at four CTAs of 256 per SM,
+// and 4 at three CTAs per SM in the kernel that also keeps the radix histogram
+constexpr int N2V_BATCH_COUNT = 3, N2V_BATCH_SP = 2, N2V_BATCH_TP = 4;
 // Weighted tries per round.  Every try of a round is gathered, so a larger batch buys latency with
 // gathers that a 60 % acceptance rate wastes: two per round, except PPR in the sample-parallel
 // kernel (walks die young there, the kernel is short of loads in flight; four measured faster).
@@ -114,10 +117,10 @@ __host__ __device__ constexpr int weight_batch() { return APP == ND_APP_PPR && !
 //
 // The rejection loops of DeepWalk / PPR / node2vec draw their tries from the keyed stream in
 // order, so try k of an invocation is a pure function of (sample, step, k).  The loops below
-// evaluate TRY_BATCH tries per round: the gathers of the whole round are issued together (one
+// evaluate a batch of tries per round: the gathers of the whole round are issued together (one
 // memory latency instead of one per try) and the first try that accepts, in draw order, wins --
 // the same vertex the one-try-at-a-time loop returns.  Only the tries up to the winner are counted.
-template <int APP, bool STREAM = true>
+template <int APP, bool STREAM = true, int N2V_BATCH = N2V_BATCH_COUNT>
 __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkParams &wp, int step,
                                             int32_t transit, int32_t rs, int32_t n, int32_t &state_t,
                                             Rng &rng, int *status, Events &ev) {
@@ -167,6 +170,7 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
     const uint32_t n_buckets = ((uint32_t)(ts + tn) >> 2) - ((uint32_t)ts >> 2);
     const int4 *__restrict__ region = reinterpret_cast<const int4 *>(wp.adjset) + 2 * (size_t)((uint32_t)ts >> 2);
     const bool use_set = tn >= SET_MIN_DEG;
+    constexpr int TRY_BATCH = N2V_BATCH;
     for (int it = 0;; it += TRY_BATCH) {
       int32_t x[TRY_BATCH], v[TRY_BATCH];
       float y[TRY_BATCH];
@@ -287,17 +291,17 @@ __global__ void init_map_kernel(const int32_t *__restrict__ initial, int32_t V, 
 
 // ---------------------------------------------------------------- transit-parallel next()
 
-// node2vec keeps a round of candidates and set buckets in registers: three CTAs per SM (80
-// registers) measured faster than two (116) or four (64, spilling)
+// node2vec keeps a round of candidates and set buckets in registers: four CTAs of 256 per SM (64
+// registers) with rounds of 2-3 tries measured faster than three CTAs with rounds of 4
 template <int APP>
-constexpr int walk_min_ctas() { return APP == ND_APP_NODE2VEC ? 3 : 1; }
+constexpr int walk_min_ctas() { return APP == ND_APP_NODE2VEC ? 4 : 1; }
 
 constexpr int NEXT_THREADS = 256;
 
 // One CTA per radix tile of the transit->sample map.  HIST: also count the first radix digit of the
 // new keys (layout and digit as the radix scatter of pass 0 expects them).
 template <int APP, bool HIST>
-__global__ void __launch_bounds__(NEXT_THREADS, walk_min_ctas<APP>())
+__global__ void __launch_bounds__(NEXT_THREADS, APP == ND_APP_NODE2VEC ? 3 : 1)
 walk_next_tp_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample, int tile_size,
                     const int32_t *__restrict__ in_key, const int32_t *__restrict__ in_val,
                     const int32_t *__restrict__ d_n, int32_t *__restrict__ out_key,
@@ -330,7 +334,7 @@ walk_next_tp_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample
           Rng rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
           int32_t st = 0;
           if (APP == ND_APP_NODE2VEC && step > 0) st = state[s];
-          nbr = app_next<APP>(g, wp, step, t, rs, deg, st, rng, status, ev);
+          nbr = app_next<APP, true, N2V_BATCH_TP>(g, wp, step, t, rs, deg, st, rng, status, ev);
           if (APP == ND_APP_NODE2VEC && nbr >= 0) state[s] = st;
         }
       }
@@ -538,7 +542,7 @@ walk_sp_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_t S,
       int32_t nbr = -1;
       if (deg > 0) {
         Rng rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
-        nbr = app_next<APP, false>(g, wp, step, cur, rs, deg, st, rng, status, ev);
+        nbr = app_next<APP, false, N2V_BATCH_SP>(g, wp, step, cur, rs, deg, st, rng, status, ev);
       }
       if (nbr < 0) break;
       tmp[(int64_t)step * S + s] = nbr;
