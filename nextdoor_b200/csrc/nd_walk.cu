@@ -293,8 +293,12 @@ __global__ void init_map_kernel(const int32_t *__restrict__ initial, int32_t V, 
 
 // node2vec keeps a round of candidates and set buckets in registers: four CTAs of 256 per SM (64
 // registers) with rounds of 2-3 tries measured faster than three CTAs with rounds of 4
+// (the weighted apps: five CTAs per SM in the ticket kernel, six in the sample-parallel one,
+// measured against 4-8 on the 2^20- and 2^24-vertex graphs)
 template <int APP>
-constexpr int walk_min_ctas() { return APP == ND_APP_NODE2VEC ? 4 : 1; }
+constexpr int walk_min_ctas() { return APP == ND_APP_NODE2VEC ? 4 : (APP == ND_APP_UNIFORM_WALK ? 1 : 5); }
+template <int APP>
+constexpr int walk_min_ctas_sp() { return APP == ND_APP_NODE2VEC ? 4 : (APP == ND_APP_UNIFORM_WALK ? 1 : 6); }
 
 constexpr int NEXT_THREADS = 256;
 
@@ -525,7 +529,7 @@ walk_scatter_kernel(const int32_t *__restrict__ d_n, int32_t V, const int32_t *_
 // ---------------------------------------------------------------- sample-parallel: a thread owns a walk
 
 template <int APP>
-__global__ void __launch_bounds__(256, walk_min_ctas<APP>())
+__global__ void __launch_bounds__(256, walk_min_ctas_sp<APP>())
 walk_sp_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_t S,
                const int32_t *__restrict__ initial, int32_t *__restrict__ tmp,
                int32_t *__restrict__ len, int *__restrict__ status, unsigned long long *__restrict__ stats) {
