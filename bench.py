@@ -120,7 +120,8 @@ def next_bytes(wl, st, mode):
     8 B map-out per pair of every step but the last (no maps in sample-parallel mode); weighted
     apps + 4 B max weight per next() and 4 B per weight read; node2vec + previous vertex (4+4 B,
     kept in a register in sample-parallel mode), 8 B for its row, and per try 4 B candidate + 4 B per
-    binary-search probe.  k-hop: per pair 8 B map-in + 8 B row offsets, per neighbour 4 B + 4 B,
+    word read by the membership test (one 8-id bucket of the previous vertex's neighbour set = 32 B;
+    tests the draw decides without are not made and not counted).  k-hop: per pair 8 B map-in + 8 B row offsets, per neighbour 4 B + 4 B,
     8 B map-out per neighbour of every hop but the last.  Collective: 4 B per gathered neighbour id
     (+4 B weight for LADIES), 8 B per unique candidate, 8 B per sampled vertex."""
     pairs, edges = st["live_pairs"], st["sampled_edges"]
