@@ -405,7 +405,10 @@ def main():
         smp2 = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=init_np)
         smp2.set_stream(stream.cuda_stream)
         pair = [(smp, nd_dist.device_samples(smp)), (smp2, nd_dist.device_samples(smp2))]
-        fulls = [torch.empty((world * S, fs), dtype=torch.int32, device="cuda") for _ in range(2)]
+        # (two gathered arrays; when they would not fit comfortably -- the 2^24-vertex workload on 8 GPUs
+        # gathers 54 GB -- one array is used and a gather waits for the previous one: less overlap)
+        n_full = 2 if 2 * world * S * fs * 4 < (48 << 30) else 1
+        fulls = [torch.empty((world * S, fs), dtype=torch.int32, device="cuda") for _ in range(n_full)]
         side = torch.cuda.Stream()
         pending = [None, None]
 
@@ -417,9 +420,11 @@ def main():
             s_k.sample(mode, sync=False)
             ev = torch.cuda.Event()
             ev.record(stream)
+            if n_full == 1 and pending[k ^ 1] is not None:
+                pending[k ^ 1].wait()          # the single gathered array is still being written
             with torch.cuda.stream(side):
                 side.wait_event(ev)
-                pending[k] = dist.all_gather_into_tensor(fulls[k], shard_k, async_op=True)
+                pending[k] = dist.all_gather_into_tensor(fulls[k % n_full], shard_k, async_op=True)
 
         def gather_drain():
             for k in range(2):
@@ -439,7 +444,7 @@ def main():
         y1.record(stream)
         barrier()
         ms_gather = y0.elapsed_time(y1)
-        gather_ok = bool((fulls[(a.steps - 1) % 2][rank * S:(rank + 1) * S] == pair[(a.steps - 1) % 2][1]).all())
+        gather_ok = bool((fulls[((a.steps - 1) % 2) % n_full][rank * S:(rank + 1) * S] == pair[(a.steps - 1) % 2][1]).all())
         assert gather_ok, "the gathered array does not hold this rank's shard"
         del fulls
         smp2.free()
