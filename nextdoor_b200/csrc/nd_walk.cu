@@ -113,13 +113,113 @@ constexpr int N2V_BATCH_COUNT = 3, N2V_BATCH_SP = 2, N2V_BATCH_TP = 4;
 template <int APP, bool STREAM>
 __host__ __device__ constexpr int weight_batch() { return APP == ND_APP_PPR && !STREAM ? 4 : 2; }
 
-// One next() of the app on a transit with n > 0 neighbours; -1 = no vertex.
-//
+constexpr int32_t ROUND_AGAIN = -2;   // a round of tries ended without an accepted vertex
+
 // The rejection loops of DeepWalk / PPR / node2vec draw their tries from the keyed stream in
-// order, so try k of an invocation is a pure function of (sample, step, k).  The loops below
-// evaluate a batch of tries per round: the gathers of the whole round are issued together (one
-// memory latency instead of one per try) and the first try that accepts, in draw order, wins --
-// the same vertex the one-try-at-a-time loop returns.  Only the tries up to the winner are counted.
+// order, so try k of an invocation is a pure function of (sample, step, k).  A ROUND evaluates a
+// batch of tries: the gathers of the whole round are issued together (one memory latency instead
+// of one per try) and the first try that accepts, in draw order, wins -- the same vertex the
+// one-try-at-a-time loop returns.  Only the tries up to the winner are counted.  `rng` carries the
+// draw position from round to round.
+
+// weighted rejection (randomWalks.cu:81-89): {x = rand_int(n); y = u * max_w} until !(y > w[x])
+template <bool STREAM, int BATCH>
+__device__ __forceinline__ int32_t weighted_round(const WalkParams &wp, int32_t rs, int32_t n, float max_w, Rng &rng,
+                                                  Events &ev) {
+  const int2 *__restrict__ recs = wp.colw + rs;
+  float y[BATCH];
+  int2 rec[BATCH];
+#pragma unroll
+  for (int k = 0; k < BATCH; k++) {
+    const int32_t x = rng.rand_int(n);
+    y[k] = __fmul_rn(rng.uniform(), max_w);
+    rec[k] = ld_graph<STREAM>(recs + x);
+  }
+#pragma unroll
+  for (int k = 0; k < BATCH; k++) {
+    ev.weight_tries++;
+    if (!(y[k] > __int_as_float(rec[k].y))) return rec[k].x;
+  }
+  return ROUND_AGAIN;
+}
+
+// node2vec (randomWalks.cu:151-171).  A candidate that is not the previous vertex t is accepted
+// when y < 1/q (neighbour of t) or y < 1 (not a neighbour): below `lo` the membership does not
+// matter, at or above `hi` neither; below `sure` nothing about the candidate matters.
+struct N2vConsts {
+  float inv_q, bound, lo, hi, sure;
+  __device__ __forceinline__ explicit N2vConsts(const WalkParams &wp) {
+    inv_q = __fdiv_rn(1.0f, wp.q);
+    bound = wp.p > inv_q ? wp.p : inv_q;
+    if (bound < 1.0f) bound = 1.0f;
+    lo = inv_q < 1.0f ? inv_q : 1.0f;
+    hi = inv_q < 1.0f ? 1.0f : inv_q;
+    sure = lo < wp.p ? lo : wp.p;
+  }
+};
+
+// t = previous vertex, [ts, ts + tn) its row
+template <bool STREAM, int BATCH>
+__device__ __forceinline__ int32_t n2v_round(const NdGraphView &g, const WalkParams &wp, const N2vConsts &c, int32_t rs,
+                                             int32_t n, int32_t t, int32_t ts, int32_t tn, Rng &rng, Events &ev) {
+  const int32_t *__restrict__ edges = g.col + rs;
+  const uint32_t n_buckets = ((uint32_t)(ts + tn) >> 2) - ((uint32_t)ts >> 2);
+  const int4 *__restrict__ region = reinterpret_cast<const int4 *>(wp.adjset) + 2 * (size_t)((uint32_t)ts >> 2);
+  const bool use_set = tn >= SET_MIN_DEG;
+  int32_t x[BATCH], v[BATCH];
+  float y[BATCH];
+  int n_try = BATCH;  // the round ends at the first try that is sure to accept
+#pragma unroll
+  for (int k = 0; k < BATCH; k++) {
+    if (k < n_try) {
+      x[k] = rng.rand_int(n);
+      y[k] = __fmul_rn(rng.uniform(), c.bound);
+      if (y[k] < c.sure) n_try = k + 1;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < BATCH; k++) v[k] = k < n_try ? ld_graph<STREAM>(edges + x[k]) : -1;
+  // membership gathers of the tries that need one, issued together
+  bool is_ret[BATCH], need[BATCH];
+  uint32_t bucket[BATCH];
+  int4 ba[BATCH], bb[BATCH];
+#pragma unroll
+  for (int k = 0; k < BATCH; k++) {
+    is_ret[k] = wp.n2v_compat ? (x[k] == t) : (v[k] == t);  // randomWalks.cu:159 compares the index
+    need[k] = k < n_try && !is_ret[k] && y[k] >= c.lo && y[k] < c.hi;
+    bucket[k] = set_bucket(v[k], n_buckets);
+    if (need[k] && use_set) {
+      ba[k] = ld_graph<STREAM>(region + 2 * (size_t)bucket[k]);
+      bb[k] = ld_graph<STREAM>(region + 2 * (size_t)bucket[k] + 1);
+    } else {
+      ba[k] = make_int4(SET_EMPTY, SET_EMPTY, SET_EMPTY, SET_EMPTY);
+      bb[k] = ba[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < BATCH; k++) {
+    if (k < n_try) {
+      ev.n2v_tries++;
+      bool accept;
+      if (is_ret[k]) {
+        accept = y[k] < wp.p;
+      } else if (!need[k]) {
+        accept = y[k] < c.lo;
+      } else {
+        bool found = ba[k].x == v[k] || ba[k].y == v[k] || ba[k].z == v[k] || ba[k].w == v[k] ||
+                     bb[k].x == v[k] || bb[k].y == v[k] || bb[k].z == v[k] || bb[k].w == v[k];
+        if (use_set) ev.n2v_probes += 8;
+        if (!found && (!use_set || bb[k].w != SET_EMPTY))
+          found = n2v_member_slow<STREAM>(g, wp.adjset, ts, tn, v[k], bucket[k], n_buckets, ev.n2v_probes);
+        accept = y[k] < (found ? c.inv_q : 1.0f);
+      }
+      if (accept) return v[k];
+    }
+  }
+  return ROUND_AGAIN;
+}
+
+// One next() of the app on a transit with n > 0 neighbours; -1 = no vertex.
 template <int APP, bool STREAM = true, int N2V_BATCH = N2V_BATCH_COUNT>
 __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkParams &wp, int step,
                                             int32_t transit, int32_t rs, int32_t n, int32_t &state_t,
@@ -134,100 +234,28 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
       if (pr < wp.stop_prob) return -1;
     }
     if (n == 1) return ld_graph<STREAM>(edges);
-    const int2 *__restrict__ recs = wp.colw + rs;
     const float max_w = __ldg(g.max_w + transit);
     constexpr int WEIGHT_BATCH = weight_batch<APP, STREAM>();
-    for (int it = 0;; it += WEIGHT_BATCH) {
-      float y[WEIGHT_BATCH];
-      int2 rec[WEIGHT_BATCH];
-#pragma unroll
-      for (int k = 0; k < WEIGHT_BATCH; k++) {
-        const int32_t x = rng.rand_int(n);
-        y[k] = __fmul_rn(rng.uniform(), max_w);
-        rec[k] = ld_graph<STREAM>(recs + x);
-      }
-#pragma unroll
-      for (int k = 0; k < WEIGHT_BATCH; k++) {
-        ev.weight_tries++;
-        if (!(y[k] > __int_as_float(rec[k].y))) return rec[k].x;
-      }
-      if (it > RETRY_CAP) { atomicOr(status, ND_DEV_RETRY_LIMIT); return rec[WEIGHT_BATCH - 1].x; }
+    for (int it = 0; it <= RETRY_CAP; it += WEIGHT_BATCH) {
+      const int32_t r = weighted_round<STREAM, WEIGHT_BATCH>(wp, rs, n, max_w, rng, ev);
+      if (r != ROUND_AGAIN) return r;
     }
+    atomicOr(status, ND_DEV_RETRY_LIMIT);
+    return ld_graph<STREAM>(edges);
   }
   if (APP == ND_APP_NODE2VEC) {  // randomWalks.cu:141-172
     if (n == 1 || step == 0) { state_t = transit; return ld_graph<STREAM>(edges); }
-    const float inv_q = __fdiv_rn(1.0f, wp.q);
-    float bound = wp.p > inv_q ? wp.p : inv_q;
-    if (bound < 1.0f) bound = 1.0f;
-    // a candidate that is not the previous vertex is accepted when y < 1/q (neighbour of t) or
-    // y < 1 (not a neighbour): below `lo` the membership does not matter, at or above `hi` neither;
-    // below `sure` nothing about the candidate matters
-    const float lo = inv_q < 1.0f ? inv_q : 1.0f, hi = inv_q < 1.0f ? 1.0f : inv_q;
-    const float sure = lo < wp.p ? lo : wp.p;
+    const N2vConsts c(wp);
     const int32_t t = state_t;
     const int32_t ts = __ldg(g.row_ptr + t);
     const int32_t tn = __ldg(g.row_ptr + t + 1) - ts;
-    const uint32_t n_buckets = ((uint32_t)(ts + tn) >> 2) - ((uint32_t)ts >> 2);
-    const int4 *__restrict__ region = reinterpret_cast<const int4 *>(wp.adjset) + 2 * (size_t)((uint32_t)ts >> 2);
-    const bool use_set = tn >= SET_MIN_DEG;
-    constexpr int TRY_BATCH = N2V_BATCH;
-    for (int it = 0;; it += TRY_BATCH) {
-      int32_t x[TRY_BATCH], v[TRY_BATCH];
-      float y[TRY_BATCH];
-      int n_try = TRY_BATCH;  // the round ends at the first try that is sure to accept
-#pragma unroll
-      for (int k = 0; k < TRY_BATCH; k++) {
-        if (k < n_try) {
-          x[k] = rng.rand_int(n);
-          y[k] = __fmul_rn(rng.uniform(), bound);
-          if (y[k] < sure) n_try = k + 1;
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < TRY_BATCH; k++) v[k] = k < n_try ? ld_graph<STREAM>(edges + x[k]) : -1;
-      // membership gathers of the tries that need one, issued together
-      bool is_ret[TRY_BATCH], need[TRY_BATCH];
-      uint32_t bucket[TRY_BATCH];
-      int4 ba[TRY_BATCH], bb[TRY_BATCH];
-#pragma unroll
-      for (int k = 0; k < TRY_BATCH; k++) {
-        is_ret[k] = wp.n2v_compat ? (x[k] == t) : (v[k] == t);  // randomWalks.cu:159 compares the index
-        need[k] = k < n_try && !is_ret[k] && y[k] >= lo && y[k] < hi;
-        bucket[k] = set_bucket(v[k], n_buckets);
-        if (need[k] && use_set) {
-          ba[k] = ld_graph<STREAM>(region + 2 * (size_t)bucket[k]);
-          bb[k] = ld_graph<STREAM>(region + 2 * (size_t)bucket[k] + 1);
-        } else {
-          ba[k] = make_int4(SET_EMPTY, SET_EMPTY, SET_EMPTY, SET_EMPTY);
-          bb[k] = ba[k];
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < TRY_BATCH; k++) {
-        if (k < n_try) {
-          ev.n2v_tries++;
-          bool accept;
-          if (is_ret[k]) {
-            accept = y[k] < wp.p;
-          } else if (!need[k]) {
-            accept = y[k] < lo;
-          } else {
-            bool found = ba[k].x == v[k] || ba[k].y == v[k] || ba[k].z == v[k] || ba[k].w == v[k] ||
-                         bb[k].x == v[k] || bb[k].y == v[k] || bb[k].z == v[k] || bb[k].w == v[k];
-            if (use_set) ev.n2v_probes += 8;
-            if (!found && (!use_set || bb[k].w != SET_EMPTY))
-              found = n2v_member_slow<STREAM>(g, wp.adjset, ts, tn, v[k], bucket[k], n_buckets, ev.n2v_probes);
-            accept = y[k] < (found ? inv_q : 1.0f);
-          }
-          if (accept) { state_t = transit; return v[k]; }
-        }
-      }
-      if (it > RETRY_CAP) {
-        atomicOr(status, ND_DEV_RETRY_LIMIT);
-        state_t = transit;
-        return v[n_try - 1 < 0 ? 0 : n_try - 1];
-      }
+    state_t = transit;
+    for (int it = 0; it <= RETRY_CAP; it += N2V_BATCH) {
+      const int32_t r = n2v_round<STREAM, N2V_BATCH>(g, wp, c, rs, n, t, ts, tn, rng, ev);
+      if (r != ROUND_AGAIN) return r;
     }
+    atomicOr(status, ND_DEV_RETRY_LIMIT);
+    return ld_graph<STREAM>(edges);
   }
   return -1;
 }
@@ -557,6 +585,93 @@ walk_sp_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_t S,
   if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
 }
 
+// Sample-parallel walks of the apps with a rejection loop, as a per-lane state machine.  In
+// walk_sp_kernel a warp spends, at every step, as many rounds as its unluckiest lane (about 2.2
+// rounds per step for node2vec although a walk needs 1.13 on average).  Here a loop trip is ONE
+// round for every lane, wherever its walk stands: a lane whose try was accepted moves on to its
+// next step (the row offsets of the new vertex are fetched at the end of the trip, so that the
+// next trip starts with them in registers), a lane that was rejected stays on its step, a lane
+// whose walk ended takes the next walk.  Over 100 steps the lanes' round counts even out, so a
+// warp makes about as many trips as the average walk needs rounds.  Draws are keyed by (sample,
+// step) and counted per step, so the walks are the same as in every other kernel.
+template <int APP>
+__global__ void __launch_bounds__(256, walk_min_ctas_sp<APP>())
+walk_sp_rounds_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_t S,
+                      const int32_t *__restrict__ initial, int32_t *__restrict__ tmp,
+                      int32_t *__restrict__ len, int *__restrict__ status, unsigned long long *__restrict__ stats) {
+  constexpr bool N2V = APP == ND_APP_NODE2VEC;
+  Events ev;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t s = blockIdx.x * (int64_t)blockDim.x + threadIdx.x - stride;
+  bool have = false, fresh = true;
+  int32_t cur = 0, rs = 0, deg = 0, prev = 0, ts = 0, tn = 0;
+  int step = 0, rounds = 0;
+  float max_w = 0.f;
+  Rng rng(wp.seed, 0u, 0u, 0u);
+  const N2vConsts c(wp);
+  bool done = false;  // this lane has no walk left
+  // every lane of the warp stays in the loop until the last one is done: the vote at the loop
+  // head is where the lanes meet again after a trip, so that a trip runs as one instruction stream
+  while (__any_sync(0xffffffffu, !done)) {
+    if (!done && !have) {  // take the next walk of this lane
+      s += stride;
+      if (s >= S) {
+        done = true;
+      } else {
+        cur = initial[s];
+        if (cur >= 0 && cur < g.V) {  // otherwise len is -1 already and the lane tries the next walk in the next trip
+          rs = __ldg(g.row_ptr + cur);
+          deg = __ldg(g.row_ptr + cur + 1) - rs;
+          if (!N2V) max_w = __ldg(g.max_w + cur);
+          step = 0;
+          have = true;
+          fresh = true;
+        }
+      }
+    }
+    if (have) {
+      int32_t nbr = ROUND_AGAIN;
+      if (deg == 0) {
+        nbr = -1;
+      } else if (fresh) {  // first trip of a step: the draws of the step start, the cases without a rejection loop
+        rng = Rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
+        rounds = 0;
+        fresh = false;
+        if (APP == ND_APP_PPR) {
+          const float pr = rng.uniform();
+          if (pr < wp.stop_prob) nbr = -1;
+        }
+        if (nbr == ROUND_AGAIN && (deg == 1 || (N2V && step == 0))) nbr = __ldg(g.col + rs);
+      }
+      if (nbr == ROUND_AGAIN) {
+        if (N2V) nbr = n2v_round<false, N2V_BATCH_SP>(g, wp, c, rs, deg, prev, ts, tn, rng, ev);
+        else nbr = weighted_round<false, 2>(wp, rs, deg, max_w, rng, ev);
+        if (nbr == ROUND_AGAIN && ++rounds > RETRY_CAP) {
+          atomicOr(status, ND_DEV_RETRY_LIMIT);
+          nbr = __ldg(g.col + rs);
+        }
+      }
+      if (nbr == -1) {  // the walk ends here
+        len[s] = step;
+        have = false;
+      } else if (nbr >= 0) {
+        tmp[(int64_t)step * S + s] = nbr;
+        prev = cur; ts = rs; tn = deg;
+        cur = nbr;
+        if (++step == wp.steps) {
+          have = false;
+        } else {
+          rs = __ldg(g.row_ptr + cur);
+          deg = __ldg(g.row_ptr + cur + 1) - rs;
+          if (!N2V) max_w = __ldg(g.max_w + cur);
+          fresh = true;
+        }
+      }  // ROUND_AGAIN: the lane stays on its step
+    }
+  }
+  ev.flush(stats);
+}
+
 // ---------------------------------------------------------------- finalize: step-major -> sample-major
 
 constexpr int FIN_SAMPLES = 32;   // samples per CTA
@@ -640,8 +755,13 @@ template <int APP>
 int launch_sp(nd_sampler *s, const WalkParams &wp) {
   const int64_t blocks = (s->S + 255) / 256;
   const int grid = (int)(blocks < (int64_t)s->dev.sms * 32 ? blocks : (int64_t)s->dev.sms * 32);
-  walk_sp_kernel<APP><<<grid, 256, 0, s->stream>>>(nd_view(s->g), wp, s->first, s->S, s->d_initial,
-                                                    s->d_tmp, s->d_len, s->d_status, s->d_stats);
+  static const bool plain = getenv("ND_SP_PLAIN") != nullptr;
+  if (APP == ND_APP_UNIFORM_WALK || plain)   // no rejection loop: one round per step for every lane anyway
+    walk_sp_kernel<APP><<<grid, 256, 0, s->stream>>>(nd_view(s->g), wp, s->first, s->S, s->d_initial,
+                                                      s->d_tmp, s->d_len, s->d_status, s->d_stats);
+  else
+    walk_sp_rounds_kernel<APP><<<grid, 256, 0, s->stream>>>(nd_view(s->g), wp, s->first, s->S, s->d_initial,
+                                                             s->d_tmp, s->d_len, s->d_status, s->d_stats);
   return ND_OK;
 }
 
