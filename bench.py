@@ -379,13 +379,15 @@ def main():
     copy_stream = torch.cuda.Stream()
     pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init_np, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
                                stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream)
+    # walks: in the sample-parallel mode, the one the reference's Python sample() runs (src/nextDoorPythonModule.cu:54-58)
+    e2e_mode = 2 if wl["kind"] == WALK else mode
     for _ in range(2):
-        pipe.run(init_pin, out_pin, mode)
+        pipe.run(init_pin, out_pin, e2e_mode)
     barrier()
     x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     x0.record(stream)
     for i in range(a.steps):                  # step i+1 starts sampling while the tail of step i is being copied
-        pipe.run_async(init_pin, out_pin if i % 2 == 0 else out_pin2, mode)
+        pipe.run_async(init_pin, out_pin if i % 2 == 0 else out_pin2, e2e_mode)
     pipe.wait()                               # every step's result has landed on the host
     x1.record(stream)
     barrier()
@@ -489,7 +491,7 @@ def main():
                        "sampled_edges_per_step_per_gpu": edges_step},
             "e2e": {"value": total_edges * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
                     "h2d_bytes_per_step": int(init_np.nbytes), "d2h_bytes_per_step": int(S * fs * 4),
-                    "chunks": E2E_CHUNKS, "depth": E2E_DEPTH, "valid_vertices_in_host_result": e2e_check},
+                    "chunks": E2E_CHUNKS, "depth": E2E_DEPTH, "mode": {0: "tp", 1: "tp_lb", 2: "sp"}[e2e_mode], "valid_vertices_in_host_result": e2e_check},
             "gpu_launches": int(launches),
             "sample_parallel": None if mode == 2 else {"value": total_edges * a.steps / (ms_sp * 1e-3), "unit": "sampled edges/s",
                                                        "note": "same sampler, same samples, nd_mode SampleParallel"},
