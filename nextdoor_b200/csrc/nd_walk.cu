@@ -14,6 +14,8 @@
 // Why no adjacency staging here: a walk draws one neighbour per visit, and at stationarity a
 // transit of degree d is visited by about d * S / E walks per step (1/32 of d on the 2^20-vertex
 // graph), so the visits touch fewer sectors than the list holds; staging pays for k-hop, not for walks.
+#include <mutex>
+
 #include "nd_common.cuh"
 #include "nd_philox.cuh"
 
@@ -767,8 +769,13 @@ int launch_sp(nd_sampler *s, const WalkParams &wp) {
 
 }  // namespace
 
+// The derived layouts of a graph are built by the first sampler that needs them; samplers of one
+// graph may be created from several host threads, so the builds are serialised.
+static std::mutex g_derived_mutex;
+
 // interleaved (neighbour id, weight) records of a graph, built on first use
 int nd_graph_ensure_colw(const nd_graph *g, int sms) {
+  std::lock_guard<std::mutex> lock(g_derived_mutex);
   if (g->colw || g->E == 0) return ND_OK;
   int2 *cw = nullptr;
   ND_CUDA(cudaMalloc(&cw, sizeof(int2) * (size_t)g->E));
@@ -876,6 +883,7 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_CUDA(cudaMalloc(&s->d_len, sizeof(int32_t) * (size_t)S));
   if (s->p.app == ND_APP_NODE2VEC) {
     ND_CUDA(cudaMalloc(&s->d_state, sizeof(int32_t) * (size_t)S));
+    std::lock_guard<std::mutex> lock(g_derived_mutex);
     if (!s->g->adjset) {  // 8 bytes per CSR entry, built once per graph
       const size_t slots = 8 * ((size_t)(s->g->E / 4) + 2);
       int32_t *set = nullptr;
