@@ -62,3 +62,15 @@ def test_bad_arguments_are_rejected(lib):
     assert lib.lib.nd_shard_range(10, 3, 3, C.byref(f), C.byref(c)) == 1
     assert b"bad argument" in lib.lib.nd_last_error()
     assert lib.lib.nd_sampler_sample(None, 0) == 1
+
+
+def test_header_is_plain_c_and_cxx():
+    """The boundary is a C ABI: the header must compile as C11 and as C++17 without any CUDA or
+    torch include."""
+    import shutil
+    import subprocess
+    hdr = os.path.join(ROOT, "include", "nextdoor_b200.h")
+    for cc, lang, std in (("gcc", "c", "-std=c11"), ("g++", "c++", "-std=c++17")):
+        exe = shutil.which(cc) or os.path.join("/usr/bin", cc)
+        r = subprocess.run([exe, std, "-fsyntax-only", "-Wall", "-x", lang, hdr], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr

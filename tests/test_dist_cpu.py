@@ -98,3 +98,27 @@ def test_partitioned_walk_two_ranks_equals_replicated_job():
         mp.spawn(_partitioned_worker, args=(world, _free_port(), 257, 15, ret), nprocs=world, join=True)
         assert ret["ok"]
         assert ret["sent"] > 0
+
+
+def test_partition_helpers_cover_the_graph_exactly():
+    """split_bounds / local_rows: the ranges tile [0, V), every CSR entry lands in exactly one
+    part, and a part's rows are the graph's rows with the foreign rows empty."""
+    sys.path.insert(0, ROOT)
+    from nextdoor_b200 import partitioned as ndp
+    from oracle import ndo
+    g = ndo.rmat_graph(700, 5000, seed=6)
+    for parts in (1, 2, 3, 8):
+        b = ndp.split_bounds(g.row_ptr, parts)
+        assert b[0] == 0 and b[-1] == g.V and (np.diff(b) >= 0).all()
+        total = 0
+        for r in range(parts):
+            rp, col, w = ndp.local_rows(g.row_ptr, g.col, g.w, int(b[r]), int(b[r + 1]))
+            assert rp.shape[0] == g.V + 1 and rp[0] == 0 and rp[-1] == col.shape[0] == w.shape[0]
+            deg = np.diff(rp)
+            assert (deg[: b[r]] == 0).all() and (deg[b[r + 1]:] == 0).all()
+            assert np.array_equal(deg[b[r]: b[r + 1]], np.diff(g.row_ptr)[b[r]: b[r + 1]])
+            assert np.array_equal(col, g.col[g.row_ptr[b[r]]: g.row_ptr[b[r + 1]]])
+            total += col.shape[0]
+        assert total == g.E
+        sizes = [int(g.row_ptr[b[r + 1]] - g.row_ptr[b[r]]) for r in range(parts)]
+        assert max(sizes) - min(sizes) <= 2 * int(np.diff(g.row_ptr).max())   # balanced up to one hub list
