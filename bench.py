@@ -1,15 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the sampling hot path: sampled edges/s, device-timed.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2] [--mode tp_lb]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c5] [--mode tp_lb]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-A "step" is one sample() pass over the whole batch of samples.  Default workload (one GPU):
-node2vec p=2 q=0.5, length 100, one walk per vertex, on a synthetic R-MAT graph with 2^20
-vertices and 16M undirected edges (seed 0, generated on the device), transit-parallel mode with
-load balancing.  With N ranks every rank holds a replica of the graph and samples its own range
-of seeds (weak scaling: rank r owns the samples [r*S, (r+1)*S)); no collective is on the data
-path, the final all-gather is timed separately.
+A "step" is one sample() pass over the whole job.  Default workload: weighted PPR, stop
+probability 0.15, maximum length 100, one walk per vertex, on a synthetic R-MAT graph with 2^24
+vertices and 256M undirected edges (seed 0, generated on the device), transit-parallel mode with
+load balancing.  With N ranks every rank holds a replica of the graph and ONE job is cut into
+contiguous seed ranges by the reference's rule (PartStartPointer / PartDivisionSize,
+src/utils.hpp:26-27; used at src/nextdoor.cu:2024-2025, 3221-3222): strong scaling, the draws are
+keyed by the global sample index, so the concatenated shards equal the 1-GPU output.  No collective
+is on the sampling path; the gather of the final samples to rank 0 is timed separately
+(`with_gather`).  Next to the main workload a short node2vec pass on the 2^20-vertex graph (workload
+c2) gives the roofline of the transit-parallel next() kernel the target is stated on
+(`c2_next_roofline`), and on one GPU the reference's own GPU build is timed on the same c2 graph
+(`reference_gpu`) when its binaries are present.
 
 Prints ONE JSON line (rank 0).  --impl reference times the reference's own next() bodies on the
 host cores (oracle/_ref, else the oracle port) on a bounded sample of the same workload.
@@ -104,14 +110,16 @@ def params_for(mod, wl, seed):
 
 
 def seeds_for(wl, first, S):
-    """Initial transits of samples [first, first+S): walks start sample i at vertex i % V; k-hop and
-    collective batches draw their seeds uniformly (numpy Philox stream keyed by the sample range)."""
+    """Initial transits of samples [first, first+S) of the job: walks start sample i at vertex i % V;
+    k-hop and collective batches draw their seeds uniformly (one numpy Philox stream for the whole
+    job, so a shard's seeds do not depend on how the job is cut)."""
     V = wl["V"]
     if wl["kind"] == WALK:
         return (np.arange(first, first + S, dtype=np.int64) % V).astype(np.int32)
     per = 1 if wl["kind"] == KHOP else wl["B"]
-    rng = np.random.Generator(np.random.Philox(key=first + 1))
-    return rng.integers(0, V, S * per, dtype=np.int64).astype(np.int32)
+    rng = np.random.Generator(np.random.Philox(key=1))
+    total = wl.get("S", V)
+    return rng.integers(0, V, total * per, dtype=np.int64).astype(np.int32)[first * per:(first + S) * per]
 
 
 def next_bytes(wl, st, mode):
@@ -148,20 +156,44 @@ def next_bytes(wl, st, mode):
     return (8 if app == 9 else 4) * st["union_ids"] + 8 * st["union_unique"] + 8 * edges
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the next() kernel, from the ncu captures
-# summarised under profiles/ (bytes; same workload and mode, warm caches)
-NCU_TRAFFIC = {("c2", "tp_lb"): 167.4e6}
+def ncu_traffic(workload, mode, pairs_per_launch):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the next() kernel, from the ncu
+    captures recorded in profiles/ncu_traffic.json (each entry names its capture command).  An entry
+    captured on a smaller case of the same kernel carries the pairs one captured launch processed
+    and is scaled to this run's launches by the pairs per launch."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            tab = json.load(f)
+    except Exception:
+        return None, None
+    e = tab.get(f"{workload}:{mode}")
+    if not e:
+        return None, None
+    b = float(e["dram_bytes_per_launch"])
+    if e.get("scale_by_pairs") and e.get("pairs_per_launch") and pairs_per_launch:
+        b *= pairs_per_launch / float(e["pairs_per_launch"])
+    return b, e.get("source")
+
+
+def build_probe():
+    """libnd_bench_probe.so beside this file (bench_probe.cu), compiled on first use if absent."""
+    so, src = os.path.join(ROOT, "libnd_bench_probe.so"), os.path.join(ROOT, "bench_probe.cu")
+    if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.run([os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc"), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+                        "-O3", "-shared", "-Xcompiler", "-fPIC", src, "-o", so], check=True, capture_output=True)
+    return so
 
 
 def gather_ceiling(wl, st, g, next_ms, next_launches, device):
     """The second ceiling of the walk kernels, measured live: next() is a few independent random
     4-byte gathers into the graph arrays per pair, and a GPU serves those at a rate set by the
-    arrays' footprint against the L2 (nd_probe_random_gather), far below the copy bandwidth that
+    arrays' footprint against the L2 (bench_probe.cu), far below the copy bandwidth that
     `peak` is.  graph_gathers = the gathers into graph-sized arrays one pass needs (uniform walk:
     one neighbour id per edge; weighted: one (id, weight) record per try; node2vec: one candidate
     per try + one set bucket per membership test), floor = graph_gathers / rate."""
     import ctypes as C
-    from nextdoor_b200._lib import lib, check
+    probe = C.CDLL(build_probe())
+    probe.nd_bench_random_gather.argtypes = [C.c_int, C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_double)]
     app = wl["app"]
     if app == 0:
         gathers, footprint = st["sampled_edges"], 4 * g.E
@@ -171,9 +203,10 @@ def gather_ceiling(wl, st, g, next_ms, next_launches, device):
         gathers, footprint = st["n2v_tries"] + st["n2v_probes"] // 8, 12 * g.E
     per_launch = max(int(gathers / max(next_launches, 1)), 1)
     rate = C.c_double(0.0)
-    check(lib.nd_probe_random_gather(device, int(footprint), 1 << 24, 3, C.byref(rate)))
     small = C.c_double(0.0)   # the same at the size of one launch: fixed launch and ramp costs included
-    check(lib.nd_probe_random_gather(device, int(footprint), per_launch, 20, C.byref(small)))
+    if probe.nd_bench_random_gather(device, int(footprint), 1 << 24, 3, C.byref(rate)) != 0 or \
+            probe.nd_bench_random_gather(device, int(footprint), per_launch, 20, C.byref(small)) != 0:
+        return None
     floor_ms = gathers / rate.value * 1e3
     return {"footprint_bytes": int(footprint), "rate_gathers_per_s": rate.value,
             "rate_at_launch_size": small.value, "graph_gathers_per_pass": int(gathers),
@@ -260,15 +293,175 @@ def partitioned_bench(a, wl, nd, torch, rank, world, local, seed):
         dist.destroy_process_group()
 
 
+def reference_arm(a, wl, seed):
+    """--impl reference: the reference's next() bodies (oracle/_ref) or the oracle port on all host
+    threads, each step a bounded prefix of the workload's samples."""
+    from oracle import ndo
+    V, M = wl["V"], wl["M"]
+    t0 = time.perf_counter()
+    hg = host_graph_cached(ndo, V, M, seed)   # same generator definition as the device one
+    t_graph = time.perf_counter() - t0
+    vals = []
+    for i in range(a.warmup + a.steps):
+        cb = cpu_baseline(hg, wl, seed, budget_s=6.0)
+        if i >= a.warmup:
+            vals.append(cb)
+    v = float(np.mean([c["value"] for c in vals]))
+    cb = dict(vals[-1], value=v)
+    print(json.dumps({
+        "impl": "reference", "metric": "sampled edges/sec", "value": v, "unit": "sampled edges/s", "n_gpus": a.gpus,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 * float(np.mean([c["seconds"] for c in vals])),
+        "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+        "config": {"workload": f"{a.workload}: {wl['desc']}", "host_graph_build_s": round(t_graph, 2)},
+        "cpu_baseline": cb, "e2e": {"value": v, "unit": "sampled edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def host_graph_cached(ndo, V, M, seed):
+    """The oracle's R-MAT graph on the host.  Building the 2^24-vertex graph takes minutes on the
+    host cores and the driver runs this arm once per GPU count, so the arrays are kept in the
+    system's temporary directory between runs of one box."""
+    import tempfile
+    if M < (1 << 26):
+        return ndo.rmat_graph(V, M, seed)
+    d = os.path.join(tempfile.gettempdir(), f"nd_b200_rmat_{V}_{M}_{seed}")
+    names = ("row_ptr", "col", "w", "max_w")
+    try:
+        if os.path.exists(os.path.join(d, "done")):
+            arrs = [np.load(os.path.join(d, n + ".npy")) for n in names]
+            if arrs[0].shape[0] == V + 1 and arrs[1].shape[0] == int(arrs[0][-1]):
+                return ndo.HostGraph(*arrs)
+    except Exception:
+        pass
+    hg = ndo.rmat_graph(V, M, seed)
+    try:
+        os.makedirs(d, exist_ok=True)
+        for n in names:
+            np.save(os.path.join(d, n + ".npy"), getattr(hg, n))
+        open(os.path.join(d, "done"), "w").close()
+    except Exception:
+        pass
+    return hg
+
+
+def next_kernel_name(nd, smp, mode):
+    """The next() kernel the library launches for this sampler and mode (asked from the library)."""
+    import ctypes as C
+    buf = C.create_string_buffer(128)
+    nd.check(nd.lib.nd_sampler_next_kernel(smp._h, mode, buf, 128))
+    return buf.value.decode()
+
+
+def timed_passes(torch, stream, barrier, fn, steps, warmup):
+    """`warmup` untimed and `steps` timed calls of fn() between barriers; device time in ms."""
+    for _ in range(warmup):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    barrier()
+    return e0.elapsed_time(e1)
+
+
+def roofline_of(nd, smp, wl, workload, mode_name, mode, ms_per_step, hbm_peak, peak_kind, device, with_gather_probe=True):
+    """One instrumented pass (an event pair around every launch; no graph replay) -> the roofline
+    object of the next() launches."""
+    smp.set_profiling(True)
+    smp.sample(mode)
+    ph = smp.phase_ms()
+    smp.set_profiling(False)
+    st = smp.stats()
+    nb = next_bytes(wl, st, mode)
+    if wl["kind"] != COLL:
+        next_ms, next_launches = ph["next"]
+    else:
+        next_ms, next_launches = ph["next"][0] + ph["collect"][0], ph["next"][1] + ph["collect"][1]
+    achieved = nb / (next_ms * 1e-3) / 1e9 if next_ms > 0 else 0.0
+    phase_sum = sum(v[0] for v in ph.values())
+    # the timed steps replay a CUDA graph, the instrumented pass does not: the same launches, scaled
+    # by their share of the instrumented pass, inside the replayed step
+    replay_ms = ms_per_step * next_ms / phase_sum if phase_sum > 0 and ms_per_step else None
+    pairs_per_launch = st["live_pairs"] / max(next_launches, 1) if wl["kind"] == WALK else None
+    traffic, traffic_src = ncu_traffic(workload, mode_name, pairs_per_launch)
+    gather = None
+    if wl["kind"] == WALK and with_gather_probe:
+        gather = gather_ceiling(wl, st, smp.graph, next_ms, next_launches, device)
+    r = {"bound": "hbm", "kernel": next_kernel_name(nd, smp, mode), "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+         "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": traffic, "traffic_source": traffic_src,
+         "launches": next_launches, "avg_launch_us": 1e3 * next_ms / max(next_launches, 1),
+         "avg_launch_us_in_replayed_step": 1e3 * replay_ms / max(next_launches, 1) if replay_ms else None,
+         "algorithmic_bytes_per_pass": nb, "random_gather": gather}
+    return r, ph, st
+
+
+def side_pass_c2(nd, torch, stream, barrier, local, seed, hbm_peak, peak_kind, steps):
+    """A short node2vec pass on the 2^20-vertex graph in the transit-parallel + load-balanced mode:
+    the kernel and workload the roofline target is stated on.  Every rank runs it (a replica each,
+    one walk per vertex); rank 0 reports."""
+    wl = WORKLOADS["c2"]
+    g = nd.Graph.rmat(wl["V"], wl["M"], seed, device=local)
+    pr = params_for(nd, wl, seed)
+    smp = nd.Sampler(g, pr, num_samples=wl["V"], first_sample=0, initial=seeds_for(wl, 0, wl["V"]))
+    smp.set_stream(stream.cuda_stream)
+    ms = timed_passes(torch, stream, barrier, lambda: smp.sample(1, sync=False), steps, 3) / steps
+    edges = smp.stats()["sampled_edges"]
+    r, ph, st = roofline_of(nd, smp, wl, "c2", "tp_lb", 1, ms, hbm_peak, peak_kind, local)
+    r.update({"workload": f"c2: {wl['desc']}", "mode": "tp_lb", "ms_per_step": ms, "value": edges / (ms * 1e-3),
+              "unit_of_value": "sampled edges/s (one GPU)", "phases_ms": {k: round(v[0], 4) for k, v in ph.items()}})
+    smp.free()
+    return r, g
+
+
+def reference_gpu_leg(g, wl, timeout=120):
+    """The reference's own GPU build (oracle/_ref/ref_gpu_*, compiled from the reference tree for
+    sm_100 where that tree is present) on the graph `g`, in its three modes; the figure is its own
+    "End to end time" print (src/nextdoor.cu:2965, :3194).  A baseline leg like cpu_baseline."""
+    import re
+    import tempfile
+    names = {0: "ref_gpu_uniform", 1: "ref_gpu_deepwalk", 2: "ref_gpu_ppr", 3: "ref_gpu_node2vec", 4: "ref_gpu_khop"}
+    exe = os.path.join(ROOT, "oracle", "_ref", names.get(wl["app"], "none"))
+    if not os.path.exists(exe):
+        return {"unavailable": "the reference's GPU build is not present (oracle/_ref/ref_gpu_*: built only where the reference tree is)"}
+    out = {"graph": "the c2 graph written as the reference's 12-byte binary edge list", "unit": "sampled edges/s"}
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "graph.bin")
+        row_ptr, col, w, _ = g.to_host()
+        rec = np.empty(col.shape[0], dtype=[("s", "<i4"), ("d", "<i4"), ("w", "<f4")])
+        rec["s"] = np.repeat(np.arange(g.V, dtype=np.int32), np.diff(row_ptr))
+        rec["d"], rec["w"] = col, w
+        rec.tofile(path)
+        del rec, row_ptr, col, w
+        for key, kernel, lb in (("tp", "TransitParallel", 0), ("tp_lb", "TransitParallel", 1), ("sp", "SampleParallel", 0)):
+            try:
+                r = subprocess.run([exe, path, kernel, str(lb), "1"], capture_output=True, text=True, timeout=timeout)
+            except subprocess.TimeoutExpired:
+                out[key] = None
+                out["error"] = f"{kernel} lb={lb}: no result within {timeout} s"
+                break      # no further run after one that did not end
+            t = re.search(r"End to end time ([0-9.eE+-]+) secs", r.stdout)
+            n = re.search(r"totalSampledVertices (\d+)", r.stdout)
+            if r.returncode != 0 or not t or not n or float(t.group(1)) <= 0:
+                out[key] = None
+                out["error"] = f"{kernel} lb={lb}: rc {r.returncode}: {(r.stderr or r.stdout)[-200:]}"
+                break
+            out[key] = int(n.group(1)) / float(t.group(1))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c2", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="c5", choices=list(WORKLOADS))
     ap.add_argument("--mode", default="tp_lb", choices=list(MODES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="skip the c2 roofline pass and the reference-GPU leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end and gather legs (kernel A/B runs)")
     ap.add_argument("--partitioned", action="store_true",
                     help="walk over the graph PARTITIONED across the ranks (nextdoor_b200.partitioned) instead of replicated; "
                          "walk workloads without node2vec; prints its own JSON line")
@@ -282,29 +475,11 @@ def main():
     seed = 0
     hbm_peak, peak_kind = peaks()
     V, M, app = wl["V"], wl["M"], wl["app"]
-    S = wl.get("S", V)
+    S_total = wl.get("S", V)
 
     if a.impl == "reference":
-        if rank != 0:
-            return
-        from oracle import ndo
-        t0 = time.perf_counter()
-        hg = ndo.rmat_graph(V, M, seed)      # same generator definition as the device one
-        t_graph = time.perf_counter() - t0
-        vals = []
-        for i in range(a.warmup + a.steps):
-            cb = cpu_baseline(hg, wl, seed, budget_s=6.0)
-            if i >= a.warmup:
-                vals.append(cb)
-        v = float(np.mean([c["value"] for c in vals]))
-        cb = dict(vals[-1], value=v)
-        print(json.dumps({
-            "impl": "reference", "metric": "sampled edges/sec", "value": v, "unit": "sampled edges/s", "n_gpus": a.gpus,
-            "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 * float(np.mean([c["seconds"] for c in vals])),
-            "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int32", "data": "synthetic",
-            "config": {"workload": f"{a.workload}: {wl['desc']}", "host_graph_build_s": round(t_graph, 2)},
-            "cpu_baseline": cb, "e2e": {"value": v, "unit": "sampled edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        if rank == 0:
+            reference_arm(a, wl, seed)
         return
 
     import torch
@@ -318,7 +493,7 @@ def main():
     mode = MODES[a.mode]
     g = nd.Graph.rmat(V, M, seed, device=local)
     pr = params_for(nd, wl, seed)
-    first = rank * S
+    first, S = nd.shard_range(S_total, rank, world)     # the reference's seed ranges: one job, cut N ways
     init_np = seeds_for(wl, first, S)
     smp = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=init_np)
     fs = smp.fs
@@ -345,94 +520,103 @@ def main():
     clocks = ClockSampler(local)
     clocks.start()
     l0 = nd.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(a.steps):
-        smp.sample(mode, sync=False)
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
+    ms = timed_passes(torch, stream, barrier, lambda: smp.sample(mode, sync=False), a.steps, 0)
     launches = nd.launch_count() - l0
     edges_step = smp.stats()["sampled_edges"]
 
     # ---- the same job in the reference's other kernel type (-k SampleParallel), for comparison
     ms_sp = None
     if mode != 2:
+        ms_sp = timed_passes(torch, stream, barrier, lambda: smp.sample(2, sync=False), a.steps, 2)
+
+    # ---- end to end through the public API with host buffers, in the SAME mode as `value`: seeds
+    # H2D from pinned memory, sample, result D2H into pinned memory, through
+    # nextdoor_b200.api.PipelinedSampler: the result of a step is copied on a second stream while
+    # the next step is sampled (two sampler sets alternate).
+    ms_e2e = e2e_check = d2h = None
+    if not a.no_e2e:
+        init_host = torch.from_numpy(init_np).pin_memory()
+        out_host = torch.empty(S * fs, dtype=torch.int32).pin_memory()
+        out_host2 = torch.empty(S * fs, dtype=torch.int32).pin_memory()   # consecutive steps land in alternating buffers
+        init_pin, out_pin, out_pin2 = init_host.numpy(), out_host.numpy(), out_host2.numpy()
+        copy_stream = torch.cuda.Stream()
+        pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init_np, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
+                                   stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream)
         for _ in range(2):
-            smp.sample(2, sync=False)
+            pipe.run(init_pin, out_pin, mode)
         barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record(stream)
-        for _ in range(a.steps):
-            smp.sample(2, sync=False)
-        s1.record(stream)
+        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        x0.record(stream)
+        for i in range(a.steps):                  # step i+1 starts sampling while the tail of step i is being copied
+            pipe.run_async(init_pin, out_pin if i % 2 == 0 else out_pin2, mode)
+        pipe.wait()                               # every step's result has landed on the host
+        x1.record(stream)
         barrier()
-        ms_sp = s0.elapsed_time(s1)
-
-    # ---- end to end through the public API with host buffers: seeds H2D from pinned memory,
-    # sample, result D2H into pinned memory, through nextdoor_b200.api.PipelinedSampler: the result of a
-    # step is copied on a second stream while the next step is sampled (two sampler sets alternate).
-    init_host = torch.from_numpy(init_np).pin_memory()
-    out_host = torch.empty(S * fs, dtype=torch.int32).pin_memory()
-    out_host2 = torch.empty(S * fs, dtype=torch.int32).pin_memory()   # consecutive steps land in alternating buffers
-    init_pin, out_pin, out_pin2 = init_host.numpy(), out_host.numpy(), out_host2.numpy()
-    copy_stream = torch.cuda.Stream()
-    pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init_np, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
-                               stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream)
-    # walks: in the sample-parallel mode, the one the reference's Python sample() runs (src/nextDoorPythonModule.cu:54-58)
-    e2e_mode = 2 if wl["kind"] == WALK else mode
-    for _ in range(2):
-        pipe.run(init_pin, out_pin, e2e_mode)
-    barrier()
-    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    x0.record(stream)
-    for i in range(a.steps):                  # step i+1 starts sampling while the tail of step i is being copied
-        pipe.run_async(init_pin, out_pin if i % 2 == 0 else out_pin2, e2e_mode)
-    pipe.wait()                               # every step's result has landed on the host
-    x1.record(stream)
-    barrier()
-    if a.steps % 2 == 0:
-        out_pin = out_pin2                    # the buffer the last step wrote
+        ms_e2e = x0.elapsed_time(x1)
+        last_pin = out_pin if a.steps % 2 == 1 else out_pin2    # the buffer the last step wrote
+        e2e_check = int((last_pin != V).sum()) if wl["kind"] != COLL else None
+        pipe.free()
+        # the ceiling of that leg: the same result copy alone (every rank at once, nothing sampled)
+        src = torch.empty(S * fs, dtype=torch.int32, device="cuda")
+        for _ in range(1):
+            out_host.copy_(src, non_blocking=True)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record(stream)
+        for _ in range(2):
+            out_host.copy_(src, non_blocking=True)
+        c1.record(stream)
+        barrier()
+        d2h = c0.elapsed_time(c1) / 2
+        del src, out_host, out_host2, init_host
     clocks.stop_flag = True
-    ms_e2e = x0.elapsed_time(x1)
-    e2e_check = int((out_pin != V).sum()) if wl["kind"] != COLL else None
-    pipe.free()
 
-    # ---- the final sample gather (the only step that crosses NVLink): sample() + NCCL all-gather
+    # ---- the final sample gather (the only step that crosses NVLink): every rank sends its shard to
+    # rank 0, which holds the whole job's [S_total, finalSampleSize] array (getFinalSamples,
+    # src/nextdoor.cu:3211-3237).  Two samplers alternate: the transfer of a step's samples runs on
+    # NCCL's stream while the next step is sampled; a sampler's next run waits for the transfer
+    # that still reads its buffer.
     ms_gather = None
-    if world > 1:
-        # two samplers alternate: the all-gather of a step's samples runs on NCCL's stream while the
-        # next step is sampled; a sampler's next run waits for the gather that still reads its buffer
+    if world > 1 and not a.no_e2e:
         from nextdoor_b200 import dist as nd_dist
         smp2 = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=init_np)
         smp2.set_stream(stream.cuda_stream)
         pair = [(smp, nd_dist.device_samples(smp)), (smp2, nd_dist.device_samples(smp2))]
-        # (two gathered arrays; when they would not fit comfortably -- the 2^24-vertex workload on 8 GPUs
-        # gathers 54 GB -- one array is used and a gather waits for the previous one: less overlap)
-        n_full = 2 if 2 * world * S * fs * 4 < (48 << 30) else 1
-        fulls = [torch.empty((world * S, fs), dtype=torch.int32, device="cuda") for _ in range(n_full)]
+        ranges = [nd.shard_range(S_total, r, world) for r in range(world)]
+        n_full = 2 if 2 * S_total * fs * 4 < (48 << 30) else 1
+        fulls = [torch.empty((S_total, fs), dtype=torch.int32, device="cuda") for _ in range(n_full)] if rank == 0 else []
         side = torch.cuda.Stream()
         pending = [None, None]
+
+        def wait_all(k):
+            if pending[k] is not None:
+                for wk in pending[k]:
+                    wk.wait()
+                pending[k] = None
 
         def gather_step(i):
             k = i % 2
             s_k, shard_k = pair[k]
-            if pending[k] is not None:
-                pending[k].wait()
+            wait_all(k)
             s_k.sample(mode, sync=False)
             ev = torch.cuda.Event()
             ev.record(stream)
-            if n_full == 1 and pending[k ^ 1] is not None:
-                pending[k ^ 1].wait()          # the single gathered array is still being written
+            if n_full == 1:
+                wait_all(k ^ 1)                # the single gathered array is still being written
             with torch.cuda.stream(side):
                 side.wait_event(ev)
-                pending[k] = dist.all_gather_into_tensor(fulls[k % n_full], shard_k, async_op=True)
+                if rank == 0:
+                    full = fulls[k % n_full]
+                    full[first:first + S].copy_(shard_k, non_blocking=True)
+                    ops = [dist.P2POp(dist.irecv, full[f:f + c], r) for r, (f, c) in enumerate(ranges) if r != 0 and c > 0]
+                else:
+                    ops = [dist.P2POp(dist.isend, shard_k, 0)] if S > 0 else []
+                pending[k] = dist.batch_isend_irecv(ops) if ops else None
 
         def gather_drain():
             for k in range(2):
-                if pending[k] is not None:
-                    pending[k].wait()
-                    pending[k] = None
+                wait_all(k)
+            side.synchronize()
 
         for i in range(2):
             gather_step(i)
@@ -446,63 +630,75 @@ def main():
         y1.record(stream)
         barrier()
         ms_gather = y0.elapsed_time(y1)
-        gather_ok = bool((fulls[((a.steps - 1) % 2) % n_full][rank * S:(rank + 1) * S] == pair[(a.steps - 1) % 2][1]).all())
-        assert gather_ok, "the gathered array does not hold this rank's shard"
+        if rank == 0:      # the gathered array holds the job: its valid vertices are the job's sampled edges (checked below)
+            gathered_edges = int((fulls[((a.steps - 1) % 2) % n_full] != V).sum()) if wl["kind"] != COLL else None
         del fulls
         smp2.free()
 
     # ---- per-phase device time of one instrumented pass (roofline of the next() kernels)
-    smp.set_profiling(True)
-    smp.sample(mode)
-    ph = smp.phase_ms()
-    smp.set_profiling(False)
-    st = smp.stats()
+    roof, ph, st = roofline_of(nd, smp, wl, a.workload, a.mode, mode, ms / a.steps, hbm_peak, peak_kind, local,
+                               with_gather_probe=(rank == 0))
 
-    tms = torch.tensor([ms, ms_e2e, ms_gather or 0.0, ms_sp or 0.0], dtype=torch.float64, device="cuda")
-    tot = torch.tensor([float(edges_step)], dtype=torch.float64, device="cuda")
+    tms = torch.tensor([ms, ms_e2e or 0.0, ms_gather or 0.0, ms_sp or 0.0, d2h or 0.0], dtype=torch.float64, device="cuda")
+    tot = torch.tensor([float(edges_step), float(e2e_check or 0)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-    ms, ms_e2e, ms_gather, ms_sp = float(tms[0]), float(tms[1]), float(tms[2]), float(tms[3])
-    total_edges = float(tot[0])
+    ms, ms_e2e, ms_gather, ms_sp, d2h = (float(x) for x in tms)
+    total_edges, e2e_total = float(tot[0]), float(tot[1])
+    if world > 1 and ms_gather and rank == 0 and gathered_edges is not None:
+        assert gathered_edges == int(total_edges), "the array gathered on rank 0 does not hold the whole job"
+
+    # ---- cpu baseline (one GPU only), then the main sampler's buffers are released for the side passes
+    cb = None
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        from oracle import ndo
+        row_ptr, col, w, mw = g.to_host()
+        cb = cpu_baseline(ndo.HostGraph(row_ptr, col, w, mw), wl, seed)
+        del row_ptr, col, w, mw
+    graph_desc = f"R-MAT a=.57 b=.19 c=.19 d=.05 seed 0, V={V}, CSR entries={g.E}, max degree={g.max_degree}"
+    smp.free()
+    g.free()
+
+    # ---- the kernel the roofline target is stated on, and the reference's GPU build beside it
+    c2_roof = ref_gpu = None
+    if not a.no_side and a.workload != "c2":
+        c2_roof, g2 = side_pass_c2(nd, torch, stream, barrier, local, seed, hbm_peak, peak_kind, a.steps)
+        if rank == 0 and world == 1:
+            ref_gpu = reference_gpu_leg(g2, WORKLOADS["c2"])
+        g2.free()
+        barrier()
 
     if rank == 0:
-        nb = next_bytes(wl, st, mode)
-        next_ms, next_launches = ph["next"] if wl["kind"] != COLL else (ph["next"][0] + ph["collect"][0], ph["next"][1] + ph["collect"][1])
-        achieved = nb / (next_ms * 1e-3) / 1e9 if next_ms > 0 else 0.0
-        kernel = {WALK: {0: "walk_next_tp_kernel", 1: "walk_next_count_kernel", 2: "walk_sp_kernel"}[mode],
-                  KHOP: "khop_pairs_kernel + khop_staged_kernel" if mode == 1 else "khop_pairs_kernel",
-                  COLL: "coll_gather/sort/weigh/sample kernels"}[wl["kind"]]
-        kernel = kernel if wl["kind"] != COLL else "coll_bitmap_kernel"
-        gather = gather_ceiling(wl, st, g, next_ms, next_launches, torch.cuda.current_device()) if wl["kind"] == WALK else None
-        cb = None
-        if world == 1 and not a.no_cpu_baseline:
-            from oracle import ndo
-            row_ptr, col, w, mw = g.to_host()
-            cb = cpu_baseline(ndo.HostGraph(row_ptr, col, w, mw), wl, seed)
+        per_step = total_edges
         line = {
-            "metric": "sampled edges/sec", "value": total_edges * a.steps / (ms * 1e-3), "unit": "sampled edges/s",
+            "metric": "sampled edges/sec", "value": per_step * a.steps / (ms * 1e-3), "unit": "sampled edges/s",
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
             "config": {"workload": f"{a.workload}: {wl['desc']}", "app": APP_NAMES[app], "mode": a.mode,
-                       "samples_per_gpu": S, "final_sample_size": fs,
-                       "graph": f"R-MAT a=.57 b=.19 c=.19 d=.05 seed 0, V={V}, CSR entries={g.E}, max degree={g.max_degree}",
+                       "samples_total": S_total, "samples_rank0": S, "final_sample_size": fs,
+                       "sharding": "one job, contiguous seed ranges (src/utils.hpp:26-27), graph replicated per GPU",
+                       "graph": graph_desc,
                        "l2": "working set (graph + sample buffers) larger than L2; no flush between steps",
-                       "sampled_edges_per_step_per_gpu": edges_step},
-            "e2e": {"value": total_edges * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
-                    "h2d_bytes_per_step": int(init_np.nbytes), "d2h_bytes_per_step": int(S * fs * 4),
-                    "chunks": E2E_CHUNKS, "depth": E2E_DEPTH, "mode": {0: "tp", 1: "tp_lb", 2: "sp"}[e2e_mode], "valid_vertices_in_host_result": e2e_check},
+                       "sampled_edges_per_step": per_step},
+            "e2e": None if ms_e2e is None or ms_e2e <= 0 else {
+                "value": per_step * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
+                "h2d_bytes_per_step": int(4 * S_total * smp.isz), "d2h_bytes_per_step": int(S_total * fs * 4),
+                "chunks": E2E_CHUNKS, "depth": E2E_DEPTH, "mode": a.mode, "valid_vertices_in_host_result": int(e2e_total),
+                "d2h_ceiling_gbs": S_total * fs * 4 / (d2h * 1e-3) / 1e9 if d2h else None,
+                "d2h_ceiling_note": "all ranks copying their shard of the result to pinned host memory at once, nothing else running; "
+                                    "aggregate GB/s; value <= d2h_ceiling / (4 * final_sample_size) * sampled edges per sample slot"},
             "gpu_launches": int(launches),
-            "sample_parallel": None if mode == 2 else {"value": total_edges * a.steps / (ms_sp * 1e-3), "unit": "sampled edges/s",
+            "sample_parallel": None if mode == 2 else {"value": per_step * a.steps / (ms_sp * 1e-3), "unit": "sampled edges/s",
                                                        "note": "same sampler, same samples, nd_mode SampleParallel"},
-            "with_gather": None if world == 1 else {
-                "value": total_edges * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",
-                "collective": "ncclAllGather of the final samples, overlapped with the next step's sampling (two samplers alternate)", "bytes_per_rank_per_step": int(S * fs * 4)},
-            "roofline": {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
-                         "traffic": NCU_TRAFFIC.get((a.workload, a.mode)),
-                         "launches": next_launches, "avg_launch_us": 1e3 * next_ms / max(next_launches, 1),
-                         "algorithmic_bytes_per_pass": nb, "random_gather": gather},
+            "with_gather": None if not ms_gather else {
+                "value": per_step * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",
+                "collective": "every rank sends its shard to rank 0 (NCCL send/recv), overlapped with the next step's sampling (two samplers alternate)",
+                "bytes_into_rank0_per_step": int((S_total - S) * fs * 4),
+                "floor_ms_at_770_GBps": (S_total - S) * fs * 4 / 770e9 * 1e3},
+            "roofline": roof,
+            "c2_next_roofline": c2_roof,
+            "reference_gpu": ref_gpu,
             "phases_ms": {k: round(v[0], 4) for k, v in ph.items()},
             "counters": st,
             "cpu_baseline": cb,

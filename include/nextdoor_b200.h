@@ -157,6 +157,11 @@ typedef enum nd_phase {
 } nd_phase;
 int nd_sampler_set_profiling(nd_sampler *s, int on);
 int nd_sampler_phase_ms(nd_sampler *s, float *ms, int32_t *launches, int n);
+/* Name of the next() kernel (for walks: with the app) that nd_sampler_sample(s, mode) launches: the
+ * reference picks its kernels by kernelType and the load-balancing flag (src/nextdoor.cu:2400-2928),
+ * this library also by app, graph size and its environment switches, so a measurement can label
+ * itself with what ran.  `name` receives at most n bytes including the terminator. */
+int nd_sampler_next_kernel(const nd_sampler *s, int mode, char *name, int n);
 /* freeDeviceData (src/nextdoor.cu:2088-2115) */
 int nd_sampler_destroy(nd_sampler *s);
 
@@ -180,6 +185,13 @@ int nd_invert_map(int device, int64_t n, int32_t *keys_in, int32_t *vals_in, int
  * stream capture begins. */
 int nd_invert_map_static(int device, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t invalid,
                          int32_t *keys_out, int32_t *vals_out, int64_t *n_live_out);
+/* The same on a stream of the caller's (a cudaStream_t): every copy and kernel is enqueued on
+ * `stream` and only that stream is waited for before the call returns, so work on the device's
+ * other streams is not held up.  nd_invert_map_static is this with stream = NULL, the legacy
+ * default stream, which synchronises with every blocking stream of the device.  No counterpart in
+ * the reference either. */
+int nd_invert_map_static_on(int device, void *stream, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t invalid,
+                            int32_t *keys_out, int32_t *vals_out, int64_t *n_live_out);
 int64_t nd_static_max_pairs(void);
 /* remove_duplicates_in_hop_per_block (src/distinct.cuh:1-111): every segment of seg_len ints is
  * sorted ascending, made unique, compacted to the front and padded with `invalid`;
@@ -203,6 +215,11 @@ int nd_walk_step(const nd_graph *g, const nd_app_params *p, int step, int64_t n,
  * a walk that ended comes back as all ones.  Device pointers, enqueued on `stream`. */
 int nd_walk_step_packed(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const uint64_t *d_walkers_in,
                         uint64_t *d_walkers_out, void *stream);
+/* Device status of nd_walk_step / nd_walk_step_packed on `device` (the reference aborts inside
+ * CHK_CU instead, src/utils.hpp:16): waits for `stream`, then *status receives the bits the step
+ * kernels have set since the last call (8 = a rejection loop hit its iteration cap and took
+ * edges[0]) and the word is cleared. */
+int nd_walk_step_status(int device, void *stream, int *status);
 /* Routing of packed walkers between the ranks of a partitioned job (no counterpart in the
  * reference, whose multi-GPU path replicates the graph, src/nextdoor.cu:1893-1911).  `d_bounds`
  * (device, parts + 1 int64) are the contiguous key ranges of the parts; the key of a walker is its
@@ -219,14 +236,6 @@ int nd_route_scatter(int device, int64_t n, const uint64_t *d_walkers, int by_sa
  * first_sample + count); d_out is the rank's [count, steps] result array. */
 int nd_records_store(int device, int64_t n, const uint64_t *d_records, int step, int64_t first_sample, int64_t count,
                      int steps, int32_t *d_out, void *stream);
-/* Measurement aid, no counterpart in the reference: the rate (gathers per second) at which this
- * GPU serves independent random 4-byte gathers from an array of footprint_bytes, n_gathers per
- * launch, averaged over `repeats` launches after two warm-up launches.  A walk step is a few such
- * gathers per (transit, sample) pair, so this rate -- not the copy bandwidth -- is the ceiling of
- * the next() kernels on graphs that do not fit the L2.  Allocates and frees its own array. */
-int nd_probe_random_gather(int device, int64_t footprint_bytes, int64_t n_gathers, int repeats,
-                           double *gathers_per_second);
-
 #ifdef __cplusplus
 }
 #endif

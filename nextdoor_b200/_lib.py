@@ -79,18 +79,20 @@ _SIGS = {
     "nd_sampler_stats": (C.c_int, [VP, VP, C.c_int]),
     "nd_sampler_set_profiling": (C.c_int, [VP, C.c_int]),
     "nd_sampler_phase_ms": (C.c_int, [VP, VP, VP, C.c_int]),
+    "nd_sampler_next_kernel": (C.c_int, [VP, C.c_int, C.c_char_p, C.c_int]),
     "nd_sampler_destroy": (C.c_int, [VP]),
     "nd_invert_map": (C.c_int, [C.c_int, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
     "nd_invert_map_static": (C.c_int, [C.c_int, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
+    "nd_invert_map_static_on": (C.c_int, [C.c_int, VP, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
     "nd_static_max_pairs": (C.c_int64, []),
     "nd_distinct_segments":(C.c_int, [C.c_int, VP, C.c_int64, C.c_int32, C.c_int32, VP]),
     "nd_philox_uniform": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, VP, VP]),
     "nd_walk_step": (C.c_int, [VP, C.POINTER(AppParams), C.c_int, C.c_int64, VP, VP, VP, VP]),
     "nd_walk_step_packed": (C.c_int, [VP, C.POINTER(AppParams), C.c_int, C.c_int64, VP, VP, VP]),
+    "nd_walk_step_status": (C.c_int, [C.c_int, VP, C.POINTER(C.c_int)]),
     "nd_route_count": (C.c_int, [C.c_int, C.c_int64, VP, C.c_int, VP, C.c_int, VP, VP]),
     "nd_route_scatter": (C.c_int, [C.c_int, C.c_int64, VP, C.c_int, VP, C.c_int, VP, VP, VP, VP]),
     "nd_records_store": (C.c_int, [C.c_int, C.c_int64, VP, C.c_int, C.c_int64, C.c_int64, C.c_int, VP, VP]),
-    "nd_probe_random_gather": (C.c_int, [C.c_int, C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_double)]),
 }
 
 for _name, (_res, _args) in _SIGS.items():

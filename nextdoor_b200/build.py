@@ -25,15 +25,17 @@ def _newest_header():
     return max(os.path.getmtime(h) for h in hs)
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, extra=(), lib: str = LIB,
+          obj_dir: str = OBJ) -> str:
+    """`extra`: further nvcc flags (e.g. -D tuning macros) for a variant built into `lib` / `obj_dir`."""
+    os.makedirs(obj_dir, exist_ok=True)
     hdr = _newest_header()
     jobs = []
     for f in sources():
         src = os.path.join(CSRC, f)
-        obj = os.path.join(OBJ, f[:-3] + ".o")
+        obj = os.path.join(obj_dir, f[:-3] + ".o")
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr):
-            cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
+            cmd = [NVCC] + FLAGS + list(extra) + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):
@@ -45,14 +47,14 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         list(ex.map(run, jobs))
-    objs = [os.path.join(OBJ, f[:-3] + ".o") for f in sources()]
-    if jobs or not os.path.exists(LIB):
-        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs
+    objs = [os.path.join(obj_dir, f[:-3] + ".o") for f in sources()]
+    if jobs or not os.path.exists(lib):
+        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib] + objs
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":

@@ -2,6 +2,7 @@
 // timers and the single-operator entry points.  The reference's counterparts are named in
 // include/nextdoor_b200.h beside each declaration.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "nd_common.cuh"
@@ -53,19 +54,6 @@ void nd_phase_end(nd_sampler *s) {
 
 namespace {
 
-// independent random 4-byte gathers, one per thread and loop trip: the access pattern of a walk step
-__global__ void random_gather_kernel(const int32_t *__restrict__ a, uint64_t words, int64_t total, int32_t *sink, uint32_t salt) {
-  int32_t acc = 0;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    uint32_t x = (uint32_t)i ^ (salt * 0x9e3779b9u), y = (uint32_t)(i >> 32) + salt;
-    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
-    y = (y ^ x) * 0x85ebca6bu; y ^= y >> 13;
-    const uint64_t idx = (((uint64_t)y << 32) | x) % words;
-    acc ^= __ldg(a + idx);
-  }
-  if (acc == 0x5a5a5a5a) *sink = acc;  // never true for the fill pattern: keeps the loads alive
-}
-
 __global__ void philox_uniform_kernel(uint64_t seed, int64_t n, const uint32_t *__restrict__ t4, float *__restrict__ out) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -91,9 +79,10 @@ void free_sampler(nd_sampler *s) {
   for (int i = 0; i < 2; i++) { cudaFree(s->d_map_key[i]); cudaFree(s->d_map_val[i]); }
   cudaFree(s->d_init_key); cudaFree(s->d_init_val); cudaFree(s->d_nlive); cudaFree(s->d_stats); cudaFree(s->d_status);
   cudaFree(s->d_runs); cudaFree(s->d_bin_counts); cudaFree(s->d_hop_counts);
-  cudaFree(s->d_adj_row); cudaFree(s->d_adj_col); cudaFree(s->d_prob); cudaFree(s->d_cand); cudaFree(s->d_cand_w); cudaFree(s->d_acc);
+  cudaFree(s->d_adj_row); cudaFree(s->d_adj_col); cudaFree(s->d_prob); cudaFree(s->d_cand); cudaFree(s->d_cand_w); cudaFree(s->d_acc); cudaFree(s->d_bm);
   cudaFree(s->d_cnt); cudaFree(s->d_offs); cudaFree(s->d_bsum); cudaFree(s->d_rank);
-  for (int i = 0; i < 2; i++) { cudaFree(s->d_lb_key[i]); cudaFree(s->d_prev[i]); }
+  for (int i = 0; i < 2; i++) cudaFree(s->d_srec[i]);
+  cudaFree(s->d_init_rec); cudaFree(s->d_uext);
   for (int i = 0; i < 3; i++) if (s->graph_exec[i]) cudaGraphExecDestroy(s->graph_exec[i]);
   if (s->copy_event) cudaEventDestroy(s->copy_event);
   if (s->copy_done) cudaEventDestroy(s->copy_done);
@@ -167,6 +156,9 @@ int nd_sampler_create(const nd_graph *g, const nd_app_params *p, int64_t num_sam
   ND_REQUIRE(first_sample + num_samples <= 0xffffffffll, ND_ERR_RANGE, "global sample index exceeds 32 bits");
   ND_REQUIRE(num_samples * (int64_t)nd_final_sample_size(p) < ((int64_t)1 << 40), ND_ERR_RANGE, "output too large");
   ND_CUDA(cudaSetDevice(g->device));
+  if (const char *fg = getenv("ND_L2_FETCH")) {  // experiment: L2 fetch granularity of this context (32, 64 or 128 bytes)
+    if (cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, (size_t)atoi(fg)) != cudaSuccess) cudaGetLastError();
+  }
   nd_sampler *s = new nd_sampler();
   s->g = g;
   s->p = *p;
@@ -339,6 +331,28 @@ int nd_sampler_phase_ms(nd_sampler *s, float *ms, int32_t *launches, int n) {
   return ND_OK;
 }
 
+int nd_sampler_next_kernel(const nd_sampler *s, int mode, char *name, int n) {
+  ND_REQUIRE(s && name && n > 0, ND_ERR_ARG, "nd_sampler_next_kernel: bad argument");
+  ND_REQUIRE(mode >= ND_MODE_TRANSIT_PARALLEL && mode <= ND_MODE_SAMPLE_PARALLEL, ND_ERR_ARG, "unknown mode %d", mode);
+  static const char *const walk_app[] = {"uniform walk", "DeepWalk", "PPR", "node2vec"};
+  const int app = s->p.app;
+  if (nd_is_walk(app)) {
+    const char *k = mode == ND_MODE_TRANSIT_PARALLEL ? "walk_next_tp_kernel"
+                    : mode == ND_MODE_TRANSIT_PARALLEL_LB ? "walk_next_count_kernel"
+                    : (app == ND_APP_UNIFORM_WALK || getenv("ND_SP_PLAIN")) ? "walk_sp_kernel" : "walk_sp_rounds_kernel";
+    snprintf(name, (size_t)n, "%s<%s>", k, walk_app[app]);
+  } else if (nd_is_khop(app)) {
+    const char *e = getenv("ND_KHOP_STAGING");
+    const bool staged = mode == ND_MODE_TRANSIT_PARALLEL_LB && e && e[0] == '1';
+    snprintf(name, (size_t)n, "%s", staged ? "khop_bin_kernel + khop_pairs_kernel + khop_staged_kernel" : "khop_pairs_kernel");
+  } else if (app == ND_APP_FASTGCN_REF || app == ND_APP_LADIES_REF) {
+    snprintf(name, (size_t)n, "coll_ref_kernel");
+  } else {
+    snprintf(name, (size_t)n, "%s", nd_collective_kernel_name(s));
+  }
+  return ND_OK;
+}
+
 int nd_sampler_destroy(nd_sampler *s) {
   if (!s) return ND_OK;
   cudaSetDevice(s->g->device);
@@ -413,37 +427,10 @@ int nd_walk_step_packed(const nd_graph *g, const nd_app_params *p, int step, int
   return nd_walk_step_packed_launch(g, p, step, n, d_walkers_in, d_walkers_out, (cudaStream_t)stream);
 }
 
-int nd_probe_random_gather(int device, int64_t footprint_bytes, int64_t n_gathers, int repeats,
-                           double *gathers_per_second) {
-  ND_REQUIRE(footprint_bytes >= 4 && n_gathers > 0 && repeats > 0 && gathers_per_second, ND_ERR_ARG,
-             "nd_probe_random_gather: bad argument");
+int nd_walk_step_status(int device, void *stream, int *status) {
+  ND_REQUIRE(status, ND_ERR_ARG, "nd_walk_step_status: null argument");
   ND_CUDA(cudaSetDevice(device));
-  NdDeviceInfo dev;
-  ND_TRY(nd_device_info(device, &dev));
-  const uint64_t words = (uint64_t)footprint_bytes / 4;
-  int32_t *a = nullptr, *sink = nullptr;
-  ND_CUDA(cudaMalloc(&a, words * 4));
-  ND_CUDA(cudaMalloc(&sink, 4));
-  ND_CUDA(cudaMemset(a, 1, words * 4));
-  cudaEvent_t e0, e1;
-  cudaEventCreate(&e0);
-  cudaEventCreate(&e1);
-  const int64_t blocks = (n_gathers + 255) / 256;
-  const int grid = (int)(blocks < (int64_t)dev.sms * 8 ? blocks : (int64_t)dev.sms * 8);
-  for (int r = 0; r < 2; r++) random_gather_kernel<<<grid, 256>>>(a, words, n_gathers, sink, (uint32_t)r);
-  cudaEventRecord(e0);
-  for (int r = 0; r < repeats; r++) random_gather_kernel<<<grid, 256>>>(a, words, n_gathers, sink, (uint32_t)(r + 2));
-  cudaEventRecord(e1);
-  const cudaError_t err = cudaEventSynchronize(e1);
-  float ms = 0.f;
-  cudaEventElapsedTime(&ms, e0, e1);
-  cudaEventDestroy(e0);
-  cudaEventDestroy(e1);
-  cudaFree(a);
-  cudaFree(sink);
-  ND_REQUIRE(err == cudaSuccess && ms > 0.f, ND_ERR_CUDA, "nd_probe_random_gather: %s", cudaGetErrorString(err));
-  *gathers_per_second = (double)n_gathers * repeats / ((double)ms * 1e-3);
-  return ND_OK;
+  return nd_walk_step_status_read((cudaStream_t)stream, status);
 }
 
 int nd_philox_uniform(int device, uint64_t seed, int64_t n, const uint32_t *tuples4, float *out) {

@@ -278,9 +278,17 @@ constexpr int BM_THREADS = 1024;
 constexpr int BM_GROUP_WORDS = 16;   // 512 candidates per group
 constexpr int BM_BIG_LIST = 4096;    // lists at least this long are streamed by the whole CTA
 
+// The bitmap, the group prefix counts and the group CDF make the "big" part (about V/8 + 3V/128
+// bytes); it lives in shared memory when the whole layout fits the CTA's opt-in shared memory
+// (graphs up to about 1.4 M vertices) and otherwise in a per-CTA slice of a global scratch array
+// (glob_bytes > 0), where the same code runs on L2-resident words.  The small part (transits,
+// layer, row sums, reduction scratch) is always in shared memory.
 struct BmLayout {
   int words, groups;
-  uint32_t off_gcdf, off_gpref, off_tr, off_layer, off_rowsum, off_red, bytes;
+  uint32_t off_gcdf, off_gpref;                        // inside the big part (the bitmap is at 0)
+  uint32_t off_tr, off_layer, off_rowsum, off_red;     // inside shared memory
+  uint32_t bytes;                                      // dynamic shared memory of the launch
+  uint32_t glob_bytes;                                 // per-CTA slice of the global scratch, 0 = big part in shared memory
 };
 
 __device__ __forceinline__ void bm_mark(uint32_t *bm, int32_t v) {
@@ -411,13 +419,14 @@ __device__ __forceinline__ void bm_scan_f64(double *a, int n, double *red) {
 
 template <bool LADIES>
 __global__ void __launch_bounds__(BM_THREADS, 1)
-coll_bitmap_kernel(NdGraphView g, CollParams cp, int steps, int64_t S, BmLayout lay, const int32_t *__restrict__ initial,
-                   int32_t *out, double *__restrict__ acc_all, int32_t *__restrict__ adj_row,
+coll_bitmap_kernel(NdGraphView g, CollParams cp, int steps, int64_t S, BmLayout lay, unsigned char *__restrict__ gscratch,
+                   const int32_t *__restrict__ initial, int32_t *out, double *__restrict__ acc_all, int32_t *__restrict__ adj_row,
                    int32_t *__restrict__ adj_col, float *__restrict__ prob, unsigned long long *__restrict__ stats) {
   extern __shared__ __align__(16) unsigned char bm_smem[];
-  uint32_t *bm = reinterpret_cast<uint32_t *>(bm_smem);
-  double *gcdf = reinterpret_cast<double *>(bm_smem + lay.off_gcdf);
-  uint32_t *gpref = reinterpret_cast<uint32_t *>(bm_smem + lay.off_gpref);
+  unsigned char *big = lay.glob_bytes ? gscratch + (size_t)blockIdx.x * lay.glob_bytes : bm_smem;
+  uint32_t *bm = reinterpret_cast<uint32_t *>(big);
+  double *gcdf = reinterpret_cast<double *>(big + lay.off_gcdf);
+  uint32_t *gpref = reinterpret_cast<uint32_t *>(big + lay.off_gpref);
   int32_t *sh_tr = reinterpret_cast<int32_t *>(bm_smem + lay.off_tr);
   int32_t *sh_layer = reinterpret_cast<int32_t *>(bm_smem + lay.off_layer);
   float *sh_rowsum = reinterpret_cast<float *>(bm_smem + lay.off_rowsum);
@@ -569,22 +578,37 @@ coll_bitmap_kernel(NdGraphView g, CollParams cp, int steps, int64_t S, BmLayout 
   }
 }
 
-static BmLayout bm_layout(int32_t V, int ntr_max, int L) {
+// shared memory the layout may use; ND_COLLECTIVE_BITMAP_GLOBAL=1 puts the big part into global
+// scratch whatever the graph's size (the tests use it to cover that path on small graphs)
+static int bm_smem_budget(const nd_sampler *s) {
+  const char *e = getenv("ND_COLLECTIVE_BITMAP_GLOBAL");
+  return e && e[0] == '1' ? 0 : s->dev.smem_optin;
+}
+
+static BmLayout bm_layout(int32_t V, int ntr_max, int L, int smem_optin) {
   BmLayout l;
   l.words = (int)((((int64_t)V + 31) / 32 + BM_GROUP_WORDS - 1) / BM_GROUP_WORDS * BM_GROUP_WORDS);
   l.groups = l.words / BM_GROUP_WORDS;
-  uint32_t off = 4u * (uint32_t)l.words;       // a multiple of 64
-  l.off_gcdf = off; off += 8u * (uint32_t)l.groups;
+  uint32_t big = 4u * (uint32_t)l.words;       // a multiple of 64
+  l.off_gcdf = big; big += 8u * (uint32_t)l.groups;
+  l.off_gpref = big; big += 4u * (uint32_t)(l.groups + 1);
+  big = (big + 255u) & ~255u;
+  const uint32_t small = 8u * 32u + 4u * 32u + 4u * (uint32_t)ntr_max + 4u * (uint32_t)L + 4u * (uint32_t)ntr_max;
+  const bool in_smem = (int64_t)big + small <= (int64_t)smem_optin;
+  uint32_t off = in_smem ? big : 0u;
   l.off_red = off; off += 8u * 32u + 4u * 32u;
-  l.off_gpref = off; off += 4u * (uint32_t)(l.groups + 1);
   l.off_tr = off; off += 4u * (uint32_t)ntr_max;
   l.off_layer = off; off += 4u * (uint32_t)L;
   l.off_rowsum = off; off += 4u * (uint32_t)ntr_max;
   l.bytes = off;
+  l.glob_bytes = in_smem ? 0u : big;
   return l;
 }
 
-__global__ void coll_reset_kernel(unsigned long long *stats) { if (threadIdx.x < 8) stats[threadIdx.x] = 0ull; }
+// clears the counters; stats[1] (live pairs) is known up front for these apps
+__global__ void coll_reset_kernel(unsigned long long *stats, unsigned long long pairs) {
+  if (threadIdx.x < 8) stats[threadIdx.x] = threadIdx.x == 1 ? pairs : 0ull;
+}
 
 }  // namespace
 
@@ -616,16 +640,16 @@ int nd_collective_alloc(nd_sampler *s) {
   ND_CUDA(cudaMalloc(&s->d_tmp, sizeof(int64_t) * (S1 + 1)));        // per-sample region offsets
   ND_CUDA(cudaMalloc(&s->d_nlive, sizeof(int32_t) * 4));
   if (p.app == ND_APP_FASTGCN_IS || p.app == ND_APP_LADIES_IS) {
-    // bitmap path when a bit per vertex (plus the group arrays) fits the opt-in shared memory of a CTA;
-    // ND_COLLECTIVE_SORT=1 forces the sort pipeline (used by the tests to keep it covered)
-    int optin = 0;
-    ND_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, s->g->device));
-    const BmLayout lay = bm_layout(s->g->V, B > L ? B : L, L);
+    // the union is built as a bitmap with a bit per vertex: in shared memory when it fits the CTA's
+    // opt-in shared memory, else in a per-CTA slice of global scratch; ND_COLLECTIVE_SORT=1 selects
+    // the sort pipeline instead (kept for the tests, which compare the two)
+    const BmLayout lay = bm_layout(s->g->V, B > L ? B : L, L, bm_smem_budget(s));
     const char *force = getenv("ND_COLLECTIVE_SORT");
     const bool ladies = p.app == ND_APP_LADIES_IS;
-    if ((int64_t)lay.bytes <= (int64_t)optin && B <= 1024 && L <= 1024 && !(force && force[0] == '1')) {
+    if (B <= 1024 && L <= 1024 && !(force && force[0] == '1')) {
       s->coll_bitmap = true;
       s->coll_grid = (int)std::min<int64_t>(S1, (int64_t)s->dev.sms);
+      if (lay.glob_bytes) ND_CUDA(cudaMalloc(&s->d_bm, (size_t)lay.glob_bytes * (size_t)s->coll_grid));
       if (ladies) {
         ND_CUDA(cudaFuncSetAttribute(coll_bitmap_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lay.bytes));
         ND_CUDA(cudaMalloc(&s->d_acc, sizeof(double) * (size_t)s->coll_grid * (size_t)s->g->V));
@@ -639,6 +663,11 @@ int nd_collective_alloc(nd_sampler *s) {
   return ND_OK;
 }
 
+const char *nd_collective_kernel_name(const nd_sampler *s) {
+  if (!s->coll_bitmap) return "coll_sizes/gather/weigh/sample kernels + radix sort";
+  return s->d_bm ? "coll_bitmap_kernel (bitmap in global scratch)" : "coll_bitmap_kernel (bitmap in shared memory)";
+}
+
 int nd_collective_sample(nd_sampler *s, int mode) {
   (void)mode;  // the reference runs next() of collective apps through sampleParallelKernel in every mode (src/nextdoor.cu:2900-2916)
   const nd_app_params &p = s->p;
@@ -648,10 +677,12 @@ int nd_collective_sample(nd_sampler *s, int mode) {
   CollParams cp;
   cp.seed = p.seed; cp.first_sample = s->first; cp.V = s->g->V; cp.fs = s->fs; cp.L = p.fanout[0]; cp.B = p.batch;
   cp.stride = (cp.B > cp.L ? cp.B : cp.L) * cp.L; cp.step = 0; cp.ntr = cp.B; cp.app = p.app;
-  coll_reset_kernel<<<1, 32, 0, st>>>(s->d_stats);
+  const bool ref_app = p.app == ND_APP_FASTGCN_REF || p.app == ND_APP_LADIES_REF;
+  const unsigned long long pairs = (unsigned long long)(S * (cp.B + (int64_t)(p.steps - 1) * cp.L));
+  coll_reset_kernel<<<1, 32, 0, st>>>(s->d_stats, s->coll_bitmap && !ref_app ? pairs : 0ull);
   nd_count_launches(1);
   const int grid = (int)std::min<int64_t>(S, (int64_t)s->dev.sms * 8);
-  if (p.app == ND_APP_FASTGCN_REF || p.app == ND_APP_LADIES_REF) {
+  if (ref_app) {
     nd_phase_begin(s, ND_PHASE_NEXT);
     coll_ref_kernel<<<grid, CTHREADS, 0, st>>>(gv, cp, p.steps, S, s->d_initial, s->d_out, s->d_adj_row, s->d_adj_col, s->d_stats);
     nd_phase_end(s);
@@ -659,24 +690,21 @@ int nd_collective_sample(nd_sampler *s, int mode) {
     ND_CUDA(cudaGetLastError());
     return ND_OK;
   }
-  if (s->coll_bitmap) {
-    const BmLayout lay = bm_layout(cp.V, cp.B > cp.L ? cp.B : cp.L, cp.L);
+  if (s->coll_bitmap) {  // one launch per layer, nothing comes back to the host: asynchronous like the walk and k-hop jobs
+    const BmLayout lay = bm_layout(cp.V, cp.B > cp.L ? cp.B : cp.L, cp.L, bm_smem_budget(s));
     for (int step = 0; step < p.steps; step++) {
       cp.step = step;
       cp.ntr = step == 0 ? cp.B : cp.L;
       nd_phase_begin(s, ND_PHASE_NEXT);
       if (p.app == ND_APP_LADIES_IS)
-        coll_bitmap_kernel<true><<<s->coll_grid, BM_THREADS, lay.bytes, st>>>(gv, cp, p.steps, S, lay, s->d_initial, s->d_out, s->d_acc,
+        coll_bitmap_kernel<true><<<s->coll_grid, BM_THREADS, lay.bytes, st>>>(gv, cp, p.steps, S, lay, s->d_bm, s->d_initial, s->d_out, s->d_acc,
                                                                              s->d_adj_row, s->d_adj_col, s->d_prob, s->d_stats);
       else
-        coll_bitmap_kernel<false><<<s->coll_grid, BM_THREADS, lay.bytes, st>>>(gv, cp, p.steps, S, lay, s->d_initial, s->d_out, nullptr,
+        coll_bitmap_kernel<false><<<s->coll_grid, BM_THREADS, lay.bytes, st>>>(gv, cp, p.steps, S, lay, s->d_bm, s->d_initial, s->d_out, nullptr,
                                                                               s->d_adj_row, s->d_adj_col, s->d_prob, s->d_stats);
       nd_phase_end(s);
       nd_count_launches(1);
     }
-    const unsigned long long pairs = (unsigned long long)(S * (cp.B + (int64_t)(p.steps - 1) * cp.L));
-    ND_CUDA(cudaMemcpyAsync(s->d_stats + 1, &pairs, sizeof(unsigned long long), cudaMemcpyHostToDevice, st));
-    ND_CUDA(cudaStreamSynchronize(st));
     ND_CUDA(cudaGetLastError());
     return ND_OK;
   }

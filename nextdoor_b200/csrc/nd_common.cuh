@@ -170,8 +170,11 @@ struct nd_sampler {
   // counting inversion of the walk maps: per-vertex counters, their exclusive scan, chunk sums, ranks
   uint32_t *d_cnt = nullptr, *d_offs = nullptr, *d_bsum = nullptr;
   int32_t *d_rank = nullptr;
-  int32_t *d_lb_key[2] = {nullptr, nullptr};   // second sorted map of the load-balanced walk loop
-  int32_t *d_prev[2] = {nullptr, nullptr};     // node2vec: previous vertex carried with the sorted map
+  // load-balanced walk loop: the transit-sorted map as records (8 bytes, node2vec 32 bytes), ping-pong,
+  // the initial map in the same form, and (node2vec) what next() hands to the scatter per pair
+  void *d_srec[2] = {nullptr, nullptr};
+  void *d_init_rec = nullptr;
+  int4 *d_uext = nullptr;
   // the step loop of a walk job captured once per mode and replayed (needs a non-default stream)
   cudaGraphExec_t graph_exec[3] = {nullptr, nullptr, nullptr};
   int graph_launches[3] = {0, 0, 0};
@@ -193,6 +196,7 @@ struct nd_sampler {
   bool coll_bitmap = false;       // importance sampling through the shared-memory bitmap kernel
   int coll_grid = 0;
   double *d_acc = nullptr;        // LADIES: per-CTA accumulators of the candidates' weights
+  unsigned char *d_bm = nullptr;  // per-CTA bitmap slices when a bit per vertex does not fit shared memory
 
   NdPhaseTimer timer;
   int64_t host_stats[8] = {0};
@@ -209,12 +213,15 @@ int nd_walk_step_packed_launch(const nd_graph *g, const nd_app_params *p, int st
 int nd_walk_step_launch(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const int32_t *d_transits,
                         const int64_t *d_samples, int32_t *d_next, cudaStream_t st);
 
+int nd_walk_step_status_read(cudaStream_t st, int *status);
+
 int nd_walk_alloc(nd_sampler *s);
 int nd_walk_sample(nd_sampler *s, int mode);
 int nd_khop_alloc(nd_sampler *s);
 int nd_khop_sample(nd_sampler *s, int mode);
 int nd_collective_alloc(nd_sampler *s);
 int nd_collective_sample(nd_sampler *s, int mode);
+const char *nd_collective_kernel_name(const nd_sampler *s);  // union path of the importance samplers
 int nd_sampler_build_initial_map(nd_sampler *s);
 
 int nd_graph_finish(nd_graph *g, cudaStream_t st);  // max_w (if null) + max_degree

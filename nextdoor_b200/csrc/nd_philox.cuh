@@ -61,6 +61,11 @@ struct Rng {
     draw++;
     return x;
   }
+  // continue at draw `d` of the invocation (the draws before it were consumed elsewhere)
+  __device__ __forceinline__ void seek(uint32_t d) {
+    draw = d;
+    if (d & 3u) philox4x32_10(sample, step, slot, d >> 2, k0, k1, lanes);
+  }
   __device__ __forceinline__ float uniform() { return u32_to_uniform(next_u32()); }
   __device__ __forceinline__ int32_t rand_int(int32_t n) { return rand_int_from(uniform(), n); }
 };

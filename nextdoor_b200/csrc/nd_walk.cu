@@ -16,6 +16,7 @@
 // graph), so the visits touch fewer sectors than the list holds; staging pays for k-hop, not for walks.
 #include <mutex>
 
+#include "nd_cache.cuh"
 #include "nd_common.cuh"
 #include "nd_philox.cuh"
 
@@ -221,6 +222,20 @@ __device__ __forceinline__ int32_t n2v_round(const NdGraphView &g, const WalkPar
   return ROUND_AGAIN;
 }
 
+// node2vec next() on a transit with n > 1 neighbours at a step > 0 when the row [ts, ts + tn) of the
+// previous vertex t is known already
+template <bool STREAM, int N2V_BATCH>
+__device__ __forceinline__ int32_t n2v_next_known(const NdGraphView &g, const WalkParams &wp, int32_t rs, int32_t n,
+                                                  int32_t t, int32_t ts, int32_t tn, Rng &rng, int *status, Events &ev) {
+  const N2vConsts c(wp);
+  for (int it = 0; it <= RETRY_CAP; it += N2V_BATCH) {
+    const int32_t r = n2v_round<STREAM, N2V_BATCH>(g, wp, c, rs, n, t, ts, tn, rng, ev);
+    if (r != ROUND_AGAIN) return r;
+  }
+  atomicOr(status, ND_DEV_RETRY_LIMIT);
+  return ld_graph<STREAM>(g.col + rs);
+}
+
 // One next() of the app on a transit with n > 0 neighbours; -1 = no vertex.
 template <int APP, bool STREAM = true, int N2V_BATCH = N2V_BATCH_COUNT>
 __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkParams &wp, int step,
@@ -247,17 +262,11 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
   }
   if (APP == ND_APP_NODE2VEC) {  // randomWalks.cu:141-172
     if (n == 1 || step == 0) { state_t = transit; return ld_graph<STREAM>(edges); }
-    const N2vConsts c(wp);
     const int32_t t = state_t;
     const int32_t ts = __ldg(g.row_ptr + t);
     const int32_t tn = __ldg(g.row_ptr + t + 1) - ts;
     state_t = transit;
-    for (int it = 0; it <= RETRY_CAP; it += N2V_BATCH) {
-      const int32_t r = n2v_round<STREAM, N2V_BATCH>(g, wp, c, rs, n, t, ts, tn, rng, ev);
-      if (r != ROUND_AGAIN) return r;
-    }
-    atomicOr(status, ND_DEV_RETRY_LIMIT);
-    return ld_graph<STREAM>(edges);
+    return n2v_next_known<STREAM, N2V_BATCH>(g, wp, rs, n, t, ts, tn, rng, status, ev);
   }
   return -1;
 }
@@ -417,57 +426,386 @@ constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_PER_THREAD = CNT_SUPER / SCAN_THREADS;   // 32 consecutive counters per thread
 constexpr int MAX_SMEM_BINS = 8192;                         // coarse bins kept in shared memory (V <= 2^25)
 
+// The kernel.  A (transit, sample) pair of a walk is a chain of dependent memory accesses (map
+// entry -> row offsets -> draws -> neighbour gather [-> set bucket] -> ticket), each a DRAM or L2
+// latency, and a launch holds only a few waves of threads: with one pair per thread the kernel
+// waits on that chain, wave after wave.  So
+//  * the CTAs are persistent (as many as are resident) and take tiles of 256 * PPT pairs; a
+//    thread works on PPT pairs at once, phase by phase, so the loads of a phase are in flight
+//    together (PPT chains overlap);
+//  * the first round of tries of every pair is straight-line code (no divergence); a pair that
+//    the first round does not settle (all tries rejected, or a membership test that has to walk
+//    past a full bucket: about one pair in eight) is put on a per-warp queue in shared memory,
+//    and whenever a queue holds 32 pairs the warp runs them through the general loop with all
+//    lanes busy.  The draws of a pair depend only on (sample, step), so the queue changes nothing;
+//  * the coarse histogram is flushed once per CTA.
+constexpr int COUNT_THREADS = 256;
+constexpr int COUNT_WARPS = COUNT_THREADS / 32;
+
+#ifndef ND_TUNE_PPT_UNIFORM
+#define ND_TUNE_PPT_UNIFORM 1
+#endif
+#ifndef ND_TUNE_PPT_WEIGHTED
+#define ND_TUNE_PPT_WEIGHTED 1
+#endif
+#ifndef ND_TUNE_PPT_N2V
+#define ND_TUNE_PPT_N2V 1
+#endif
+#ifndef ND_TUNE_N2V_FIRST
+#define ND_TUNE_N2V_FIRST 4
+#endif
+#ifndef ND_TUNE_WEIGHTED_INLINE
+#define ND_TUNE_WEIGHTED_INLINE 0
+#endif
+#ifndef ND_TUNE_GRID_PER_SM
+#define ND_TUNE_GRID_PER_SM 0   // CTAs per SM of a launch; 0 = as many as are resident
+#endif
+#ifndef ND_TUNE_CTAS_UNIFORM
+#define ND_TUNE_CTAS_UNIFORM 4
+#endif
+#ifndef ND_TUNE_CTAS_WEIGHTED
+#define ND_TUNE_CTAS_WEIGHTED 5
+#endif
+#ifndef ND_TUNE_CTAS_N2V
+#define ND_TUNE_CTAS_N2V 3
+#endif
+template <int APP>
+__host__ __device__ constexpr int count_ppt() {
+  return APP == ND_APP_NODE2VEC ? ND_TUNE_PPT_N2V : (APP == ND_APP_UNIFORM_WALK ? ND_TUNE_PPT_UNIFORM : ND_TUNE_PPT_WEIGHTED);
+}
+template <int APP>
+__host__ __device__ constexpr int count_ctas() {
+  return APP == ND_APP_NODE2VEC ? ND_TUNE_CTAS_N2V : (APP == ND_APP_UNIFORM_WALK ? ND_TUNE_CTAS_UNIFORM : ND_TUNE_CTAS_WEIGHTED);
+}
+constexpr int N2V_FIRST = ND_TUNE_N2V_FIRST;   // tries of the straight-line first round
+constexpr int WEIGHT_FIRST = 2;
+
+// A record of the transit-sorted map in the load-balanced mode.  One record = one aligned piece
+// of one 32-byte sector, so the scatter kernel places a pair with ONE random sector write:
+// {transit, sample} (8 bytes), or for node2vec 32 bytes {transit, sample, previous vertex, row
+// start of the previous vertex, its degree, 0, 0, 0} -- the previous vertex's row travels with
+// the pair, so next() never gathers row offsets by a random vertex id.
+template <bool N2V>
+struct MapRec {
+  int32_t t, s, pv;
+  int2 prow;
+};
+template <bool N2V>
+__host__ __device__ constexpr size_t map_rec_bytes() { return N2V ? 32 : 8; }
+
+template <bool N2V>
+__device__ __forceinline__ MapRec<N2V> map_rec_load(const ndmem::Keep &keep, const void *base, int i) {
+  MapRec<N2V> r;
+  if (N2V) {
+    const int4 *p = reinterpret_cast<const int4 *>(base) + 2 * (size_t)i;
+    const int4 a = keep.ld(p);
+    r.t = a.x; r.s = a.y; r.pv = a.z;
+    r.prow = make_int2(a.w, keep.ld(reinterpret_cast<const int32_t *>(p + 1)));
+  } else {
+    const int2 a = keep.ld(reinterpret_cast<const int2 *>(base) + i);
+    r.t = a.x; r.s = a.y; r.pv = 0;
+    r.prow = make_int2(0, 0);
+  }
+  return r;
+}
+
+// what the kernel writes for one settled pair
+template <bool COUNT>
+__device__ __forceinline__ void count_emit(const ndmem::Keep &keep, int i, int32_t s, int32_t nbr, int32_t V, int step,
+                                           bool smem_bins, uint32_t *sh_bins, int32_t *__restrict__ out_key,
+                                           int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
+                                           uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum,
+                                           int32_t *__restrict__ tmp_step, int32_t *__restrict__ len,
+                                           int4 *__restrict__ out_ext, int32_t t, int32_t rs, int32_t deg) {
+#ifndef ND_DIAG_NO_TMP
+  if (nbr >= 0) keep.st(tmp_step + s, nbr); else len[s] = step;
+#else
+  if (nbr < 0) len[s] = step;
+#endif
+  if (COUNT) {
+    keep.st(out_key + i, nbr >= 0 ? nbr : V);
+    if (nbr >= 0) {
+      keep.st(out_val + i, s);
+      keep.st(out_rank + i, (int32_t)keep.atom_add(cnt + nbr, 1u));
+      if (out_ext) keep.st(out_ext + i, make_int4(t, rs, deg, 0));  // node2vec: this transit is the pair's previous vertex next step
+      if (smem_bins) atomicAdd(&sh_bins[nbr >> CNT_SUPER_SHIFT], 1u);
+      else atomicAdd(&bsum[nbr >> CNT_SUPER_SHIFT], 1u);
+    }
+  }
+}
+
 template <int APP, bool COUNT>
-__global__ void __launch_bounds__(256, walk_min_ctas<APP>())
+__global__ void __launch_bounds__(COUNT_THREADS, count_ctas<APP>())
 walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample,
-                       const int32_t *__restrict__ in_key, const int32_t *__restrict__ in_val,
-                       const int32_t *__restrict__ in_prev, const int32_t *__restrict__ d_n,
+                       const void *__restrict__ in_rec, const int32_t *__restrict__ d_n,
                        int32_t *__restrict__ out_key, int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
-                       uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum, int bins, int32_t *__restrict__ tmp_step,
+                       int4 *__restrict__ out_ext, uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum, int bins, int32_t *__restrict__ tmp_step,
                        int32_t *__restrict__ len, int *__restrict__ status, unsigned long long *__restrict__ stats) {
-  extern __shared__ uint32_t sh_bins[];
+  constexpr int PPT = count_ppt<APP>();
+  constexpr int QCAP = 32 * PPT + 32;
+  constexpr bool N2V = APP == ND_APP_NODE2VEC;
+  constexpr bool WEIGHTED = APP == ND_APP_DEEPWALK || APP == ND_APP_PPR;
+  extern __shared__ uint32_t sh_dyn[];
   Events ev;
   const int n = *d_n;
-  if ((int64_t)blockIdx.x * blockDim.x >= n) return;  // no pair for this CTA
+  constexpr int TILE = COUNT_THREADS * PPT;
+  if ((int64_t)blockIdx.x * TILE >= n) return;  // no pair for this CTA
   const bool smem_bins = COUNT && bins <= MAX_SMEM_BINS;
+  uint32_t *sh_bins = sh_dyn;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int32_t *queue = reinterpret_cast<int32_t *>(sh_dyn + (smem_bins ? bins : 0)) + warp * QCAP;
+  int q_count = 0;  // warp-uniform
   if (smem_bins) {
 #pragma unroll 1
-    for (int b = threadIdx.x; b < bins; b += blockDim.x) sh_bins[b] = 0u;
+    for (int b = threadIdx.x; b < bins; b += COUNT_THREADS) sh_bins[b] = 0u;
     __syncthreads();
   }
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const int32_t t = in_key[i];
-    const int32_t s = in_val[i];
-    int32_t nbr = -1;
-    if (t < 0 || t >= g.V) {
-      atomicOr(status, ND_DEV_BAD_TRANSIT);
-    } else {
-      const int32_t rs = __ldg(g.row_ptr + t);
-      const int32_t deg = __ldg(g.row_ptr + t + 1) - rs;
-      if (deg > 0) {  // next() runs only on transits with edges (src/nextdoor.cu:255,412)
-        Rng rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
-        int32_t st = 0;
-        if (APP == ND_APP_NODE2VEC && step > 0) st = in_prev[i];
-        nbr = app_next<APP>(g, wp, step, t, rs, deg, st, rng, status, ev);
+  const N2vConsts c(wp);
+  const ndmem::Keep keep;
+
+  // runs 32 queued pairs (or the rest, when `all`) through the general loop.  A queue entry is the
+  // pair's position in the map; bit 31 set = the first round rejected all its tries, so the loop
+  // continues behind them in the pair's draw sequence; clear = the pair starts over (node2vec, a
+  // membership test that the home bucket did not answer).
+  constexpr uint32_t Q_CONTINUE = 0x80000000u;
+  auto drain = [&](bool all) {
+    while (q_count >= 32 || (all && q_count > 0)) {
+      const int take = q_count < 32 ? q_count : 32;
+      q_count -= take;
+      __syncwarp();
+      if (lane < take) {
+        const uint32_t q = (uint32_t)queue[q_count + lane];
+        const int i = (int)(q & ~Q_CONTINUE);
+        const bool cont = (q & Q_CONTINUE) != 0u;
+        const MapRec<N2V> r = map_rec_load<N2V>(keep, in_rec, i);
+        const int32_t rs = keep.ld_const(g.row_ptr + r.t);
+        const int32_t deg = keep.ld_const(g.row_ptr + r.t + 1) - rs;
+        Rng rng(wp.seed, (uint32_t)(first_sample + r.s), (uint32_t)step, 0u);
+        int32_t nbr = ROUND_AGAIN;
+        if (N2V) {
+          if (cont) { rng.seek(2u * N2V_FIRST); ev.n2v_tries += N2V_FIRST; }
+          nbr = n2v_next_known<true, N2V_BATCH_COUNT>(g, wp, rs, deg, r.pv, r.prow.x, r.prow.y, rng, status, ev);
+        } else if (WEIGHTED) {
+          rng.seek((APP == ND_APP_PPR ? 1u : 0u) + 2u * WEIGHT_FIRST);
+          ev.weight_tries += WEIGHT_FIRST;
+          const float max_w = __ldg(g.max_w + r.t);
+          for (int it = 0; it <= RETRY_CAP && nbr == ROUND_AGAIN; it += 2) nbr = weighted_round<true, 2>(wp, rs, deg, max_w, rng, ev);
+          if (nbr == ROUND_AGAIN) { atomicOr(status, ND_DEV_RETRY_LIMIT); nbr = __ldcs(g.col + rs); }
+        }
+        count_emit<COUNT>(keep, i, r.s, nbr, g.V, step, smem_bins, sh_bins, out_key, out_val, out_rank, cnt, bsum, tmp_step, len,
+                          out_ext, r.t, rs, deg);
+      }
+      __syncwarp();
+    }
+  };
+
+  for (int base = blockIdx.x * TILE; base < n; base += gridDim.x * TILE) {
+    int idx[PPT];
+    int32_t t[PPT], s[PPT], rs[PPT], deg[PPT], nbr[PPT];
+    bool live[PPT], settled[PPT], cont[PPT];
+    // ---- map entries
+    int32_t pv[PPT];
+    int2 prow[PPT];
+#pragma unroll
+    for (int k = 0; k < PPT; k++) {
+      idx[k] = base + k * COUNT_THREADS + threadIdx.x;
+      live[k] = idx[k] < n;
+      MapRec<N2V> r;
+      r.t = 0; r.s = 0; r.pv = 0; r.prow = make_int2(0, 0);
+      if (live[k]) r = map_rec_load<N2V>(keep, in_rec, idx[k]);
+      t[k] = r.t; s[k] = r.s; pv[k] = r.pv; prow[k] = r.prow;
+    }
+    // ---- row offsets
+#pragma unroll
+    for (int k = 0; k < PPT; k++) {
+      const bool ok = live[k] && t[k] >= 0 && t[k] < g.V;
+      if (live[k] && !ok) atomicOr(status, ND_DEV_BAD_TRANSIT);
+      rs[k] = ok ? keep.ld_const(g.row_ptr + t[k]) : 0;
+      deg[k] = ok ? keep.ld_const(g.row_ptr + t[k] + 1) - rs[k] : 0;
+      nbr[k] = -1;
+      cont[k] = WEIGHTED;  // a weighted pair is queued only after a full round of rejected tries
+      settled[k] = deg[k] <= 0;  // next() runs only on transits with edges (src/nextdoor.cu:255,412)
+    }
+    // ---- first round
+    if (APP == ND_APP_UNIFORM_WALK) {  // example/uniformRandWalk.cu:35-36
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
+        const int32_t x = rng.rand_int(deg[k] > 0 ? deg[k] : 1);
+#if defined(ND_DIAG_NO_GATHER)
+        if (deg[k] > 0) nbr[k] = (int32_t)(((uint32_t)(rs[k] + x) * 2654435761u) % (uint32_t)g.V);
+#elif defined(ND_DIAG_LDG)
+        if (deg[k] > 0) nbr[k] = __ldg(g.col + rs[k] + x);
+#else
+        if (deg[k] > 0) nbr[k] = __ldcs(g.col + rs[k] + x);
+#endif
+        settled[k] = true;
       }
     }
-    if (nbr >= 0) tmp_step[s] = nbr; else len[s] = step;
-    if (COUNT) {
-      out_key[i] = nbr >= 0 ? nbr : g.V;
-      if (nbr >= 0) {
-        out_val[i] = s;
-        out_rank[i] = (int32_t)atomicAdd(&cnt[nbr], 1u);
-        if (smem_bins) atomicAdd(&sh_bins[nbr >> CNT_SUPER_SHIFT], 1u);
-        else atomicAdd(&bsum[nbr >> CNT_SUPER_SHIFT], 1u);
+#if ND_TUNE_WEIGHTED_INLINE
+    if (WEIGHTED) {  // the rejection loop in place, one pair after the other
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        if (deg[k] > 0) {
+          Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
+          int32_t st = 0;
+          nbr[k] = app_next<APP>(g, wp, step, t[k], rs[k], deg[k], st, rng, status, ev);
+          settled[k] = true;
+        }
       }
+    }
+#else
+    if (WEIGHTED) {  // randomWalks.cu:74-90, 102-124
+      float mw[PPT], y[PPT][WEIGHT_FIRST];
+      int2 rec[PPT][WEIGHT_FIRST];
+      bool stop[PPT];
+#pragma unroll
+      for (int k = 0; k < PPT; k++) mw[k] = deg[k] > 1 ? __ldg(g.max_w + t[k]) : 0.f;
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
+        stop[k] = false;
+        if (APP == ND_APP_PPR) stop[k] = rng.uniform() < wp.stop_prob;
+        const bool go = deg[k] > 0 && !stop[k];
+#pragma unroll
+        for (int j = 0; j < WEIGHT_FIRST; j++) {
+          const int32_t x = rng.rand_int(deg[k] > 0 ? deg[k] : 1);   // a single neighbour: x = 0
+          y[k][j] = __fmul_rn(rng.uniform(), mw[k]);
+          rec[k][j] = go && (j == 0 || deg[k] > 1) ? __ldcs(wp.colw + rs[k] + x) : make_int2(-1, 0);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        if (deg[k] > 0) {
+          if (stop[k]) {
+            settled[k] = true;
+          } else if (deg[k] == 1) {
+            nbr[k] = rec[k][0].x;
+            settled[k] = true;
+          } else {
+            int32_t res = ROUND_AGAIN;
+            uint32_t tries = WEIGHT_FIRST;
+#pragma unroll
+            for (int j = WEIGHT_FIRST - 1; j >= 0; j--)
+              if (!(y[k][j] > __int_as_float(rec[k][j].y))) { res = rec[k][j].x; tries = j + 1; }
+            if (res != ROUND_AGAIN) { nbr[k] = res; settled[k] = true; ev.weight_tries += tries; }
+          }
+        }
+      }
+    }
+#endif
+    if (N2V) {  // randomWalks.cu:141-172
+      int32_t x[PPT][N2V_FIRST], v[PPT][N2V_FIRST];
+      float y[PPT][N2V_FIRST];
+      int n_try[PPT];
+      bool simple[PPT];
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        simple[k] = deg[k] == 1 || step == 0;
+        Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
+        n_try[k] = N2V_FIRST;
+#pragma unroll
+        for (int j = 0; j < N2V_FIRST; j++) {
+          x[k][j] = 0; y[k][j] = 0.f;
+          if (j < n_try[k]) {
+            x[k][j] = rng.rand_int(deg[k] > 0 ? deg[k] : 1);
+            y[k][j] = __fmul_rn(rng.uniform(), c.bound);
+            if (y[k][j] < c.sure) n_try[k] = j + 1;
+          }
+        }
+        if (simple[k]) { n_try[k] = 1; x[k][0] = 0; }
+        if (deg[k] <= 0) n_try[k] = 0;
+      }
+#pragma unroll
+      for (int k = 0; k < PPT; k++)
+#pragma unroll
+        for (int j = 0; j < N2V_FIRST; j++) v[k][j] = j < n_try[k] ? __ldcs(g.col + rs[k] + x[k][j]) : -1;
+      bool is_ret[PPT][N2V_FIRST], need[PPT][N2V_FIRST];
+      int4 ba[PPT][N2V_FIRST], bb[PPT][N2V_FIRST];
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        const int32_t ts = prow[k].x, tn = prow[k].y;
+        const uint32_t n_buckets = ((uint32_t)(ts + tn) >> 2) - ((uint32_t)ts >> 2);
+        const int4 *__restrict__ region = reinterpret_cast<const int4 *>(wp.adjset) + 2 * (size_t)((uint32_t)ts >> 2);
+#pragma unroll
+        for (int j = 0; j < N2V_FIRST; j++) {
+          is_ret[k][j] = wp.n2v_compat ? (x[k][j] == pv[k]) : (v[k][j] == pv[k]);  // randomWalks.cu:159 compares the index
+          need[k][j] = !simple[k] && j < n_try[k] && !is_ret[k][j] && y[k][j] >= c.lo && y[k][j] < c.hi;
+          const uint32_t bucket = set_bucket(v[k][j], n_buckets);
+          const bool fetch = need[k][j] && tn >= SET_MIN_DEG;
+          ba[k][j] = fetch ? __ldcs(region + 2 * (size_t)bucket) : make_int4(SET_EMPTY, SET_EMPTY, SET_EMPTY, SET_EMPTY);
+          bb[k][j] = fetch ? __ldcs(region + 2 * (size_t)bucket + 1) : make_int4(SET_EMPTY, SET_EMPTY, SET_EMPTY, SET_EMPTY);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        if (deg[k] > 0) {
+          if (simple[k]) {
+            nbr[k] = v[k][0];
+            settled[k] = true;
+          } else {
+            const bool use_set = prow[k].y >= SET_MIN_DEG;
+            int32_t res = ROUND_AGAIN;
+            uint32_t tries = (uint32_t)n_try[k], probes = 0;
+            bool slow = false;  // a membership test the home bucket does not answer, before any accepted try
+#pragma unroll
+            for (int j = N2V_FIRST - 1; j >= 0; j--) {
+              if (j < n_try[k]) {
+                bool accept, unsure = false;
+                uint32_t pj = 0;
+                if (is_ret[k][j]) {
+                  accept = y[k][j] < wp.p;
+                } else if (!need[k][j]) {
+                  accept = y[k][j] < c.lo;
+                } else {
+                  const int32_t vv = v[k][j];
+                  const bool found = ba[k][j].x == vv || ba[k][j].y == vv || ba[k][j].z == vv || ba[k][j].w == vv ||
+                                     bb[k][j].x == vv || bb[k][j].y == vv || bb[k][j].z == vv || bb[k][j].w == vv;
+                  if (use_set) pj = 8;
+                  unsure = !found && (!use_set || bb[k][j].w != SET_EMPTY);
+                  accept = y[k][j] < (found ? c.inv_q : 1.0f);
+                }
+                // walking from the last try to the first: an earlier try overrides what later ones said
+                if (unsure) { slow = true; res = ROUND_AGAIN; probes = 0; }
+                else if (accept) { slow = false; res = v[k][j]; tries = j + 1; probes = pj; }
+                else { probes += pj; }
+              }
+            }
+            if (!slow && res != ROUND_AGAIN) {
+              nbr[k] = res; settled[k] = true;
+              ev.n2v_tries += tries; ev.n2v_probes += probes;
+            } else if (!slow) {  // every try rejected: the queue continues behind them
+              cont[k] = true;
+              ev.n2v_probes += probes;
+            }
+          }
+        }
+      }
+    }
+    // ---- settled pairs are written, the others queued
+#pragma unroll
+    for (int k = 0; k < PPT; k++)
+      if (live[k] && settled[k])
+        count_emit<COUNT>(keep, idx[k], s[k], nbr[k], g.V, step, smem_bins, sh_bins, out_key, out_val, out_rank, cnt, bsum, tmp_step, len,
+                          out_ext, t[k], rs[k], deg[k]);
+    if (APP != ND_APP_UNIFORM_WALK) {
+#pragma unroll
+      for (int k = 0; k < PPT; k++) {
+        const bool push = live[k] && !settled[k];
+        const uint32_t m = __ballot_sync(0xffffffffu, push);
+        if (push) queue[q_count + __popc(m & ((1u << lane) - 1u))] = (int32_t)((uint32_t)idx[k] | (cont[k] ? Q_CONTINUE : 0u));
+        q_count += __popc(m);
+      }
+      drain(false);
     }
   }
+  if (APP != ND_APP_UNIFORM_WALK) drain(true);
   if (smem_bins) {
     __syncthreads();
 #pragma unroll 1
-    for (int b = threadIdx.x; b < bins; b += blockDim.x) {
-      const uint32_t c = sh_bins[b];
-      if (c) atomicAdd(&bsum[b], c);
+    for (int b = threadIdx.x; b < bins; b += COUNT_THREADS) {
+      const uint32_t cb = sh_bins[b];
+      if (cb) atomicAdd(&bsum[b], cb);
     }
   }
   if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
@@ -536,23 +874,63 @@ cnt_scan_kernel(uint32_t *__restrict__ cnt, const uint32_t *__restrict__ bsum, u
   if (is_last && threadIdx.x == SCAN_THREADS - 1) *d_n_out = (int32_t)run;
 }
 
-// Moves every live pair to its place in the sorted map of the next step; clears the coarse bins
-// (the scan before it was their last reader).
+// Moves every live pair to its place in the sorted map of the next step -- one record, one random
+// sector write (see MapRec) -- and clears the coarse bins (the scan before it was their last reader).
+constexpr int SCATTER_PPT = 2;
+template <bool N2V>
 __global__ void __launch_bounds__(256)
 walk_scatter_kernel(const int32_t *__restrict__ d_n, int32_t V, const int32_t *__restrict__ ukey,
                     const int32_t *__restrict__ uval, const int32_t *__restrict__ urank,
-                    const int32_t *__restrict__ cur_transit, const uint32_t *__restrict__ offs,
-                    int32_t *__restrict__ okey, int32_t *__restrict__ oval, int32_t *__restrict__ oprev,
+                    const int4 *__restrict__ uext, const uint32_t *__restrict__ offs, void *__restrict__ out_rec,
                     uint32_t *__restrict__ bsum, int bins) {
   const int n = *d_n;
+  const ndmem::Keep keep;
   for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < bins; b += gridDim.x * blockDim.x) bsum[b] = 0u;
+  constexpr int TILE = 256 * SCATTER_PPT;
+  for (int base = blockIdx.x * TILE; base < n; base += gridDim.x * TILE) {
+    int32_t k[SCATTER_PPT], v[SCATTER_PPT], r[SCATTER_PPT];
+    int4 ext[SCATTER_PPT];
+    uint32_t pos[SCATTER_PPT];
+#pragma unroll
+    for (int j = 0; j < SCATTER_PPT; j++) {
+      const int i = base + j * 256 + threadIdx.x;
+      k[j] = i < n ? keep.ld(ukey + i) : V;
+      const bool ok = k[j] != V;
+      v[j] = ok ? keep.ld(uval + i) : 0;
+      r[j] = ok ? keep.ld(urank + i) : 0;
+      if (N2V) ext[j] = ok ? keep.ld(uext + i) : make_int4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < SCATTER_PPT; j++) pos[j] = k[j] != V ? keep.ld(offs + k[j]) + (uint32_t)r[j] : 0u;
+#pragma unroll
+    for (int j = 0; j < SCATTER_PPT; j++) {
+      if (k[j] != V) {
+        if (N2V) {
+          int4 *dst = reinterpret_cast<int4 *>(out_rec) + 2 * (size_t)pos[j];
+          keep.st(dst, make_int4(k[j], v[j], ext[j].x, ext[j].y));
+          keep.st(dst + 1, make_int4(ext[j].z, 0, 0, 0));
+        } else {
+          keep.st(reinterpret_cast<int2 *>(out_rec) + pos[j], make_int2(k[j], v[j]));
+        }
+      }
+    }
+  }
+}
+
+// the transit-sorted initial map (key, value arrays) as records
+template <bool N2V>
+__global__ void __launch_bounds__(256)
+pack_map_kernel(const int32_t *__restrict__ d_n, const int32_t *__restrict__ key, const int32_t *__restrict__ val,
+                void *__restrict__ rec) {
+  const int n = *d_n;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const int32_t k = ukey[i];
-    if (k == V) continue;
-    const uint32_t pos = __ldg(offs + k) + (uint32_t)urank[i];
-    okey[pos] = k;
-    oval[pos] = uval[i];
-    if (oprev) oprev[pos] = cur_transit[i];
+    if (N2V) {
+      int4 *dst = reinterpret_cast<int4 *>(rec) + 2 * (size_t)i;
+      dst[0] = make_int4(key[i], val[i], 0, 0);
+      dst[1] = make_int4(0, 0, 0, 0);
+    } else {
+      reinterpret_cast<int2 *>(rec)[i] = make_int2(key[i], val[i]);
+    }
   }
 }
 
@@ -753,6 +1131,37 @@ int launch_next_tp(nd_sampler *s, const WalkParams &wp, int step, bool hist, int
   return ND_OK;
 }
 
+// next() of one step in the load-balanced mode: as many CTAs as are resident, at most one per tile
+template <int APP>
+int launch_count(nd_sampler *s, const WalkParams &wp, int step, bool last, int bins, const void *in_rec, const int32_t *d_n,
+                 int32_t *ukey, int32_t *uval, int32_t *tmp_step) {
+  constexpr int PPT = count_ppt<APP>();
+  const size_t smem = sizeof(uint32_t) * ((bins <= MAX_SMEM_BINS && !last ? (size_t)bins : 0) + (size_t)COUNT_WARPS * (32 * PPT + 32));
+  static int resident[2] = {0, 0};  // CTAs per SM (with and without the histogram), asked once
+  int &res = resident[last ? 1 : 0];
+  if (res == 0) {
+    int r = 0;
+    cudaError_t e = last ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, walk_next_count_kernel<APP, false>, COUNT_THREADS, smem)
+                         : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, walk_next_count_kernel<APP, true>, COUNT_THREADS, smem);
+    if (e != cudaSuccess || r < 1) { cudaGetLastError(); r = count_ctas<APP>(); }
+    res = r;
+  }
+  const int64_t tiles = (s->S + COUNT_THREADS * PPT - 1) / (COUNT_THREADS * PPT);
+  const int64_t cap = (int64_t)s->dev.sms * (ND_TUNE_GRID_PER_SM ? ND_TUNE_GRID_PER_SM : res);
+  const int grid = (int)(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
+  NdGraphView gv = nd_view(s->g);
+  int4 *uext = APP == ND_APP_NODE2VEC && !last ? s->d_uext : nullptr;
+  if (last)
+    walk_next_count_kernel<APP, false><<<grid, COUNT_THREADS, smem, s->stream>>>(
+        gv, wp, step, s->first, in_rec, d_n, ukey, uval, s->d_rank, uext, s->d_cnt, s->d_bsum, bins,
+        tmp_step, s->d_len, s->d_status, s->d_stats);
+  else
+    walk_next_count_kernel<APP, true><<<grid, COUNT_THREADS, smem, s->stream>>>(
+        gv, wp, step, s->first, in_rec, d_n, ukey, uval, s->d_rank, uext, s->d_cnt, s->d_bsum, bins,
+        tmp_step, s->d_len, s->d_status, s->d_stats);
+  return ND_OK;
+}
+
 template <int APP>
 int launch_sp(nd_sampler *s, const WalkParams &wp) {
   const int64_t blocks = (s->S + 255) / 256;
@@ -834,6 +1243,19 @@ walk_step_packed_kernel(NdGraphView g, WalkParams wp, int step, int64_t n, const
   }
 }
 }  // namespace
+
+// reads and clears the status word of the two step operators on the current device, after `st` drained
+int nd_walk_step_status_read(cudaStream_t st, int *status) {
+  ND_CUDA(cudaStreamSynchronize(st));
+  int h = 0;
+  ND_CUDA(cudaMemcpyFromSymbol(&h, g_step_status, sizeof(int)));
+  if (h != 0) {
+    const int zero = 0;
+    ND_CUDA(cudaMemcpyToSymbol(g_step_status, &zero, sizeof(int)));
+  }
+  *status = h;
+  return ND_OK;
+}
 
 int nd_walk_step_packed_launch(const nd_graph *g, const nd_app_params *p, int step, int64_t n, const uint64_t *d_in,
                                uint64_t *d_out, cudaStream_t st) {
@@ -917,10 +1339,11 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_CUDA(cudaMalloc(&s->d_rank, sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
   ND_CUDA(cudaMemset(s->d_cnt, 0, sizeof(uint32_t) * bins * CNT_SUPER));
   ND_CUDA(cudaMemset(s->d_bsum, 0, sizeof(uint32_t) * bins));
-  for (int i = 0; i < 2; i++) {
-    ND_CUDA(cudaMalloc(&s->d_lb_key[i], sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
-    if (s->p.app == ND_APP_NODE2VEC) ND_CUDA(cudaMalloc(&s->d_prev[i], sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
-  }
+  const size_t rec = s->p.app == ND_APP_NODE2VEC ? map_rec_bytes<true>() : map_rec_bytes<false>();
+  const size_t S1 = (size_t)(S > 0 ? S : 1);
+  for (int i = 0; i < 2; i++) ND_CUDA(cudaMalloc(&s->d_srec[i], rec * S1));
+  ND_CUDA(cudaMalloc(&s->d_init_rec, rec * S1));
+  if (s->p.app == ND_APP_NODE2VEC) ND_CUDA(cudaMalloc(&s->d_uext, sizeof(int4) * S1));
   return ND_OK;
 }
 
@@ -943,6 +1366,11 @@ int nd_sampler_build_initial_map(nd_sampler *s) {
   const int src = in_b ? 1 : 0;
   ND_CUDA(cudaMemcpyAsync(s->d_init_key, s->d_map_key[src], sizeof(int32_t) * n, cudaMemcpyDeviceToDevice, s->stream));
   ND_CUDA(cudaMemcpyAsync(s->d_init_val, s->d_map_val[src], sizeof(int32_t) * n, cudaMemcpyDeviceToDevice, s->stream));
+  if (s->d_init_rec) {  // walks: the records the load-balanced mode starts from
+    const int pg = (int)(blocks < s->dev.sms * 16 ? (blocks > 0 ? blocks : 1) : s->dev.sms * 16);
+    if (s->p.app == ND_APP_NODE2VEC) pack_map_kernel<true><<<pg, 256, 0, s->stream>>>(s->d_nlive, s->d_map_key[src], s->d_map_val[src], s->d_init_rec);
+    else pack_map_kernel<false><<<pg, 256, 0, s->stream>>>(s->d_nlive, s->d_map_key[src], s->d_map_val[src], s->d_init_rec);
+  }
   return ND_OK;  // stream-ordered: no host synchronisation, so chunks on different streams overlap
 }
 
@@ -1007,45 +1435,35 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     // load-balanced transit-parallel: next() draws tickets, counting inversion
     const int V = s->g->V;
     const int bins = (V + CNT_SUPER - 1) / CNT_SUPER;
-    const size_t smem = bins <= MAX_SMEM_BINS ? sizeof(uint32_t) * (size_t)bins : 0;
-    const int64_t blocks = (S + 255) / 256;
-    const int grid = (int)(blocks < (int64_t)s->dev.sms * 16 ? blocks : (int64_t)s->dev.sms * 16);
-    NdGraphView gv = nd_view(s->g);
     const bool n2v = app == ND_APP_NODE2VEC;
-    // unsorted pairs written by next(): key/val in d_map_*[0]; sorted maps ping-pong between
-    // (d_map_key[1], d_map_val[1], d_prev[0]) and (d_lb_key[0], d_lb_key[1], d_prev[1])
+    // unsorted pairs written by next(): key/val in d_map_*[0], rank, (node2vec) d_uext; the sorted
+    // maps are records that ping-pong between d_srec[0] and d_srec[1]
     int32_t *ukey = s->d_map_key[0], *uval = s->d_map_val[0];
-    int32_t *skey[2] = {s->d_map_key[1], s->d_lb_key[0]};
-    int32_t *sval[2] = {s->d_map_val[1], s->d_lb_key[1]};
-    const int32_t *in_key = s->d_init_key, *in_val = s->d_init_val, *in_prev = nullptr;
+    const void *in_rec = s->d_init_rec;
+    const int64_t sblocks = (S + 256 * SCATTER_PPT - 1) / (256 * SCATTER_PPT);
+    const int sgrid = (int)(sblocks < (int64_t)s->dev.sms * 16 ? (sblocks > 0 ? sblocks : 1) : (int64_t)s->dev.sms * 16);
     int cur = 0;  // sorted map the scatter of this step writes
     for (int step = 0; step < steps; step++) {
       const bool last = step == steps - 1;
       const int32_t *d_n = s->d_nlive + step;
       int32_t *tmp_step = s->d_tmp + (int64_t)step * S;
       nd_phase_begin(s, ND_PHASE_NEXT);
-#define ND_LAUNCH_COUNT(APPID)                                                                                         \
-  if (last) walk_next_count_kernel<APPID, false><<<grid, 256, 0, st>>>(gv, wp, step, s->first, in_key, in_val, in_prev, d_n, ukey, uval, s->d_rank, s->d_cnt, s->d_bsum, bins, tmp_step, s->d_len, s->d_status, s->d_stats); \
-  else walk_next_count_kernel<APPID, true><<<grid, 256, smem, st>>>(gv, wp, step, s->first, in_key, in_val, in_prev, d_n, ukey, uval, s->d_rank, s->d_cnt, s->d_bsum, bins, tmp_step, s->d_len, s->d_status, s->d_stats);
       switch (app) {
-        case ND_APP_UNIFORM_WALK: ND_LAUNCH_COUNT(ND_APP_UNIFORM_WALK) break;
-        case ND_APP_DEEPWALK: ND_LAUNCH_COUNT(ND_APP_DEEPWALK) break;
-        case ND_APP_PPR: ND_LAUNCH_COUNT(ND_APP_PPR) break;
-        default: ND_LAUNCH_COUNT(ND_APP_NODE2VEC) break;
+        case ND_APP_UNIFORM_WALK: ND_TRY(launch_count<ND_APP_UNIFORM_WALK>(s, wp, step, last, bins, in_rec, d_n, ukey, uval, tmp_step)); break;
+        case ND_APP_DEEPWALK: ND_TRY(launch_count<ND_APP_DEEPWALK>(s, wp, step, last, bins, in_rec, d_n, ukey, uval, tmp_step)); break;
+        case ND_APP_PPR: ND_TRY(launch_count<ND_APP_PPR>(s, wp, step, last, bins, in_rec, d_n, ukey, uval, tmp_step)); break;
+        default: ND_TRY(launch_count<ND_APP_NODE2VEC>(s, wp, step, last, bins, in_rec, d_n, ukey, uval, tmp_step)); break;
       }
-#undef ND_LAUNCH_COUNT
       nd_phase_end(s);
       nd_count_launches(1);
       if (last) break;
       nd_phase_begin(s, ND_PHASE_INVERT);
       cnt_scan_kernel<<<bins, SCAN_THREADS, 0, st>>>(s->d_cnt, s->d_bsum, s->d_offs, s->d_nlive + step + 1);
-      walk_scatter_kernel<<<grid, 256, 0, st>>>(d_n, V, ukey, uval, s->d_rank, in_key, s->d_offs, skey[cur], sval[cur],
-                                                n2v ? s->d_prev[cur] : nullptr, s->d_bsum, bins);
+      if (n2v) walk_scatter_kernel<true><<<sgrid, 256, 0, st>>>(d_n, V, ukey, uval, s->d_rank, s->d_uext, s->d_offs, s->d_srec[cur], s->d_bsum, bins);
+      else walk_scatter_kernel<false><<<sgrid, 256, 0, st>>>(d_n, V, ukey, uval, s->d_rank, nullptr, s->d_offs, s->d_srec[cur], s->d_bsum, bins);
       nd_phase_end(s);
       nd_count_launches(2);
-      in_key = skey[cur];
-      in_val = sval[cur];
-      in_prev = n2v ? s->d_prev[cur] : nullptr;
+      in_rec = s->d_srec[cur];
       cur ^= 1;
     }
   }

@@ -1,6 +1,6 @@
 """Random walks over a graph that is PARTITIONED across the GPUs of a process group instead of
 replicated: rank r holds the CSR rows of one contiguous vertex range, every step runs next() on
-the walkers that currently stand on the rank's vertices (`nd_walk_step`), and the survivors are
+the walkers that currently stand on the rank's vertices (`nd_walk_step_packed`), and the survivors are
 routed to the owners of their new vertices with one all-to-all.  At the end every (sample, step,
 vertex) record travels to the sample's home rank (the reference's seed shards, src/utils.hpp:26-27)
 with one more all-to-all.
@@ -50,16 +50,58 @@ def local_rows(row_ptr, col, w, lo: int, hi: int):
     return rp, np.ascontiguousarray(col[e0:e1], np.int32), np.ascontiguousarray(w[e0:e1], np.float32)
 
 
+class _LibraryOps:
+    """The four device operations of a partitioned step, as the library's kernels (C ABI)."""
+
+    def __init__(self, graph, params, device, parts):
+        self.graph, self.params, self.device, self.parts = graph, params, device, parts
+        self._cursor = torch.zeros(parts, dtype=torch.int64, device=device)
+
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def step_packed(self, step, wk):
+        nxt = torch.empty_like(wk)
+        check(lib.nd_walk_step_packed(self.graph._h, C.byref(self.params), step, int(wk.shape[0]),
+                                      C.c_void_p(wk.data_ptr()), C.c_void_p(nxt.data_ptr()), self._stream()))
+        return nxt
+
+    def finish(self):
+        """Reads and clears the device status word of the step kernels (a rejection loop that hit
+        its cap); waits for the stream."""
+        status = C.c_int(0)
+        check(lib.nd_walk_step_status(self.device.index, self._stream(), C.byref(status)))
+        if status.value:
+            raise RuntimeError(f"partitioned walk: device status word 0x{status.value:x} (a rejection loop hit its iteration cap)")
+
+    def route_count(self, wk, by_sample, bounds, counts):
+        check(lib.nd_route_count(self.device.index, int(wk.shape[0]), C.c_void_p(wk.data_ptr()), by_sample,
+                                 C.c_void_p(bounds.data_ptr()), self.parts, C.c_void_p(counts.data_ptr()), self._stream()))
+
+    def route_scatter(self, wk, by_sample, bounds, counts, n_out):
+        out = torch.empty(n_out, dtype=torch.int64, device=self.device)
+        check(lib.nd_route_scatter(self.device.index, int(wk.shape[0]), C.c_void_p(wk.data_ptr()), by_sample,
+                                   C.c_void_p(bounds.data_ptr()), self.parts, C.c_void_p(counts.data_ptr()),
+                                   C.c_void_p(self._cursor.data_ptr()), C.c_void_p(out.data_ptr()), self._stream()))
+        return out
+
+    def records_store(self, mine, step, first, count, steps, out):
+        check(lib.nd_records_store(self.device.index, int(mine.shape[0]), C.c_void_p(mine.data_ptr()), step, first, count, steps,
+                                   C.c_void_p(out.data_ptr()), self._stream()))
+
+
 class PartitionedWalker:
     """One rank of a partitioned walk job.
 
     row_ptr_local / col_local / w_local: this rank's rows as returned by local_rows().
     bounds: the vertex boundaries of ALL ranks (split_bounds), identical on every rank.
-    step_fn(cur, sid, step) -> next: replaces the library's kernel (tests of the routing logic on
-    CPU use it); tensors live on `device`.
+    ops: an object with the four device operations (step_packed, route_count, route_scatter,
+    records_store; see _LibraryOps for their contracts).  Default: the library's kernels on
+    `device`.  The CPU tests of the multi-rank host logic pass their own restatement, so that they
+    drive the same routing code the GPUs run.
     """
 
-    def __init__(self, row_ptr_local, col_local, w_local, bounds, params, group=None, device=None, step_fn=None):
+    def __init__(self, row_ptr_local, col_local, w_local, bounds, params, group=None, device=None, ops=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -70,113 +112,18 @@ class PartitionedWalker:
         self.V = int(np.asarray(row_ptr_local).shape[0] - 1)
         self.bounds = np.asarray(bounds, np.int64)
         assert self.bounds.shape[0] == self.world + 1 and self.bounds[-1] == self.V
-        self.step_fn = step_fn
-        if step_fn is None:
+        if ops is None:
             dev_index = torch.cuda.current_device() if device is None else torch.device(device).index
             self.device = torch.device("cuda", dev_index)
             self.graph = api.Graph.from_csr(row_ptr_local, col_local, w_local, device=dev_index)
+            self.ops = _LibraryOps(self.graph, params, self.device, self.world)
         else:
             self.device = torch.device(device or "cpu")
             self.graph = None
-        self._inner = torch.as_tensor(self.bounds[1:-1], dtype=torch.int64, device=self.device)
+            self.ops = ops
         # collectives run on the tensors' own device unless the backend cannot (gloo with CUDA tensors)
         self._comm_cpu = dist.is_initialized() and dist.get_backend(group) == "gloo" and self.device.type == "cuda"
         self.bytes_sent = 0
-
-    # ------------------------------------------------------------------ one step of next()
-    def _next(self, cur, sid, step):
-        if self.step_fn is not None:
-            return self.step_fn(cur, sid, step)
-        n = int(cur.shape[0])
-        out = torch.empty(n, dtype=torch.int32, device=self.device)
-        if n:
-            stream = torch.cuda.current_stream(self.device).cuda_stream
-            check(lib.nd_walk_step(self.graph._h, C.byref(self.params), step, n, C.c_void_p(cur.data_ptr()),
-                                   C.c_void_p(sid.data_ptr()), C.c_void_p(out.data_ptr()), C.c_void_p(stream)))
-        return out
-
-    # ------------------------------------------------------------------ all-to-all of ragged rows
-    def _exchange(self, dest, columns):
-        """Sends row i of every tensor in `columns` to rank dest[i]; returns the received columns."""
-        if self.world == 1:
-            return columns
-        order = torch.argsort(dest, stable=True)
-        counts = torch.bincount(dest, minlength=self.world)
-        send_counts = counts.cpu()
-        recv_counts = torch.empty_like(send_counts)
-        cdev = torch.device("cpu") if (self._comm_cpu or self.device.type == "cpu") else self.device
-        sc, rc = send_counts.to(cdev), recv_counts.to(cdev)
-        dist.all_to_all_single(rc, sc, group=self.group)
-        recv_counts = rc.cpu()
-        in_split, out_split = send_counts.tolist(), recv_counts.tolist()
-        received = []
-        for col in columns:
-            src = col[order].contiguous()
-            if self._comm_cpu:
-                src = src.cpu()
-            dst = torch.empty(int(sum(out_split)), dtype=src.dtype, device=src.device)
-            dist.all_to_all_single(dst, src, output_split_sizes=out_split, input_split_sizes=in_split, group=self.group)
-            self.bytes_sent += src.element_size() * (int(sum(in_split)) - in_split[self.rank])
-            received.append(dst.to(self.device))
-        return received
-
-    def _owner(self, v):
-        return torch.bucketize(v.to(torch.int64), self._inner, right=True)
-
-    # ------------------------------------------------------------------ the job
-    def run(self, total_samples: int, initial=None):
-        """Walks samples [0, total_samples); returns this rank's home shard [count, steps] (int32 on
-        `device`, invalid = V) and the shard's first sample.  `initial`: the initial vertex of every
-        sample (array of total_samples), default sample s starts at vertex s mod V."""
-        if self.step_fn is None:
-            return self._run_packed(total_samples, initial)
-        steps = int(self.params.steps)
-        first, count = api.shard_range(total_samples, self.rank, self.world)
-        sid = torch.arange(first, first + count, dtype=torch.int64, device=self.device)
-        if initial is None:
-            cur = (sid % self.V).to(torch.int32)
-        else:
-            cur = torch.as_tensor(np.ascontiguousarray(initial[first:first + count], np.int32), device=self.device)
-        ok = (cur >= 0) & (cur < self.V)
-        cur, sid = self._exchange(self._owner(cur[ok]), [cur[ok], sid[ok]])
-        rec_sid, rec_step, rec_v = [], [], []
-        for step in range(steps):
-            nxt = self._next(cur.contiguous(), sid.contiguous(), step)
-            alive = nxt >= 0
-            sid, nxt = sid[alive], nxt[alive]
-            rec_sid.append(sid)
-            rec_step.append(torch.full_like(sid, step, dtype=torch.int32))
-            rec_v.append(nxt)
-            left = torch.tensor([int(sid.shape[0])], dtype=torch.int64,
-                                device="cpu" if (self._comm_cpu or self.device.type == "cpu") else self.device)
-            if self.world > 1:
-                dist.all_reduce(left, group=self.group)
-            if int(left.item()) == 0 or step == steps - 1:
-                break
-            cur, sid = self._exchange(self._owner(nxt), [nxt, sid])
-        # every record goes home
-        r_sid, r_step, r_v = torch.cat(rec_sid), torch.cat(rec_step), torch.cat(rec_v)
-        per = total_samples // self.world
-        home = torch.clamp(r_sid // per, max=self.world - 1) if per > 0 else torch.full_like(r_sid, self.world - 1)
-        r_sid, r_step, r_v = self._exchange(home, [r_sid, r_step, r_v])
-        out = torch.full((count, steps), self.V, dtype=torch.int32, device=self.device)
-        out[(r_sid - first), r_step.to(torch.int64)] = r_v
-        return out, first
-
-    # ------------------------------------------------------------------ the CUDA path: packed walkers, routing kernels
-    def _count(self, wk, by_sample, bounds, counts):
-        check(lib.nd_route_count(self.device.index, int(wk.shape[0]), C.c_void_p(wk.data_ptr()), by_sample,
-                                 C.c_void_p(bounds.data_ptr()), self.world, C.c_void_p(counts.data_ptr()), self._stream()))
-
-    def _scatter(self, wk, by_sample, bounds, counts, n_out):
-        out = torch.empty(n_out, dtype=torch.int64, device=self.device)
-        check(lib.nd_route_scatter(self.device.index, int(wk.shape[0]), C.c_void_p(wk.data_ptr()), by_sample,
-                                   C.c_void_p(bounds.data_ptr()), self.world, C.c_void_p(counts.data_ptr()),
-                                   C.c_void_p(self._cursor.data_ptr()), C.c_void_p(out.data_ptr()), self._stream()))
-        return out
-
-    def _stream(self):
-        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
     def _gather_counts(self, counts):
         """Every rank's count rows (k rows of P destinations) -> [P ranks, k, P] on the host: the
@@ -206,13 +153,16 @@ class PartitionedWalker:
         self.bytes_sent += 8 * (int(sum(send)) - send[self.rank])
         return dst
 
-    def _run_packed(self, total_samples, initial):
-        steps, P, r = int(self.params.steps), self.world, self.rank
+    def run(self, total_samples: int, initial=None):
+        """Walks samples [0, total_samples); returns this rank's home shard [count, steps] (int32 on
+        `device`, invalid = V) and the shard's first sample.  `initial`: the initial vertex of every
+        sample (array of total_samples), default sample s starts at vertex s mod V.
+        A walker is one 64-bit word, (global sample id << 32) | vertex; all ones = ended."""
+        steps, P, r, ops = int(self.params.steps), self.world, self.rank, self.ops
         first, count = api.shard_range(total_samples, r, P)
         dev = self.device
         if not hasattr(self, "_counts"):
             self._counts = torch.zeros(P, dtype=torch.int64, device=dev)
-            self._cursor = torch.zeros(P, dtype=torch.int64, device=dev)
             self._vbounds = torch.as_tensor(self.bounds, dtype=torch.int64, device=dev)
         sid = torch.arange(first, first + count, dtype=torch.int64, device=dev)
         if initial is None:
@@ -224,13 +174,11 @@ class PartitionedWalker:
         for step in range(-1, steps):
             # route the live walkers to the owners of their vertices (step -1: the initial vertices)
             if step >= 0:
-                nxt = torch.empty_like(wk)
-                check(lib.nd_walk_step_packed(self.graph._h, C.byref(self.params), step, int(wk.shape[0]),
-                                              C.c_void_p(wk.data_ptr()), C.c_void_p(nxt.data_ptr()), self._stream()))
-            self._count(nxt, 0, self._vbounds, self._counts)
+                nxt = ops.step_packed(step, wk)
+            ops.route_count(nxt, 0, self._vbounds, self._counts)
             mat = self._gather_counts(self._counts)[:, 0, :]            # [sender, destination]
             send, recv = mat[r].tolist(), mat[:, r].tolist()
-            live = self._scatter(nxt, 0, self._vbounds, self._counts, int(sum(send)))
+            live = ops.route_scatter(nxt, 0, self._vbounds, self._counts, int(sum(send)))
             if step >= 0:
                 records.append(live)
             if int(mat.sum()) == 0 or step + 1 == steps:
@@ -244,11 +192,12 @@ class PartitionedWalker:
             hbounds = torch.as_tensor(starts, dtype=torch.int64, device=dev)
             hcounts = torch.zeros((len(records), P), dtype=torch.int64, device=dev)
             for k, rec in enumerate(records):
-                self._count(rec, 1, hbounds, hcounts[k])
+                ops.route_count(rec, 1, hbounds, hcounts[k])
             hmat = self._gather_counts(hcounts)                          # [sender, step, destination]
             for k, rec in enumerate(records):
                 send, recv = hmat[r, k].tolist(), hmat[:, k, r].tolist()
-                mine = self._all_to_all(self._scatter(rec, 1, hbounds, hcounts[k], int(sum(send))), send, recv)
-                check(lib.nd_records_store(dev.index, int(mine.shape[0]), C.c_void_p(mine.data_ptr()), k, first, count, steps,
-                                           C.c_void_p(out.data_ptr()), self._stream()))
+                mine = self._all_to_all(ops.route_scatter(rec, 1, hbounds, hcounts[k], int(sum(send))), send, recv)
+                ops.records_store(mine, k, first, count, steps, out)
+        if hasattr(ops, "finish"):
+            ops.finish()
         return out, first

@@ -129,10 +129,9 @@ void ndo_rmat_records(int32_t V, int64_t M, uint64_t seed, int32_t *src, int32_t
   }
 }
 
-typedef struct { int32_t s, d; float w; } rec_t;
-static int rec_cmp(const void *a, const void *b) {
-  const rec_t *x = (const rec_t *)a, *y = (const rec_t *)b;
-  if (x->s != y->s) return x->s < y->s ? -1 : 1;
+typedef struct { int32_t d; float w; } adj_t;
+static int adj_cmp(const void *a, const void *b) {
+  const adj_t *x = (const adj_t *)a, *y = (const adj_t *)b;
   if (x->d != y->d) return x->d < y->d ? -1 : 1;
   if (x->w != y->w) return x->w < y->w ? -1 : 1;
   return 0;
@@ -153,17 +152,30 @@ int32_t ndo_csr_from_records(int64_t n, const int32_t *src, const int32_t *dst, 
     V = m + 1;
   }
   if (!row_ptr) return V;
-  rec_t *r = (rec_t *)malloc(sizeof(rec_t) * (size_t)(n > 0 ? n : 1));
-  for (int64_t i = 0; i < n; i++) { r[i].s = src[i]; r[i].d = dst[i]; r[i].w = w[i]; }
-  qsort(r, (size_t)n, sizeof(rec_t), rec_cmp);
+  /* records are grouped by source with a counting pass, then every list is sorted on its own
+   * (lists in parallel): the same order as one sort by (src, dst, weight) */
+  adj_t *r = (adj_t *)malloc(sizeof(adj_t) * (size_t)(n > 0 ? n : 1));
+  int64_t *pos = (int64_t *)malloc(sizeof(int64_t) * ((size_t)V + 1));
   for (int32_t v = 0; v <= V; v++) row_ptr[v] = 0;
-  for (int64_t i = 0; i < n; i++) row_ptr[r[i].s + 1]++;
+  for (int64_t i = 0; i < n; i++) row_ptr[src[i] + 1]++;
   for (int32_t v = 0; v < V; v++) row_ptr[v + 1] += row_ptr[v];
-  for (int32_t v = 0; v < V; v++) max_w[v] = 0.0f;
+  for (int32_t v = 0; v < V; v++) pos[v] = row_ptr[v];
   for (int64_t i = 0; i < n; i++) {
-    col[i] = r[i].d; wout[i] = r[i].w;
-    if (r[i].w > max_w[r[i].s]) max_w[r[i].s] = r[i].w;
+    adj_t *q = &r[pos[src[i]]++];
+    q->d = dst[i]; q->w = w[i];
   }
+#pragma omp parallel for schedule(dynamic, 1024)
+  for (int32_t v = 0; v < V; v++) {
+    const int64_t a = row_ptr[v], b = row_ptr[v + 1];
+    if (b - a > 1) qsort(r + a, (size_t)(b - a), sizeof(adj_t), adj_cmp);
+    float m = 0.0f;
+    for (int64_t i = a; i < b; i++) {
+      col[i] = r[i].d; wout[i] = r[i].w;
+      if (r[i].w > m) m = r[i].w;
+    }
+    max_w[v] = m;
+  }
+  free(pos);
   free(r);
   return V;
 }

@@ -50,9 +50,48 @@ def test_two_ranks_gather_equals_single_job():
         assert (f0, c0) == (0, total // 2) and (f1, c1) == (total // 2, total - total // 2)
 
 
+class _CpuOps:
+    """The four device operations of nextdoor_b200.partitioned restated on CPU tensors, next()
+    from the oracle's keyed draws (uniform walk), so that PartitionedWalker.run -- the routing code
+    the GPUs run -- is driven without a GPU."""
+
+    def __init__(self, ndo, rp, col, bounds, rank, seed):
+        self.ndo, self.rp, self.col, self.bounds, self.rank, self.seed = ndo, rp, col, bounds, rank, seed
+
+    def step_packed(self, step, wk):
+        u, ri = self.ndo.lib().ndo_uniform, self.ndo.lib().ndo_rand_int
+        out = torch.empty_like(wk)
+        for i, x in enumerate(wk.tolist()):
+            s, t = (x >> 32) & 0xffffffff, x & 0xffffffff
+            assert self.bounds[self.rank] <= t < self.bounds[self.rank + 1], "a walker was routed to a rank that does not own its vertex"
+            deg = int(self.rp[t + 1] - self.rp[t])
+            out[i] = ((s << 32) | int(self.col[self.rp[t] + ri(u(self.seed, s, step, 0, 0), deg)])) if deg > 0 else -1
+        return out
+
+    @staticmethod
+    def _dest(wk, by_sample, bounds):
+        live = wk != -1
+        key = ((wk >> 32) & 0xffffffff) if by_sample else (wk & 0xffffffff)
+        return live, torch.bucketize(key, bounds[1:-1].contiguous(), right=True)
+
+    def route_count(self, wk, by_sample, bounds, counts):
+        live, dest = self._dest(wk, by_sample, bounds)
+        counts.copy_(torch.bincount(dest[live], minlength=counts.shape[0]))
+
+    def route_scatter(self, wk, by_sample, bounds, counts, n_out):
+        live, dest = self._dest(wk, by_sample, bounds)
+        out = wk[live][torch.argsort(dest[live], stable=True)]
+        assert out.shape[0] == n_out
+        return out
+
+    def records_store(self, mine, step, first, count, steps, out):
+        s, v = (mine >> 32) & 0xffffffff, mine & 0xffffffff
+        assert bool(((s >= first) & (s < first + count)).all()), "a record arrived at a rank that is not its sample's home"
+        out[s - first, step] = v.to(torch.int32)
+
+
 def _partitioned_worker(rank, world, port, total, steps, ret):
-    """The routing and bookkeeping of the partitioned walker over gloo, with next() restated in
-    Python from the keyed draws (uniform walk) so that no GPU is needed."""
+    """The routing and bookkeeping of the partitioned walker over gloo."""
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -64,18 +103,8 @@ def _partitioned_worker(rank, world, port, total, steps, ret):
     seed = 9
     bounds = ndp.split_bounds(g.row_ptr, world)
     rp, col, w = ndp.local_rows(g.row_ptr, g.col, g.w, int(bounds[rank]), int(bounds[rank + 1]))
-    u, ri = ndo.lib().ndo_uniform, ndo.lib().ndo_rand_int
-
-    def step_fn(cur, sid, step):
-        out = torch.empty_like(cur)
-        for i, (t, s) in enumerate(zip(cur.tolist(), sid.tolist())):
-            assert bounds[rank] <= t < bounds[rank + 1], "a walker was routed to a rank that does not own its vertex"
-            deg = int(rp[t + 1] - rp[t])
-            out[i] = int(col[rp[t] + ri(u(seed, s, step, 0, 0), deg)]) if deg > 0 else -1
-        return out
-
     pr = nd.app_params(nd.APP_UNIFORM_WALK, steps=steps, seed=seed)
-    walker = ndp.PartitionedWalker(rp, col, w, bounds, pr, device="cpu", step_fn=step_fn)
+    walker = ndp.PartitionedWalker(rp, col, w, bounds, pr, device="cpu", ops=_CpuOps(ndo, rp, col, bounds, rank, seed))
     init = (np.arange(total) * 7 % g.V).astype(np.int32)
     init[5] = g.V          # an invalid seed: its row stays invalid
     out, first = walker.run(total, initial=init)

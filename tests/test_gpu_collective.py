@@ -92,11 +92,13 @@ def _compare_importance(ndo, hg, opr, S, init, got, gprob, exp):
     return flips
 
 
-@pytest.fixture(params=["bitmap", "sort"])
+@pytest.fixture(params=["bitmap", "bitmap_global", "sort"])
 def union_path(request, monkeypatch):
-    """The importance samplers build the union either in a shared-memory bitmap (graphs whose
-    vertex count fits) or with the radix-sort pipeline; ND_COLLECTIVE_SORT=1 selects the latter."""
+    """The importance samplers build the union as a bitmap with a bit per vertex -- in shared
+    memory when it fits, else in global scratch (ND_COLLECTIVE_BITMAP_GLOBAL=1 forces that on small
+    graphs) -- or with the radix-sort pipeline (ND_COLLECTIVE_SORT=1)."""
     monkeypatch.setenv("ND_COLLECTIVE_SORT", "1" if request.param == "sort" else "0")
+    monkeypatch.setenv("ND_COLLECTIVE_BITMAP_GLOBAL", "1" if request.param == "bitmap_global" else "0")
     return request.param
 
 

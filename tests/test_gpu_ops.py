@@ -162,11 +162,14 @@ def test_text_loaders_match_reference_loaders(nd, tmp_path):
     assert "Incorrect graph file type" in str(e.value)
 
 
-def test_random_gather_probe_reports_a_rate(nd):
+def test_random_gather_probe_reports_a_rate():
+    """The measurement aid of bench.py (bench_probe.cu, its own small library)."""
     import ctypes as C
-    from nextdoor_b200._lib import lib, check
+    import bench
+    probe = C.CDLL(bench.build_probe())
+    probe.nd_bench_random_gather.argtypes = [C.c_int, C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_double)]
     small, large = C.c_double(0), C.c_double(0)
-    check(lib.nd_probe_random_gather(0, 8 << 20, 1 << 22, 3, C.byref(small)))     # L2-resident array
-    check(lib.nd_probe_random_gather(0, 1 << 30, 1 << 22, 3, C.byref(large)))     # 1 GiB: DRAM
+    assert probe.nd_bench_random_gather(0, 8 << 20, 1 << 22, 3, C.byref(small)) == 0     # L2-resident array
+    assert probe.nd_bench_random_gather(0, 1 << 30, 1 << 22, 3, C.byref(large)) == 0     # 1 GiB: DRAM
     assert small.value > large.value > 1e9
-    assert lib.nd_probe_random_gather(0, 0, 1, 1, C.byref(small)) != 0            # bad argument is an error, not a crash
+    assert probe.nd_bench_random_gather(0, 0, 1, 1, C.byref(small)) != 0                 # bad argument is an error, not a crash

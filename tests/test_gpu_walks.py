@@ -45,6 +45,9 @@ def test_walks_match_oracle(nd, ndo, small_graph, app, mode):
         st = s.stats()
         assert st["sampled_edges"] == exp["counters"]["sampled_edges"]
         assert st["live_pairs"] == exp["counters"]["live_pairs"]
+        # the events behind the algorithmic-bytes model: tries of the rejection loops
+        assert st["weight_tries"] == exp["counters"]["weight_tries"]
+        assert st["n2v_tries"] == exp["counters"]["n2v_tries"]
         # a second run of the same sampler gives the same answer
         s.sample(mode)
         assert np.array_equal(s.final_samples(), exp["out"])
