@@ -224,6 +224,8 @@ struct NextDoorData {
   std::vector<VertexID_t *> dInitialSamples;
   std::vector<VertexID_t *> dMapKeys[2];
   std::vector<VertexID_t *> dMapVals[2];
+  std::vector<cudaStream_t> streams;       // one per device: the devices' step loops run side by side
+  std::vector<nd_inverter *> inverters;    // map inversion with its scratch allocated once per device
   int INVALID_VERTEX = 0;
   int maxBits = 0;
   std::vector<GPUCSRPartition> gpuCSRPartitions;
@@ -287,11 +289,12 @@ __host__ __device__ inline int prefix_of(int step) {  // offset of hop `step` in
 // (src/nextdoor.cu:212-336, 1348-1518).  FROM_MAP: pair i of the transit-sorted map.
 template <class SampleType, typename App, bool FROM_MAP>
 __global__ void step_kernel(CSRPartition part, int step, uint64_t seed, int64_t first_sample, int64_t n_pairs,
-                            const VertexID_t *in_key, const VertexID_t *in_val, const VertexID_t *initial,
+                            const int32_t *d_n_pairs, const VertexID_t *in_key, const VertexID_t *in_val, const VertexID_t *initial,
                             SampleType *samples, VertexID_t *out, int fs, VertexID_t *mkey, VertexID_t *mval,
                             bool write_map, const VertexID_t *explicit_prev, int isz) {
   const int f = App().stepSize(step);
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (d_n_pairs) n_pairs = *d_n_pairs;  // live pairs of the sorted map, left on the device by the inversion
   if (tid >= n_pairs * f) return;
   const int64_t i = tid / f;
   const int j = (int)(tid - i * f);
@@ -476,6 +479,12 @@ bool allocNextDoorDataOnGPU(CSR *csr, NextDoorData<SampleType, App> &data) {
       NDC_CHECK(cudaMalloc(&data.dMapKeys[b][d], sizeof(VertexID_t) * n1 * max_pairs));
       NDC_CHECK(cudaMalloc(&data.dMapVals[b][d], sizeof(VertexID_t) * n1 * max_pairs));
     }
+    cudaStream_t st = nullptr;
+    NDC_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    data.streams.push_back(st);
+    nd_inverter *inv = nullptr;
+    if (nd_inverter_create(data.devices[d], (int64_t)(n1 * max_pairs), data.INVALID_VERTEX, &inv) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }
+    data.inverters.push_back(inv);
   }
   std::cout << "Final Size of each sample: " << fs << std::endl;
   std::cout << "Number of Samples: " << S << std::endl;
@@ -505,42 +514,54 @@ std::vector<GPUCSRPartition> transferCSRToGPUs(NextDoorDataT &data, CSR *csr) {
 }
 
 namespace ndc {
+// The step loop.  Every device's whole job is enqueued on that device's stream before any device is
+// waited for, so the devices work side by side (the reference runs one host thread per device,
+// src/nextdoor.cu:2363-2963); inside a job nothing comes back to the host: the map inversion keeps
+// its scratch between steps and leaves the live count on the device, where the next step's kernel
+// reads it (the reference copies counts to the host and allocates per step, :2413-2429, 2515-2567).
 template <class SampleType, typename App>
 bool run(CSR *csr, NextDoorData<SampleType, App> &data, bool transit_parallel) {
   const int P = (int)data.devices.size();
   if ((int)data.gpuCSRPartitions.size() != P) { printf("transferCSRToGPUs has not been called\n"); return false; }
+  if ((int)data.streams.size() != P) { printf("allocNextDoorDataOnGPU has not been called\n"); return false; }
   const int64_t S = (int64_t)data.samples.size();
   const int fs = getFinalSampleSize<App>();
   const int isz = App().initialSampleSize(csr);
   const int32_t INV = data.INVALID_VERTEX;
   const bool collective = App().samplingType() == CollectiveNeighborhood;
+  std::vector<VertexID_t> ids;   // pair ids of the initial map; must outlive the asynchronous copies
+  if (transit_parallel && !collective) {
+    int64_t longest = 0;
+    for (int d = 0; d < P; d++) longest = std::max<int64_t>(longest, part_size(S, d, P) * isz);
+    ids.resize((size_t)longest);
+    for (int64_t i = 0; i < longest; i++) ids[(size_t)i] = (VertexID_t)i;
+  }
   for (int d = 0; d < P; d++) {
     NDC_CHECK(cudaSetDevice(data.devices[d]));
+    cudaStream_t st = data.streams[d];
     const int64_t n = part_size(S, d, P), first = part_start(S, d, P);
     if (n == 0) continue;
     const CSRPartition part = data.gpuCSRPartitions[d].view;
     VertexID_t *out = data.dFinalSamples[d];
-    fill_kernel<VertexID_t><<<(unsigned)((n * fs + 255) / 256), 256>>>(out, n * fs, INV);
-    NDC_CHECK(cudaMemcpy(data.dOutputSamples[d], data.samples.data() + first, sizeof(SampleType) * (size_t)n, cudaMemcpyHostToDevice));
+    fill_kernel<VertexID_t><<<(unsigned)((n * fs + 255) / 256), 256, 0, st>>>(out, n * fs, INV);
+    NDC_CHECK(cudaMemcpyAsync(data.dOutputSamples[d], data.samples.data() + first, sizeof(SampleType) * (size_t)n, cudaMemcpyHostToDevice, st));
     if (collective) {  // next() of collective apps always runs sample-parallel (src/nextdoor.cu:2900-2916)
       for (int step = 0; step < App().steps(); step++) {
         const int64_t threads = n * App().stepSize(step);
-        collective_kernel<SampleType, App><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, n, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, isz);
+        collective_kernel<SampleType, App><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(part, step, nextdoor_seed(), first, n, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, isz);
       }
-      NDC_CHECK(cudaDeviceSynchronize());
+      NDC_CHECK(cudaGetLastError());
       continue;
     }
     const int64_t n0 = n * isz;   // initial pairs: every vertex of every initial sample
-    int64_t n_pairs = n0;      // live pairs of the current step (transit-parallel) / all pairs (sample-parallel)
     int cur = 0;
     const VertexID_t *in_key = nullptr, *in_val = nullptr;
+    const int32_t *d_live = nullptr;   // live pairs of the sorted map (device), transit-parallel only
     if (transit_parallel) {   // initial transit -> sample map, sorted by transit
       VertexID_t *k0 = data.dMapKeys[0][d], *v0 = data.dMapVals[0][d];
-      NDC_CHECK(cudaMemcpy(k0, data.initialContents.data() + first * isz, sizeof(VertexID_t) * (size_t)n0, cudaMemcpyHostToDevice));
-      std::vector<VertexID_t> ids((size_t)n0);
-      for (int64_t i = 0; i < n0; i++) ids[(size_t)i] = (VertexID_t)i;
-      NDC_CHECK(cudaMemcpy(v0, ids.data(), sizeof(VertexID_t) * (size_t)n0, cudaMemcpyHostToDevice));
-      if (nd_invert_map(data.devices[d], n0, k0, v0, INV, data.dMapKeys[1][d], data.dMapVals[1][d], &n_pairs) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }
+      NDC_CHECK(cudaMemcpyAsync(k0, data.initialContents.data() + first * isz, sizeof(VertexID_t) * (size_t)n0, cudaMemcpyHostToDevice, st));
+      NDC_CHECK(cudaMemcpyAsync(v0, ids.data(), sizeof(VertexID_t) * (size_t)n0, cudaMemcpyHostToDevice, st));
+      if (nd_inverter_run(data.inverters[d], st, n0, k0, v0, data.dMapKeys[1][d], data.dMapVals[1][d], &d_live) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }
       in_key = data.dMapKeys[1][d]; in_val = data.dMapVals[1][d];
       cur = 0;
     }
@@ -548,33 +569,36 @@ bool run(CSR *csr, NextDoorData<SampleType, App> &data, bool transit_parallel) {
       const bool last = step == App().steps() - 1;
       const int f = App().stepSize(step);
       const int64_t full_pairs = n * pairs_per_sample<App>(step, isz);
-      const int64_t pairs = transit_parallel ? n_pairs : full_pairs;
       const bool explicit_tr = App().hasExplicitTransits();
       const bool write_map = (transit_parallel || explicit_tr) && !last;
       // sample-parallel runs of explicit-transit apps ping-pong the unsorted per-pair transits
       if (!transit_parallel && explicit_tr) cur = step & 1;
       VertexID_t *mk = data.dMapKeys[cur][d], *mv = data.dMapVals[cur][d];
       const VertexID_t *explicit_prev = (!transit_parallel && explicit_tr && step > 0) ? data.dMapKeys[cur ^ 1][d] : nullptr;
-      if (write_map) fill_kernel<VertexID_t><<<(unsigned)((full_pairs * f + 255) / 256), 256>>>(mk, full_pairs * f, INV);
-      const int64_t threads = pairs * f;
+      if (write_map) fill_kernel<VertexID_t><<<(unsigned)((full_pairs * f + 255) / 256), 256, 0, st>>>(mk, full_pairs * f, INV);
+      const int64_t threads = full_pairs * f;   // the grid covers every pair; transit-parallel threads beyond the live count return
       if (threads > 0) {
-        if (transit_parallel) step_kernel<SampleType, App, true><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, in_key, in_val, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, nullptr, isz);
-        else step_kernel<SampleType, App, false><<<(unsigned)((threads + 255) / 256), 256>>>(part, step, nextdoor_seed(), first, pairs, nullptr, nullptr, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, explicit_prev, isz);
+        if (transit_parallel) step_kernel<SampleType, App, true><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(part, step, nextdoor_seed(), first, full_pairs, d_live, in_key, in_val, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, nullptr, isz);
+        else step_kernel<SampleType, App, false><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(part, step, nextdoor_seed(), first, full_pairs, nullptr, nullptr, nullptr, data.dInitialSamples[d], data.dOutputSamples[d], out, fs, mk, mv, write_map, explicit_prev, isz);
       }
       if (write_map && explicit_tr) {
         const int64_t total = full_pairs * f;
-        transits_kernel<SampleType, App><<<(unsigned)((total + 255) / 256), 256>>>(step + 1, nextdoor_seed(), first, total, (int)(total / n),
-                                                                                  data.dOutputSamples[d], mk, mv, INV);
+        transits_kernel<SampleType, App><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(step + 1, nextdoor_seed(), first, total, (int)(total / n),
+                                                                                         data.dOutputSamples[d], mk, mv, INV);
       }
       NDC_CHECK(cudaGetLastError());
       if (write_map && transit_parallel) {  // the map inversion of the step loop (src/nextdoor.cu:2924-2939)
         // buffer 0 = unsorted pairs just written, buffer 1 = sorted map (its old content, this step's
         // input, is dead once the step kernel has run)
-        if (nd_invert_map(data.devices[d], full_pairs * f, mk, mv, INV, data.dMapKeys[1][d], data.dMapVals[1][d], &n_pairs) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }
+        if (nd_inverter_run(data.inverters[d], st, full_pairs * f, mk, mv, data.dMapKeys[1][d], data.dMapVals[1][d], &d_live) != ND_OK) { std::cout << nd_last_error() << std::endl; return false; }
       }
     }
-    NDC_CHECK(cudaDeviceSynchronize());
-    NDC_CHECK(cudaMemcpy(data.samples.data() + first, data.dOutputSamples[d], sizeof(SampleType) * (size_t)n, cudaMemcpyDeviceToHost));
+  }
+  for (int d = 0; d < P; d++) {  // only now wait: every device has its whole job
+    NDC_CHECK(cudaSetDevice(data.devices[d]));
+    NDC_CHECK(cudaStreamSynchronize(data.streams[d]));
+    const int64_t n = part_size(S, d, P), first = part_start(S, d, P);
+    if (n > 0) NDC_CHECK(cudaMemcpy(data.samples.data() + first, data.dOutputSamples[d], sizeof(SampleType) * (size_t)n, cudaMemcpyDeviceToHost));
   }
   return true;
 }
@@ -616,7 +640,10 @@ void freeDeviceData(NextDoorData<SampleType, App> &data) {
       for (int b = 0; b < 2; b++) { cudaFree(data.dMapKeys[b][d]); cudaFree(data.dMapVals[b][d]); }
     }
     if (d < data.gpuCSRPartitions.size()) nd_graph_destroy(data.gpuCSRPartitions[d].handle);
+    if (d < data.inverters.size()) nd_inverter_destroy(data.inverters[d]);
+    if (d < data.streams.size()) cudaStreamDestroy(data.streams[d]);
   }
+  data.inverters.clear(); data.streams.clear();
   data.dFinalSamples.clear(); data.dInitialSamples.clear(); data.dOutputSamples.clear();
   for (int b = 0; b < 2; b++) { data.dMapKeys[b].clear(); data.dMapVals[b].clear(); }
   data.gpuCSRPartitions.clear();

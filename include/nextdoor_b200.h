@@ -173,6 +173,19 @@ int nd_sampler_destroy(nd_sampler *s);
  * are clobbered.  *n_live_out (host) receives the surviving count. */
 int nd_invert_map(int device, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t invalid,
                   int32_t *keys_out, int32_t *vals_out, int64_t *n_live_out);
+/* The same inversion as a stream-ordered operation for a step loop: the scratch is allocated once
+ * (the reference sizes its cub temp storage once before its loop, src/nextdoor.cu:2335, and sorts in
+ * every step, :2930-2933).  nd_inverter_run enqueues the sort of n pairs on `stream` and returns
+ * without waiting and without touching the allocator; the surviving count stays on the device:
+ * *d_n_live (may be NULL) receives the address of an int32 that holds it once the stream reaches
+ * that point (valid until the next run on this inverter).  The sorted pairs occupy the first
+ * *d_n_live slots of keys_out / vals_out; keys_in / vals_in are clobbered.  max_pairs bounds n;
+ * `invalid` (= the vertex count) is the dead key and bounds the key range. */
+typedef struct nd_inverter nd_inverter;
+int nd_inverter_create(int device, int64_t max_pairs, int32_t invalid, nd_inverter **out);
+int nd_inverter_run(nd_inverter *inv, void *stream, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t *keys_out,
+                    int32_t *vals_out, const int32_t **d_n_live);
+int nd_inverter_destroy(nd_inverter *inv);
 /* No counterpart in the reference.  nd_invert_map for callers that must not allocate device
  * memory: a sampler sharing a process with a training job, where cudaMalloc/cudaFree would
  * synchronise the device and stall the training streams, or where the framework's allocator has

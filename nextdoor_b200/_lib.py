@@ -82,6 +82,9 @@ _SIGS = {
     "nd_sampler_next_kernel": (C.c_int, [VP, C.c_int, C.c_char_p, C.c_int]),
     "nd_sampler_destroy": (C.c_int, [VP]),
     "nd_invert_map": (C.c_int, [C.c_int, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
+    "nd_inverter_create": (C.c_int, [C.c_int, C.c_int64, C.c_int32, C.POINTER(VP)]),
+    "nd_inverter_run": (C.c_int, [VP, VP, C.c_int64, VP, VP, VP, VP, C.POINTER(VP)]),
+    "nd_inverter_destroy": (C.c_int, [VP]),
     "nd_invert_map_static": (C.c_int, [C.c_int, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
     "nd_invert_map_static_on": (C.c_int, [C.c_int, VP, C.c_int64, VP, VP, C.c_int32, VP, VP, C.POINTER(C.c_int64)]),
     "nd_static_max_pairs": (C.c_int64, []),

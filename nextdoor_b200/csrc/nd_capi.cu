@@ -398,6 +398,64 @@ int nd_invert_map(int device, int64_t n, int32_t *keys_in, int32_t *vals_in, int
   return rc;
 }
 
+// ---- the inversion with its scratch kept between calls
+
+struct nd_inverter {
+  int device = 0;
+  NdDeviceInfo dev;
+  int64_t max_pairs = 0;
+  int32_t invalid = 0;
+  NdRadixScratch scr;
+  int32_t *d_n = nullptr;   // [2]: pairs in, live pairs out
+};
+
+int nd_inverter_create(int device, int64_t max_pairs, int32_t invalid, nd_inverter **out) {
+  ND_REQUIRE(out && max_pairs >= 1 && max_pairs < ((int64_t)1 << 31) && invalid >= 1, ND_ERR_ARG, "nd_inverter_create: bad argument");
+  ND_CUDA(cudaSetDevice(device));
+  nd_inverter *inv = new nd_inverter();
+  inv->device = device;
+  inv->max_pairs = max_pairs;
+  inv->invalid = invalid;
+  int rc = nd_device_info(device, &inv->dev);
+  if (rc == ND_OK) rc = nd_radix_scratch_alloc(&inv->scr, nd_bit_length((uint32_t)(invalid > 1 ? invalid - 1 : 1)), max_pairs);
+  if (rc == ND_OK && cudaMalloc(&inv->d_n, 2 * sizeof(int32_t)) != cudaSuccess) { nd_set_error("nd_inverter_create: cudaMalloc failed"); rc = ND_ERR_CUDA; }
+  if (rc != ND_OK) { nd_radix_scratch_free(&inv->scr); cudaFree(inv->d_n); delete inv; return rc; }
+  *out = inv;
+  return ND_OK;
+}
+
+int nd_inverter_run(nd_inverter *inv, void *stream, int64_t n, int32_t *keys_in, int32_t *vals_in, int32_t *keys_out,
+                    int32_t *vals_out, const int32_t **d_n_live) {
+  ND_REQUIRE(inv && n >= 0 && n <= inv->max_pairs, ND_ERR_ARG, "nd_inverter_run: %lld pairs exceed the inverter's capacity", (long long)n);
+  ND_REQUIRE(n == 0 || (keys_in && vals_in && keys_out && vals_out), ND_ERR_ARG, "nd_inverter_run: null pointer");
+  ND_CUDA(cudaSetDevice(inv->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int32_t n32[2] = {(int32_t)n, 0};
+  ND_CUDA(cudaMemcpyAsync(inv->d_n, n32, sizeof(n32), cudaMemcpyHostToDevice, st));  // pageable source: staged before the call returns
+  if (d_n_live) *d_n_live = inv->d_n + 1;
+  if (n == 0) return ND_OK;
+  NdSortArrays arr;
+  arr.nwords = 2;
+  arr.a[0] = (uint32_t *)keys_in; arr.a[1] = (uint32_t *)vals_in; arr.a[2] = nullptr;
+  arr.b[0] = (uint32_t *)keys_out; arr.b[1] = (uint32_t *)vals_out; arr.b[2] = nullptr;
+  bool in_b = false;
+  ND_TRY(nd_radix_sort(inv->dev, st, &inv->scr, inv->scr.plan, arr, 0, inv->d_n, inv->d_n + 1, true, (uint32_t)inv->invalid, false, &in_b));
+  if (!in_b) {  // an even number of passes: the result sits in the input arrays
+    ND_CUDA(cudaMemcpyAsync(keys_out, keys_in, sizeof(int32_t) * (size_t)n, cudaMemcpyDeviceToDevice, st));
+    ND_CUDA(cudaMemcpyAsync(vals_out, vals_in, sizeof(int32_t) * (size_t)n, cudaMemcpyDeviceToDevice, st));
+  }
+  return ND_OK;
+}
+
+int nd_inverter_destroy(nd_inverter *inv) {
+  if (!inv) return ND_OK;
+  cudaSetDevice(inv->device);
+  nd_radix_scratch_free(&inv->scr);
+  cudaFree(inv->d_n);
+  delete inv;
+  return ND_OK;
+}
+
 int nd_distinct_segments(int device, int32_t *data, int64_t n_segments, int32_t seg_len, int32_t invalid, int32_t *counts) {
   ND_REQUIRE(n_segments >= 0 && seg_len >= 1 && (data || n_segments == 0), ND_ERR_ARG, "nd_distinct_segments: bad argument");
   ND_CUDA(cudaSetDevice(device));

@@ -134,7 +134,10 @@ __device__ __forceinline__ int32_t weighted_round(const WalkParams &wp, int32_t 
   int2 rec[BATCH];
 #pragma unroll
   for (int k = 0; k < BATCH; k++) {
-    const int32_t x = rng.rand_int(n);
+    int32_t x = rng.rand_int(n);
+#ifdef ND_DIAG_HUB_FREE   // measurement only: what any staging of hub lists could save at most (hub gathers share one sector)
+    if (n >= ND_DIAG_HUB_FREE) x &= 3;
+#endif
     y[k] = __fmul_rn(rng.uniform(), max_w);
     rec[k] = ld_graph<STREAM>(recs + x);
   }
@@ -426,19 +429,22 @@ constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_PER_THREAD = CNT_SUPER / SCAN_THREADS;   // 32 consecutive counters per thread
 constexpr int MAX_SMEM_BINS = 8192;                         // coarse bins kept in shared memory (V <= 2^25)
 
-// The kernel.  A (transit, sample) pair of a walk is a chain of dependent memory accesses (map
-// entry -> row offsets -> draws -> neighbour gather [-> set bucket] -> ticket), each a DRAM or L2
-// latency, and a launch holds only a few waves of threads: with one pair per thread the kernel
-// waits on that chain, wave after wave.  So
-//  * the CTAs are persistent (as many as are resident) and take tiles of 256 * PPT pairs; a
-//    thread works on PPT pairs at once, phase by phase, so the loads of a phase are in flight
-//    together (PPT chains overlap);
-//  * the first round of tries of every pair is straight-line code (no divergence); a pair that
-//    the first round does not settle (all tries rejected, or a membership test that has to walk
-//    past a full bucket: about one pair in eight) is put on a per-warp queue in shared memory,
-//    and whenever a queue holds 32 pairs the warp runs them through the general loop with all
-//    lanes busy.  The draws of a pair depend only on (sample, step), so the queue changes nothing;
+// The kernel.  CTAs take tiles of 256 * PPT pairs of the sorted map (PPT = pairs a thread works on
+// at once, phase by phase; 1 measured best for every app, larger values are kept as a tuning macro).
+//  * uniform walk, DeepWalk, PPR: next() in place, up to 16 CTAs per SM, a tile each.
+//  * node2vec: the first round of tries of a pair is straight-line code (no divergence: the
+//    round's candidate gathers are issued together, then its set buckets); a pair the first round
+//    does not settle (every try rejected, or a membership test that has to walk past a full
+//    bucket: about one pair in eight) goes on a per-warp queue in shared memory, and whenever a
+//    queue holds 32 pairs the warp runs them through the general loop with all lanes busy --
+//    continuing behind the rejected tries in the pair's draw sequence, so nothing is gathered
+//    twice.  The draws of a pair depend only on (sample, step), so the queue changes no sample.
+//    The CTAs are persistent here (as many as are resident), so that the queues fill over tiles.
 //  * the coarse histogram is flushed once per CTA.
+// What bounds it: a pair costs a few random 32-byte sector reads that miss the L2 (one neighbour id;
+// node2vec about 1.9 candidates and 0.9 set buckets), and the memory system serves those at a
+// rate far below its streaming bandwidth; occupancy, pairs per thread, cache hints and the L2
+// fetch granularity were all measured and do not move the kernel's time by more than a few per cent.
 constexpr int COUNT_THREADS = 256;
 constexpr int COUNT_WARPS = COUNT_THREADS / 32;
 
@@ -453,12 +459,6 @@ constexpr int COUNT_WARPS = COUNT_THREADS / 32;
 #endif
 #ifndef ND_TUNE_N2V_FIRST
 #define ND_TUNE_N2V_FIRST 4
-#endif
-#ifndef ND_TUNE_WEIGHTED_INLINE
-#define ND_TUNE_WEIGHTED_INLINE 0
-#endif
-#ifndef ND_TUNE_GRID_PER_SM
-#define ND_TUNE_GRID_PER_SM 0   // CTAs per SM of a launch; 0 = as many as are resident
 #endif
 #ifndef ND_TUNE_CTAS_UNIFORM
 #define ND_TUNE_CTAS_UNIFORM 4
@@ -478,7 +478,6 @@ __host__ __device__ constexpr int count_ctas() {
   return APP == ND_APP_NODE2VEC ? ND_TUNE_CTAS_N2V : (APP == ND_APP_UNIFORM_WALK ? ND_TUNE_CTAS_UNIFORM : ND_TUNE_CTAS_WEIGHTED);
 }
 constexpr int N2V_FIRST = ND_TUNE_N2V_FIRST;   // tries of the straight-line first round
-constexpr int WEIGHT_FIRST = 2;
 
 // A record of the transit-sorted map in the load-balanced mode.  One record = one aligned piece
 // of one 32-byte sector, so the scatter kernel places a pair with ONE random sector write:
@@ -585,12 +584,6 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
         if (N2V) {
           if (cont) { rng.seek(2u * N2V_FIRST); ev.n2v_tries += N2V_FIRST; }
           nbr = n2v_next_known<true, N2V_BATCH_COUNT>(g, wp, rs, deg, r.pv, r.prow.x, r.prow.y, rng, status, ev);
-        } else if (WEIGHTED) {
-          rng.seek((APP == ND_APP_PPR ? 1u : 0u) + 2u * WEIGHT_FIRST);
-          ev.weight_tries += WEIGHT_FIRST;
-          const float max_w = __ldg(g.max_w + r.t);
-          for (int it = 0; it <= RETRY_CAP && nbr == ROUND_AGAIN; it += 2) nbr = weighted_round<true, 2>(wp, rs, deg, max_w, rng, ev);
-          if (nbr == ROUND_AGAIN) { atomicOr(status, ND_DEV_RETRY_LIMIT); nbr = __ldcs(g.col + rs); }
         }
         count_emit<COUNT>(keep, i, r.s, nbr, g.V, step, smem_bins, sh_bins, out_key, out_val, out_rank, cnt, bsum, tmp_step, len,
                           out_ext, r.t, rs, deg);
@@ -623,7 +616,7 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
       rs[k] = ok ? keep.ld_const(g.row_ptr + t[k]) : 0;
       deg[k] = ok ? keep.ld_const(g.row_ptr + t[k] + 1) - rs[k] : 0;
       nbr[k] = -1;
-      cont[k] = WEIGHTED;  // a weighted pair is queued only after a full round of rejected tries
+      cont[k] = false;
       settled[k] = deg[k] <= 0;  // next() runs only on transits with edges (src/nextdoor.cu:255,412)
     }
     // ---- first round
@@ -631,7 +624,10 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
 #pragma unroll
       for (int k = 0; k < PPT; k++) {
         Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
-        const int32_t x = rng.rand_int(deg[k] > 0 ? deg[k] : 1);
+        int32_t x = rng.rand_int(deg[k] > 0 ? deg[k] : 1);
+#ifdef ND_DIAG_HUB_FREE
+        if (deg[k] >= ND_DIAG_HUB_FREE) x &= 7;
+#endif
 #if defined(ND_DIAG_NO_GATHER)
         if (deg[k] > 0) nbr[k] = (int32_t)(((uint32_t)(rs[k] + x) * 2654435761u) % (uint32_t)g.V);
 #elif defined(ND_DIAG_LDG)
@@ -642,8 +638,7 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
         settled[k] = true;
       }
     }
-#if ND_TUNE_WEIGHTED_INLINE
-    if (WEIGHTED) {  // the rejection loop in place, one pair after the other
+    if (WEIGHTED) {  // randomWalks.cu:74-90, 102-124: the rejection loop in place (rounds of two tries)
 #pragma unroll
       for (int k = 0; k < PPT; k++) {
         if (deg[k] > 0) {
@@ -654,46 +649,6 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
         }
       }
     }
-#else
-    if (WEIGHTED) {  // randomWalks.cu:74-90, 102-124
-      float mw[PPT], y[PPT][WEIGHT_FIRST];
-      int2 rec[PPT][WEIGHT_FIRST];
-      bool stop[PPT];
-#pragma unroll
-      for (int k = 0; k < PPT; k++) mw[k] = deg[k] > 1 ? __ldg(g.max_w + t[k]) : 0.f;
-#pragma unroll
-      for (int k = 0; k < PPT; k++) {
-        Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
-        stop[k] = false;
-        if (APP == ND_APP_PPR) stop[k] = rng.uniform() < wp.stop_prob;
-        const bool go = deg[k] > 0 && !stop[k];
-#pragma unroll
-        for (int j = 0; j < WEIGHT_FIRST; j++) {
-          const int32_t x = rng.rand_int(deg[k] > 0 ? deg[k] : 1);   // a single neighbour: x = 0
-          y[k][j] = __fmul_rn(rng.uniform(), mw[k]);
-          rec[k][j] = go && (j == 0 || deg[k] > 1) ? __ldcs(wp.colw + rs[k] + x) : make_int2(-1, 0);
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < PPT; k++) {
-        if (deg[k] > 0) {
-          if (stop[k]) {
-            settled[k] = true;
-          } else if (deg[k] == 1) {
-            nbr[k] = rec[k][0].x;
-            settled[k] = true;
-          } else {
-            int32_t res = ROUND_AGAIN;
-            uint32_t tries = WEIGHT_FIRST;
-#pragma unroll
-            for (int j = WEIGHT_FIRST - 1; j >= 0; j--)
-              if (!(y[k][j] > __int_as_float(rec[k][j].y))) { res = rec[k][j].x; tries = j + 1; }
-            if (res != ROUND_AGAIN) { nbr[k] = res; settled[k] = true; ev.weight_tries += tries; }
-          }
-        }
-      }
-    }
-#endif
     if (N2V) {  // randomWalks.cu:141-172
       int32_t x[PPT][N2V_FIRST], v[PPT][N2V_FIRST];
       float y[PPT][N2V_FIRST];
@@ -934,6 +889,43 @@ pack_map_kernel(const int32_t *__restrict__ d_n, const int32_t *__restrict__ key
   }
 }
 
+// The tail of a job whose walks end early (PPR): once only a small fraction of the walks is still
+// alive, a step of the transit-parallel loop is three launches over a few thousand pairs, i.e.
+// pure launch latency.  From there on one launch finishes the job: a thread takes a pair of the
+// sorted map and walks its sample through all remaining steps.  The draws are keyed by (sample,
+// step), so the samples are the ones the step-by-step loop would have produced.
+template <int APP>
+__global__ void __launch_bounds__(256)
+walk_tail_kernel(NdGraphView g, WalkParams wp, int first_step, int64_t first_sample, const void *__restrict__ in_rec,
+                 const int32_t *__restrict__ d_n, int64_t S, int32_t *__restrict__ tmp, int32_t *__restrict__ len,
+                 int *__restrict__ status, unsigned long long *__restrict__ stats) {
+  constexpr bool N2V = APP == ND_APP_NODE2VEC;
+  Events ev;
+  const ndmem::Keep keep;
+  const int n = *d_n;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const MapRec<N2V> r = map_rec_load<N2V>(keep, in_rec, i);
+    int32_t cur = r.t, st = r.pv;
+    int step = first_step;
+    for (; step < wp.steps; step++) {
+      int32_t nbr = -1;
+      if (cur >= 0 && cur < g.V) {
+        const int32_t rs = __ldg(g.row_ptr + cur);
+        const int32_t deg = __ldg(g.row_ptr + cur + 1) - rs;
+        if (deg > 0) {
+          Rng rng(wp.seed, (uint32_t)(first_sample + r.s), (uint32_t)step, 0u);
+          nbr = app_next<APP, false, N2V_BATCH_SP>(g, wp, step, cur, rs, deg, st, rng, status, ev);
+        }
+      }
+      if (nbr < 0) break;
+      tmp[(int64_t)step * S + r.s] = nbr;
+      cur = nbr;
+    }
+    if (step < wp.steps) len[r.s] = step;
+  }
+  if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
+}
+
 // ---------------------------------------------------------------- sample-parallel: a thread owns a walk
 
 template <int APP>
@@ -1089,9 +1081,20 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
       }
       __syncthreads();
       // rows of `steps` ints, ns of them back to back
-      if (kc == steps) {
+      if (kc == steps) {  // the group's rows are one contiguous, 128-byte aligned piece: 16-byte stores
         int32_t *dst = out + s0 * steps;
-        for (int j = threadIdx.x; j < ns * steps; j += FIN_THREADS) dst[j] = tile[j % steps][j / steps];
+        const int total = ns * steps, quads = total >> 2;
+        for (int q = threadIdx.x; q < quads; q += FIN_THREADS) {
+          int i = (4 * q) / steps, k = 4 * q - i * steps;
+          int32_t e[4];
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            e[c] = tile[k][i];
+            if (++k == steps) { k = 0; i++; }
+          }
+          __stcs(reinterpret_cast<int4 *>(dst) + q, make_int4(e[0], e[1], e[2], e[3]));
+        }
+        for (int j = (quads << 2) + threadIdx.x; j < total; j += FIN_THREADS) dst[j] = tile[j % steps][j / steps];
       } else {
         for (int j = threadIdx.x; j < ns * kc; j += FIN_THREADS) {
           const int i = j / kc, k = j % kc;
@@ -1147,7 +1150,9 @@ int launch_count(nd_sampler *s, const WalkParams &wp, int step, bool last, int b
     res = r;
   }
   const int64_t tiles = (s->S + COUNT_THREADS * PPT - 1) / (COUNT_THREADS * PPT);
-  const int64_t cap = (int64_t)s->dev.sms * (ND_TUNE_GRID_PER_SM ? ND_TUNE_GRID_PER_SM : res);
+  // node2vec: as many CTAs as are resident, each working through several tiles (its per-warp queues
+  // fill up over the tiles); the others measured best with up to 16 CTAs per SM, a tile each
+  const int64_t cap = (int64_t)s->dev.sms * (APP == ND_APP_NODE2VEC ? res : 16);
   const int grid = (int)(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
   NdGraphView gv = nd_view(s->g);
   int4 *uext = APP == ND_APP_NODE2VEC && !last ? s->d_uext : nullptr;
@@ -1442,8 +1447,17 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     const void *in_rec = s->d_init_rec;
     const int64_t sblocks = (S + 256 * SCATTER_PPT - 1) / (256 * SCATTER_PPT);
     const int sgrid = (int)(sblocks < (int64_t)s->dev.sms * 16 ? (sblocks > 0 ? sblocks : 1) : (int64_t)s->dev.sms * 16);
+    // PPR: the step-by-step loop runs while a useful share of the walks is expected to be alive
+    // ((1 - stop probability)^k above 1/32), one tail launch finishes the rest
+    int tp_steps = steps;
+    if (app == ND_APP_PPR && s->p.stop_prob > 0.f && !getenv("ND_WALK_NO_TAIL")) {
+      double alive = 1.0;
+      int k = 0;
+      while (k < steps && alive > 1.0 / 32) { alive *= 1.0 - (double)s->p.stop_prob; k++; }
+      tp_steps = k < 1 ? 1 : k;
+    }
     int cur = 0;  // sorted map the scatter of this step writes
-    for (int step = 0; step < steps; step++) {
+    for (int step = 0; step < tp_steps; step++) {
       const bool last = step == steps - 1;
       const int32_t *d_n = s->d_nlive + step;
       int32_t *tmp_step = s->d_tmp + (int64_t)step * S;
@@ -1465,6 +1479,15 @@ static int walk_enqueue(nd_sampler *s, int mode) {
       nd_count_launches(2);
       in_rec = s->d_srec[cur];
       cur ^= 1;
+    }
+    if (tp_steps < steps) {
+      nd_phase_begin(s, ND_PHASE_NEXT);
+      const int64_t tb = (S / 16 + 255) / 256;   // sized for the expected survivors; the loop strides over more
+      const int tgrid = (int)(tb < (int64_t)s->dev.sms * 8 ? (tb > 0 ? tb : 1) : (int64_t)s->dev.sms * 8);
+      walk_tail_kernel<ND_APP_PPR><<<tgrid, 256, 0, st>>>(nd_view(s->g), wp, tp_steps, s->first, in_rec, s->d_nlive + tp_steps, S,
+                                                         s->d_tmp, s->d_len, s->d_status, s->d_stats);
+      nd_phase_end(s);
+      nd_count_launches(1);
     }
   }
   nd_phase_begin(s, ND_PHASE_FINALIZE);

@@ -2,6 +2,8 @@
 // source-compatibility headers of include/nextdoor/ and run on the GPU by tests/test_gpu_compat.py.
 // The first group is this project's own; with -DNDC_WITH_REFERENCE the reference's application
 // files are compiled in as well, unchanged, from the reference tree (never copied into the repo).
+#include <chrono>
+
 #include "nextdoor.cu"
 #include "libNextDoor.hpp"
 #include "main.cu"
@@ -210,6 +212,49 @@ static int run_app(const char *file, const char *kernel, int lb, int32_t *out, i
   freeDeviceData(data);
   delete csr;
   return 0;
+}
+
+// Times the sampling call alone, the way the reference prints its "End to end time"
+// (src/nextdoor.cu:2363, 2963-2965: a host clock around the step loop): `nruns` calls after one
+// warm-up call; seconds per call and the valid vertices of the last call's final samples.
+template <class SampleType, typename App>
+static int time_app(const char *file, const char *kernel, int lb, int nruns, double *seconds, int64_t *sampled) {
+  Graph graph;
+  CSR *csr = loadGraph(graph, (char *)file, (char *)"edge-list", (char *)"binary");
+  if (!csr) return 1;
+  NextDoorData<SampleType, App> data;
+  if (!allocNextDoorDataOnGPU<SampleType, App>(csr, data)) return 2;
+  data.gpuCSRPartitions = transferCSRToGPUs(data, csr);
+  const bool sp = strcmp(kernel, "SampleParallel") == 0;
+  double total = 0.0;
+  for (int i = 0; i <= nruns; i++) {
+    const auto t0 = std::chrono::steady_clock::now();
+    const bool ok = sp ? doSampleParallelSampling<SampleType, App>(csr, data) : doTransitParallelSampling<SampleType, App>(csr, data, lb != 0);
+    const auto t1 = std::chrono::steady_clock::now();
+    if (!ok) return 3;
+    if (i > 0) total += std::chrono::duration<double>(t1 - t0).count();
+  }
+  *seconds = total / (nruns > 0 ? nruns : 1);
+  std::vector<VertexID_t> &fin = getFinalSamples(data);
+  int64_t c = 0;
+  for (VertexID_t v : fin) c += v != data.INVALID_VERTEX && v != -1;
+  *sampled = c;
+  freeDeviceData(data);
+  delete csr;
+  return 0;
+}
+
+extern "C" int ndc_time(int which, const char *file, const char *kernel, int lb, int nruns, double *seconds, int64_t *sampled) {
+  switch (which) {
+    case 0: return time_app<PlainSample, OwnUniformWalk>(file, kernel, lb, nruns, seconds, sampled);
+    case 1: return time_app<PlainSample, OwnWeightedWalk>(file, kernel, lb, nruns, seconds, sampled);
+#ifdef NDC_WITH_REFERENCE
+    case 10: return time_app<UniformRandomWalkSample, UniformRandomWalkApp>(file, kernel, lb, nruns, seconds, sampled);
+    case 11: return time_app<DummySample, DeepWalkApp>(file, kernel, lb, nruns, seconds, sampled);
+    case 13: return time_app<Node2VecSample, Node2VecApp>(file, kernel, lb, nruns, seconds, sampled);
+#endif
+    default: return -1;
+  }
 }
 
 extern "C" int ndc_run(int which, const char *file, const char *kernel, int lb, int32_t *out, int64_t cap, int64_t *n_out,
