@@ -510,7 +510,9 @@ def main():
         for _ in range(a.warmup + a.steps):
             smp.sample(mode, sync=False)
         barrier()
-        print(json.dumps({"profile_only": True, "workload": a.workload, "mode": a.mode, "stats": smp.stats()}))
+        live = smp.live_pairs()[:30].tolist() if wl["kind"] == WALK and mode != 2 else None
+        print(json.dumps({"profile_only": True, "workload": a.workload, "mode": a.mode, "stats": smp.stats(),
+                          "live_pairs_of_the_first_steps": live}))
         return
 
     # ---- device-timed throughput (inputs resident)
@@ -582,7 +584,6 @@ def main():
         smp2 = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=init_np)
         smp2.set_stream(stream.cuda_stream)
         pair = [(smp, nd_dist.device_samples(smp)), (smp2, nd_dist.device_samples(smp2))]
-        ranges = [nd.shard_range(S_total, r, world) for r in range(world)]
         n_full = 2 if 2 * S_total * fs * 4 < (48 << 30) else 1
         fulls = [torch.empty((S_total, fs), dtype=torch.int32, device="cuda") for _ in range(n_full)] if rank == 0 else []
         side = torch.cuda.Stream()
@@ -605,13 +606,7 @@ def main():
                 wait_all(k ^ 1)                # the single gathered array is still being written
             with torch.cuda.stream(side):
                 side.wait_event(ev)
-                if rank == 0:
-                    full = fulls[k % n_full]
-                    full[first:first + S].copy_(shard_k, non_blocking=True)
-                    ops = [dist.P2POp(dist.irecv, full[f:f + c], r) for r, (f, c) in enumerate(ranges) if r != 0 and c > 0]
-                else:
-                    ops = [dist.P2POp(dist.isend, shard_k, 0)] if S > 0 else []
-                pending[k] = dist.batch_isend_irecv(ops) if ops else None
+                pending[k] = nd_dist.gather_samples_start(shard_k, S_total, fulls[k % n_full] if rank == 0 else None) or None
 
         def gather_drain():
             for k in range(2):

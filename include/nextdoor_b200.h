@@ -150,6 +150,11 @@ int nd_sampler_aux(nd_sampler *s, int32_t *adj_row, int32_t *adj_col, float *pro
  * tries, [4] node2vec binary-search probes, [5] neighbour ids gathered for collective unions,
  * [6] unique candidates; n <= 8 */
 int nd_sampler_stats(nd_sampler *s, int64_t *stats, int n);
+/* walks in a transit-parallel mode: live[k] = (transit, sample) pairs that entered step k of the last
+ * sample(), i.e. the size of the step's map (the reference prints the same as "totalThreads" per
+ * step, src/nextdoor.cu:2400-2410); entries of steps the run did not take step by step are those of
+ * an earlier run or zero.  n <= steps. */
+int nd_sampler_live_pairs(nd_sampler *s, int32_t *live, int n);
 /* per-phase device time of the last sample() when profiling is on: see nd_phase */
 typedef enum nd_phase {
   ND_PHASE_NEXT = 0, ND_PHASE_INVERT = 1, ND_PHASE_BIN = 2, ND_PHASE_FINALIZE = 3,

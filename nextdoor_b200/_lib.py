@@ -77,6 +77,7 @@ _SIGS = {
     "nd_sampler_final_samples_device": (C.c_int, [VP, C.POINTER(VP)]),
     "nd_sampler_aux": (C.c_int, [VP, VP, VP, VP, VP]),
     "nd_sampler_stats": (C.c_int, [VP, VP, C.c_int]),
+    "nd_sampler_live_pairs": (C.c_int, [VP, VP, C.c_int]),
     "nd_sampler_set_profiling": (C.c_int, [VP, C.c_int]),
     "nd_sampler_phase_ms": (C.c_int, [VP, VP, VP, C.c_int]),
     "nd_sampler_next_kernel": (C.c_int, [VP, C.c_int, C.c_char_p, C.c_int]),

@@ -218,6 +218,12 @@ class Sampler:
         return dict(sampled_edges=int(st[0]), live_pairs=int(st[1]), weight_tries=int(st[2]),
                     n2v_tries=int(st[3]), n2v_probes=int(st[4]), union_ids=int(st[5]), union_unique=int(st[6]))
 
+    def live_pairs(self):
+        """Walks, transit-parallel modes: pairs that entered each step of the last sample()."""
+        live = np.zeros(self.params.steps, np.int32)
+        check(lib.nd_sampler_live_pairs(self._h, _ptr(live), live.shape[0]))
+        return live
+
     def set_profiling(self, on=True):
         check(lib.nd_sampler_set_profiling(self._h, int(on)))
 

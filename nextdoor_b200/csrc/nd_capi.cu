@@ -310,6 +310,16 @@ int nd_sampler_stats(nd_sampler *s, int64_t *stats, int n) {
   return ND_OK;
 }
 
+int nd_sampler_live_pairs(nd_sampler *s, int32_t *live, int n) {
+  ND_REQUIRE(s && live && n >= 1, ND_ERR_ARG, "nd_sampler_live_pairs: bad argument");
+  ND_REQUIRE(nd_is_walk(s->p.app), ND_ERR_ARG, "nd_sampler_live_pairs: walk applications only");
+  ND_TRY(nd_sampler_sync(s));
+  const int m = n < s->p.steps ? n : s->p.steps;
+  ND_CUDA(cudaMemcpy(live, s->d_nlive, sizeof(int32_t) * (size_t)m, cudaMemcpyDeviceToHost));
+  for (int i = m; i < n; i++) live[i] = 0;
+  return ND_OK;
+}
+
 int nd_sampler_set_profiling(nd_sampler *s, int on) {
   ND_REQUIRE(s, ND_ERR_ARG, "null sampler");
   s->timer.on = on != 0;

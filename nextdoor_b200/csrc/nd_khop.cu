@@ -309,10 +309,12 @@ khop_staged_kernel(NdGraphView g, KhopParams kp, const int32_t *__restrict__ in_
     const int32_t a0 = rs & ~3;
     const int32_t a1 = (rs + deg + 3) & ~3;
     const int win = a1 - a0;
-    bool staged = win <= STAGE_CAP;
+    // after a bulk copy whose wait ran out, the CTA stops using `stage` altogether: that copy may
+    // still land there, so every later item gathers from global memory
+    bool staged = win <= STAGE_CAP && tma_ok;
     sh_q[threadIdx.x] = threadIdx.x < item.y ? in_val[item.x + threadIdx.x] : 0;  // one coalesced load, overlaps the copy
     if (staged) {
-      if (win >= TMA_MIN_INTS && tma_ok) {
+      if (win >= TMA_MIN_INTS) {
         if (threadIdx.x == 0) {
           // the previous item's reads of `stage` are ordered before this async write
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -134,10 +134,7 @@ __device__ __forceinline__ int32_t weighted_round(const WalkParams &wp, int32_t 
   int2 rec[BATCH];
 #pragma unroll
   for (int k = 0; k < BATCH; k++) {
-    int32_t x = rng.rand_int(n);
-#ifdef ND_DIAG_HUB_FREE   // measurement only: what any staging of hub lists could save at most (hub gathers share one sector)
-    if (n >= ND_DIAG_HUB_FREE) x &= 3;
-#endif
+    const int32_t x = rng.rand_int(n);
     y[k] = __fmul_rn(rng.uniform(), max_w);
     rec[k] = ld_graph<STREAM>(recs + x);
   }
@@ -516,11 +513,7 @@ __device__ __forceinline__ void count_emit(const ndmem::Keep &keep, int i, int32
                                            uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum,
                                            int32_t *__restrict__ tmp_step, int32_t *__restrict__ len,
                                            int4 *__restrict__ out_ext, int32_t t, int32_t rs, int32_t deg) {
-#ifndef ND_DIAG_NO_TMP
   if (nbr >= 0) keep.st(tmp_step + s, nbr); else len[s] = step;
-#else
-  if (nbr < 0) len[s] = step;
-#endif
   if (COUNT) {
     keep.st(out_key + i, nbr >= 0 ? nbr : V);
     if (nbr >= 0) {
@@ -624,17 +617,8 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
 #pragma unroll
       for (int k = 0; k < PPT; k++) {
         Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
-        int32_t x = rng.rand_int(deg[k] > 0 ? deg[k] : 1);
-#ifdef ND_DIAG_HUB_FREE
-        if (deg[k] >= ND_DIAG_HUB_FREE) x &= 7;
-#endif
-#if defined(ND_DIAG_NO_GATHER)
-        if (deg[k] > 0) nbr[k] = (int32_t)(((uint32_t)(rs[k] + x) * 2654435761u) % (uint32_t)g.V);
-#elif defined(ND_DIAG_LDG)
-        if (deg[k] > 0) nbr[k] = __ldg(g.col + rs[k] + x);
-#else
+        const int32_t x = rng.rand_int(deg[k] > 0 ? deg[k] : 1);
         if (deg[k] > 0) nbr[k] = __ldcs(g.col + rs[k] + x);
-#endif
         settled[k] = true;
       }
     }
@@ -1056,6 +1040,7 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
                      unsigned long long *__restrict__ stats) {
   __shared__ int32_t tile[FIN_MAX_STEPS][FIN_SAMPLES + 1];
   __shared__ int32_t sh_len[FIN_SAMPLES];
+  __shared__ int32_t sh_maxlen;   // longest walk of the group: slots beyond it are invalid in every row
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t groups = (S + FIN_SAMPLES - 1) / FIN_SAMPLES;
   unsigned long long edges = 0, live = 0;
@@ -1069,12 +1054,16 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
         edges += l > 0 ? l : 0;
         live += l < 0 ? 0 : (l < steps ? l + 1 : steps);
       }
+      const int32_t m = __reduce_max_sync(0xffffffffu, l);   // FIN_SAMPLES = one warp
+      if (threadIdx.x == 0) sh_maxlen = m;
     }
     __syncthreads();
+    const int maxlen = sh_maxlen;
     for (int k0 = 0; k0 < steps; k0 += FIN_MAX_STEPS) {
       const int kc = steps - k0 < FIN_MAX_STEPS ? steps - k0 : FIN_MAX_STEPS;
       const int32_t mylen = sh_len[lane];
-      for (int k = warp; k < kc; k += FIN_THREADS / 32) {
+      const int lim = maxlen - k0 < kc ? (maxlen - k0 > 0 ? maxlen - k0 : 0) : kc;   // staged rows of this chunk that hold anything
+      for (int k = warp; k < lim; k += FIN_THREADS / 32) {
         int32_t v = invalid;
         if (lane < ns && k0 + k < mylen) v = tmp[(int64_t)(k0 + k) * S + s0 + lane];
         tile[k][lane] = v;
@@ -1089,16 +1078,16 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
           int32_t e[4];
 #pragma unroll
           for (int c = 0; c < 4; c++) {
-            e[c] = tile[k][i];
+            e[c] = k < lim ? tile[k][i] : invalid;
             if (++k == steps) { k = 0; i++; }
           }
           __stcs(reinterpret_cast<int4 *>(dst) + q, make_int4(e[0], e[1], e[2], e[3]));
         }
-        for (int j = (quads << 2) + threadIdx.x; j < total; j += FIN_THREADS) dst[j] = tile[j % steps][j / steps];
+        for (int j = (quads << 2) + threadIdx.x; j < total; j += FIN_THREADS) dst[j] = j % steps < lim ? tile[j % steps][j / steps] : invalid;
       } else {
         for (int j = threadIdx.x; j < ns * kc; j += FIN_THREADS) {
           const int i = j / kc, k = j % kc;
-          out[(s0 + i) * steps + k0 + k] = tile[k][i];
+          out[(s0 + i) * steps + k0 + k] = k < lim ? tile[k][i] : invalid;
         }
       }
       __syncthreads();
@@ -1447,13 +1436,14 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     const void *in_rec = s->d_init_rec;
     const int64_t sblocks = (S + 256 * SCATTER_PPT - 1) / (256 * SCATTER_PPT);
     const int sgrid = (int)(sblocks < (int64_t)s->dev.sms * 16 ? (sblocks > 0 ? sblocks : 1) : (int64_t)s->dev.sms * 16);
-    // PPR: the step-by-step loop runs while a useful share of the walks is expected to be alive
-    // ((1 - stop probability)^k above 1/32), one tail launch finishes the rest
+    // PPR: the step-by-step loop runs while enough walks are expected to be alive for a step to be
+    // more than launch latency (S * (1 - stop probability)^k above S/32 and above 512 K pairs), one
+    // tail launch finishes the rest
     int tp_steps = steps;
     if (app == ND_APP_PPR && s->p.stop_prob > 0.f && !getenv("ND_WALK_NO_TAIL")) {
       double alive = 1.0;
       int k = 0;
-      while (k < steps && alive > 1.0 / 32) { alive *= 1.0 - (double)s->p.stop_prob; k++; }
+      while (k < steps && alive > 1.0 / 32 && alive * (double)S > 524288.0) { alive *= 1.0 - (double)s->p.stop_prob; k++; }
       tp_steps = k < 1 ? 1 : k;
     }
     int cur = 0;  // sorted map the scatter of this step writes
@@ -1482,7 +1472,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     }
     if (tp_steps < steps) {
       nd_phase_begin(s, ND_PHASE_NEXT);
-      const int64_t tb = (S / 16 + 255) / 256;   // sized for the expected survivors; the loop strides over more
+      const int64_t tb = (S / 4 + 255) / 256;    // sized for the expected survivors; the loop strides over more
       const int tgrid = (int)(tb < (int64_t)s->dev.sms * 8 ? (tb > 0 ? tb : 1) : (int64_t)s->dev.sms * 8);
       walk_tail_kernel<ND_APP_PPR><<<tgrid, 256, 0, st>>>(nd_view(s->g), wp, tp_steps, s->first, in_rec, s->d_nlive + tp_steps, S,
                                                          s->d_tmp, s->d_len, s->d_status, s->d_stats);

@@ -50,3 +50,36 @@ def all_gather_samples(local: torch.Tensor, total: int, group=None) -> torch.Ten
     if all(c == longest for c in counts):
         return out
     return torch.cat([out[r * longest: r * longest + counts[r]] for r in range(world)], dim=0)
+
+
+def gather_samples_start(local: torch.Tensor, total: int, full: torch.Tensor | None, dst: int = 0, group=None):
+    """Starts the transfer of every rank's shard [count_r, fs] to rank `dst`, which places the shards
+    in rank order in `full` [total, fs] -- the concatenation getFinalSamples makes across devices
+    (src/nextdoor.cu:3211-3237), but landing on ONE rank instead of all of them.  Point-to-point
+    sends and receives (NCCL or gloo); `full` is only used on `dst`.  Returns the list of pending
+    work handles: wait for all of them before `full` is read or `local` is overwritten."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    first, count = shard(total, rank, world)
+    assert local.shape[0] == count, "local shard does not have the reference's shard size"
+    if rank == dst:
+        assert full is not None and full.shape[0] == total
+        if count:
+            full[first:first + count].copy_(local, non_blocking=True)
+        ops = []
+        for r in range(world):
+            f, c = shard(total, r, world)
+            if r != dst and c > 0:
+                ops.append(dist.P2POp(dist.irecv, full[f:f + c], r, group))
+    else:
+        ops = [dist.P2POp(dist.isend, local, dst, group)] if count > 0 else []
+    return dist.batch_isend_irecv(ops) if ops else []
+
+
+def gather_samples_to(local: torch.Tensor, total: int, dst: int = 0, group=None):
+    """Blocking form: returns [total, fs] on rank `dst`, None elsewhere."""
+    rank = dist.get_rank(group)
+    full = torch.empty((total, local.shape[1]), dtype=local.dtype, device=local.device) if rank == dst else None
+    for w in gather_samples_start(local.contiguous(), total, full, dst, group):
+        w.wait()
+    return full

@@ -25,9 +25,11 @@ def _worker(rank, world, port, total, fs_steps, ret):
     first, count = nd_dist.shard(total, rank, world)
     local = ndo.sample(g, pr, count, first=first)["out"]
     full = nd_dist.all_gather_samples(torch.from_numpy(local.copy()), total)
+    one = nd_dist.gather_samples_to(torch.from_numpy(local.copy()), total, dst=0)     # the gather the benchmark times
+    assert (one is None) == (rank != 0)
     if rank == 0:
         whole = ndo.sample(g, pr, total)["out"]
-        ret["ok"] = bool(np.array_equal(full.numpy(), whole))
+        ret["ok"] = bool(np.array_equal(full.numpy(), whole)) and bool(np.array_equal(one.numpy(), whole))
         ret["ranges"] = [nd_dist.shard(total, r, world) for r in range(world)]
     dist.destroy_process_group()
 

@@ -54,6 +54,64 @@ def test_invert_map_matches_oracle(nd, ndo, n, vmax):
     assert np.array_equal(ov.cpu().numpy()[:live.value], ev)      # stable: equal keys keep their order
 
 
+def test_stream_ordered_inverter_matches_oracle(nd, ndo):
+    """nd_inverter_run: the scratch allocated once, calls of different sizes back to back on a
+    caller stream without any wait in between, the live count read from the device afterwards."""
+    import torch
+    vmax, cap = 5000, 300_000
+    inv = C.c_void_p()
+    nd.check(nd.lib.nd_inverter_create(0, cap, vmax, C.byref(inv)))
+    st = torch.cuda.Stream()
+    rng = np.random.default_rng(3)
+    jobs = []
+    with torch.cuda.stream(st):
+        for n in (cap, 1, 77_777, 2048):
+            keys = rng.integers(0, vmax + 1, n).astype(np.int32)      # vmax itself = dead pairs
+            vals = rng.permutation(n).astype(np.int32)
+            dk, dv = _dev(keys), _dev(vals)
+            ok, ov = torch.empty_like(dk), torch.empty_like(dv)
+            d_live = C.c_void_p()
+            nd.check(nd.lib.nd_inverter_run(inv, st.cuda_stream, n, dk.data_ptr(), dv.data_ptr(), ok.data_ptr(), ov.data_ptr(),
+                                            C.byref(d_live)))
+            live = torch.empty(1, dtype=torch.int32, device="cuda")   # the count of THIS run, copied in stream order
+            src = torch.as_tensor(_DevInt(d_live.value), device="cuda")
+            live.copy_(src)
+            jobs.append((keys, vals, ok, ov, live, dk, dv))
+    st.synchronize()
+    for keys, vals, ok, ov, live, _, _ in jobs:
+        ek, ev = ndo.invert_map(keys, vals, vmax)
+        n_live = int(live.item())
+        assert n_live == ek.shape[0]
+        assert np.array_equal(ok.cpu().numpy()[:n_live], ek) and np.array_equal(ov.cpu().numpy()[:n_live], ev)
+    assert nd.lib.nd_inverter_run(inv, st.cuda_stream, cap + 1, 1, 1, 1, 1, None) != 0      # beyond the capacity: refused
+    nd.check(nd.lib.nd_inverter_destroy(inv))
+
+
+class _DevInt:
+    """One int32 in device memory owned by the library, as a CUDA array."""
+
+    def __init__(self, ptr):
+        self.__cuda_array_interface__ = {"shape": (1,), "typestr": "<i4", "data": (int(ptr), False), "version": 3}
+
+
+def test_sampler_reports_its_kernel_and_live_pairs(nd, ndo, small_graph):
+    g = nd.Graph.from_csr(small_graph.row_ptr, small_graph.col, small_graph.w, small_graph.max_w)
+    pr = nd.app_params(0, steps=10, seed=1)
+    s = nd.Sampler(g, pr, num_samples=3000)
+    buf = C.create_string_buffer(128)
+    names = []
+    for mode in (0, 1, 2):
+        nd.check(nd.lib.nd_sampler_next_kernel(s._h, mode, buf, 128))
+        names.append(buf.value.decode())
+    assert names == ["walk_next_tp_kernel<uniform walk>", "walk_next_count_kernel<uniform walk>", "walk_sp_kernel<uniform walk>"]
+    s.sample(1)
+    live = s.live_pairs()
+    exp = ndo.sample(small_graph, ndo.make_params(0, steps=10, seed=1), 3000)
+    assert int(live.sum()) == exp["counters"]["live_pairs"]
+    deg = small_graph.degree()
+    assert live[0] == 3000 and live[1] == int((deg[np.arange(3000) % small_graph.V] > 0).sum())
+
+
 def test_invert_map_all_dead_and_empty(nd):
     import torch
     live = C.c_int64(-1)

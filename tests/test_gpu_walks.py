@@ -53,6 +53,28 @@ def test_walks_match_oracle(nd, ndo, small_graph, app, mode):
         assert np.array_equal(s.final_samples(), exp["out"])
 
 
+@pytest.mark.parametrize("no_tail", ["0", "1"])
+def test_ppr_tail_launch_and_step_loop_agree(nd, ndo, small_graph, monkeypatch, no_tail):
+    """PPR in the load-balanced mode finishes the few walks that are still alive with one tail
+    launch; ND_WALK_NO_TAIL=1 keeps the step-by-step loop to the end.  Both give the oracle's walks
+    and counters."""
+    if no_tail == "1":
+        monkeypatch.setenv("ND_WALK_NO_TAIL", "1")
+    else:
+        monkeypatch.delenv("ND_WALK_NO_TAIL", raising=False)
+    g = _graph(nd, small_graph)
+    pr = nd.app_params(2, steps=60, seed=21, stop_prob=0.15)
+    opr = ndo.make_params(2, steps=60, seed=21, stop_prob=0.15)
+    S = 20_000
+    s = nd.Sampler(g, pr, num_samples=S, first_sample=3)
+    s.sample(1)
+    exp = ndo.sample(small_graph, opr, S, first=3)
+    assert np.array_equal(s.final_samples(), exp["out"])
+    st = s.stats()
+    assert st["sampled_edges"] == exp["counters"]["sampled_edges"] and st["live_pairs"] == exp["counters"]["live_pairs"]
+    assert st["weight_tries"] == exp["counters"]["weight_tries"]
+
+
 @pytest.mark.parametrize("mode", MODES)
 def test_node2vec_corrected_comparison(nd, ndo, small_graph, mode):
     g = _graph(nd, small_graph)
