@@ -140,7 +140,9 @@ int nd_sampler_final_samples(nd_sampler *s, int32_t *out);
  * (nd_stream_sync) before reading `out` and before the next sample() of this sampler. */
 int nd_sampler_final_samples_async(nd_sampler *s, int32_t *out, void *copy_stream);
 int nd_stream_sync(int device, void *stream);
-/* zero-copy variant: device address of the same array */
+/* zero-copy variant: device address of the same array.  READ-ONLY for the caller: for the walk
+ * applications the library keeps the array between sample() calls and rewrites only the slots a
+ * walk uses now or used in the previous call (the rest holds the invalid id already). */
 int nd_sampler_final_samples_device(nd_sampler *s, const int32_t **out);
 /* collective apps: adjacency rows/cols (num_samples*steps*max(batch,L)*L each) and, for the
  * importance apps, the probability of every sampled vertex; k-hop distinct: per-hop counts */

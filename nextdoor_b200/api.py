@@ -349,7 +349,8 @@ class SamplingModule:
         """The final samples as a CUDA tensor [numSamples, finalSampleSize] that aliases the
         library's device buffer: no device-to-host copy and no Python list (the reference builds the
         list element by element, src/nextDoorPythonModule.cu:60-72).  Valid until the next sample()
-        or freeDeviceMemory(); hand it to a loader as is or through DLPack (torch.utils.dlpack)."""
+        or freeDeviceMemory(); hand it to a loader as is or through DLPack (torch.utils.dlpack).
+        Treat it as read-only: the library keeps this array between calls and rewrites only what changes."""
         from . import dist as _dist
         return _dist.device_samples(self._sampler)
 

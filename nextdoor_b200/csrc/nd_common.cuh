@@ -156,6 +156,7 @@ struct nd_sampler {
   // walks
   int32_t *d_tmp = nullptr;       // [steps][S] step-major staging of the walk output
   int32_t *d_len = nullptr;       // [S] number of valid steps of each walk
+  int32_t *d_plen = nullptr;      // [S] walks: leading slots of the sample's row in d_out that may hold a vertex (the rest is invalid)
   int32_t *d_state = nullptr;     // [S] per-sample app state (node2vec: previous vertex)
   // transit maps (ping-pong); key = transit, val = pair id
   int32_t *d_map_key[2] = {nullptr, nullptr};

@@ -240,7 +240,8 @@ __device__ __forceinline__ int32_t n2v_next_known(const NdGraphView &g, const Wa
 template <int APP, bool STREAM = true, int N2V_BATCH = N2V_BATCH_COUNT>
 __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkParams &wp, int step,
                                             int32_t transit, int32_t rs, int32_t n, int32_t &state_t,
-                                            Rng &rng, int *status, Events &ev) {
+                                            Rng &rng, int *status, Events &ev, bool have_max_w = false,
+                                            float max_w_in = 0.f) {  // weighted apps: the transit's maximum weight, if the caller fetched it beside the row offsets
   const int32_t *__restrict__ edges = g.col + rs;
   if (APP == ND_APP_UNIFORM_WALK) {  // example/uniformRandWalk.cu:35-36
     return ld_graph<STREAM>(edges + rng.rand_int(n));
@@ -251,7 +252,7 @@ __device__ __forceinline__ int32_t app_next(const NdGraphView &g, const WalkPara
       if (pr < wp.stop_prob) return -1;
     }
     if (n == 1) return ld_graph<STREAM>(edges);
-    const float max_w = __ldg(g.max_w + transit);
+    const float max_w = have_max_w ? max_w_in : __ldg(g.max_w + transit);
     constexpr int WEIGHT_BATCH = weight_batch<APP, STREAM>();
     for (int it = 0; it <= RETRY_CAP; it += WEIGHT_BATCH) {
       const int32_t r = weighted_round<STREAM, WEIGHT_BATCH>(wp, rs, n, max_w, rng, ev);
@@ -602,12 +603,15 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
       t[k] = r.t; s[k] = r.s; pv[k] = r.pv; prow[k] = r.prow;
     }
     // ---- row offsets
+    float mw[PPT];
 #pragma unroll
     for (int k = 0; k < PPT; k++) {
+      mw[k] = 0.f;
       const bool ok = live[k] && t[k] >= 0 && t[k] < g.V;
       if (live[k] && !ok) atomicOr(status, ND_DEV_BAD_TRANSIT);
       rs[k] = ok ? keep.ld_const(g.row_ptr + t[k]) : 0;
       deg[k] = ok ? keep.ld_const(g.row_ptr + t[k] + 1) - rs[k] : 0;
+      if (WEIGHTED) mw[k] = ok ? __ldg(g.max_w + t[k]) : 0.f;   // independent of the row offsets: one latency, not two
       nbr[k] = -1;
       cont[k] = false;
       settled[k] = deg[k] <= 0;  // next() runs only on transits with edges (src/nextdoor.cu:255,412)
@@ -628,7 +632,7 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
         if (deg[k] > 0) {
           Rng rng(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)step, 0u);
           int32_t st = 0;
-          nbr[k] = app_next<APP>(g, wp, step, t[k], rs[k], deg[k], st, rng, status, ev);
+          nbr[k] = app_next<APP>(g, wp, step, t[k], rs[k], deg[k], st, rng, status, ev, true, mw[k]);
           settled[k] = true;
         }
       }
@@ -894,11 +898,15 @@ walk_tail_kernel(NdGraphView g, WalkParams wp, int first_step, int64_t first_sam
     for (; step < wp.steps; step++) {
       int32_t nbr = -1;
       if (cur >= 0 && cur < g.V) {
+        // the walk's chain of dependent loads is what this launch lasts: row offsets and maximum
+        // weight are fetched together, so a step is two memory latencies (vertex, then edge records)
         const int32_t rs = __ldg(g.row_ptr + cur);
         const int32_t deg = __ldg(g.row_ptr + cur + 1) - rs;
+        const bool weighted = APP == ND_APP_DEEPWALK || APP == ND_APP_PPR;
+        const float mw = weighted ? __ldg(g.max_w + cur) : 0.f;
         if (deg > 0) {
           Rng rng(wp.seed, (uint32_t)(first_sample + r.s), (uint32_t)step, 0u);
-          nbr = app_next<APP, false, N2V_BATCH_SP>(g, wp, step, cur, rs, deg, st, rng, status, ev);
+          nbr = app_next<APP, false, N2V_BATCH_SP>(g, wp, step, cur, rs, deg, st, rng, status, ev, weighted, mw);
         }
       }
       if (nbr < 0) break;
@@ -1032,15 +1040,17 @@ walk_sp_rounds_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_
 
 constexpr int FIN_SAMPLES = 32;   // samples per CTA
 constexpr int FIN_THREADS = 256;
-constexpr int FIN_MAX_STEPS = 128;  // steps per smem chunk
 
+// Step-major staging -> the reference's sample-major rows, every row written whole: a CTA takes 32
+// samples, transposes through shared memory and stores 16 bytes per thread.  The kernel of the
+// apps whose walks run their full length (uniform walk, DeepWalk, node2vec).
+constexpr int FIN_MAX_STEPS = 128;  // steps per smem chunk
 __global__ void __launch_bounds__(FIN_THREADS)
-walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict__ len, int64_t S,
+walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict__ len, int32_t *__restrict__ plen, int64_t S,
                      int steps, int32_t invalid, int32_t *__restrict__ out,
                      unsigned long long *__restrict__ stats) {
   __shared__ int32_t tile[FIN_MAX_STEPS][FIN_SAMPLES + 1];
   __shared__ int32_t sh_len[FIN_SAMPLES];
-  __shared__ int32_t sh_maxlen;   // longest walk of the group: slots beyond it are invalid in every row
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t groups = (S + FIN_SAMPLES - 1) / FIN_SAMPLES;
   unsigned long long edges = 0, live = 0;
@@ -1051,19 +1061,16 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
       const int32_t l = threadIdx.x < ns ? len[s0 + threadIdx.x] : -1;
       sh_len[threadIdx.x] = l;
       if (threadIdx.x < ns) {
+        plen[s0 + threadIdx.x] = l > 0 ? l : 0;   // every row is written whole: its slots beyond the walk hold the invalid id
         edges += l > 0 ? l : 0;
         live += l < 0 ? 0 : (l < steps ? l + 1 : steps);
       }
-      const int32_t m = __reduce_max_sync(0xffffffffu, l);   // FIN_SAMPLES = one warp
-      if (threadIdx.x == 0) sh_maxlen = m;
     }
     __syncthreads();
-    const int maxlen = sh_maxlen;
     for (int k0 = 0; k0 < steps; k0 += FIN_MAX_STEPS) {
       const int kc = steps - k0 < FIN_MAX_STEPS ? steps - k0 : FIN_MAX_STEPS;
       const int32_t mylen = sh_len[lane];
-      const int lim = maxlen - k0 < kc ? (maxlen - k0 > 0 ? maxlen - k0 : 0) : kc;   // staged rows of this chunk that hold anything
-      for (int k = warp; k < lim; k += FIN_THREADS / 32) {
+      for (int k = warp; k < kc; k += FIN_THREADS / 32) {
         int32_t v = invalid;
         if (lane < ns && k0 + k < mylen) v = tmp[(int64_t)(k0 + k) * S + s0 + lane];
         tile[k][lane] = v;
@@ -1078,16 +1085,16 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
           int32_t e[4];
 #pragma unroll
           for (int c = 0; c < 4; c++) {
-            e[c] = k < lim ? tile[k][i] : invalid;
+            e[c] = tile[k][i];
             if (++k == steps) { k = 0; i++; }
           }
           __stcs(reinterpret_cast<int4 *>(dst) + q, make_int4(e[0], e[1], e[2], e[3]));
         }
-        for (int j = (quads << 2) + threadIdx.x; j < total; j += FIN_THREADS) dst[j] = j % steps < lim ? tile[j % steps][j / steps] : invalid;
+        for (int j = (quads << 2) + threadIdx.x; j < total; j += FIN_THREADS) dst[j] = tile[j % steps][j / steps];
       } else {
         for (int j = threadIdx.x; j < ns * kc; j += FIN_THREADS) {
           const int i = j / kc, k = j % kc;
-          out[(s0 + i) * steps + k0 + k] = k < lim ? tile[k][i] : invalid;
+          out[(s0 + i) * steps + k0 + k] = tile[k][i];
         }
       }
       __syncthreads();
@@ -1102,6 +1109,99 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
     if (edges) atomicAdd(&stats[0], edges);
     if (live) atomicAdd(&stats[1], live);
   }
+}
+
+
+// The result array keeps its contents from pass to pass, and the kernel keeps the invariant that
+// out[s][k] holds the invalid id for every k >= plen[s]: a pass therefore only has to write the
+// slots a walk fills now or filled last time.  For walks that end early (PPR: 3 valid steps on
+// average in rows of 100) that is a few per cent of the array, where writing every row in full is
+// 6.7 GB per pass on the 2^24-vertex job and as long as a quarter of the sampling itself.  Groups
+// of 32 samples whose rows need more than FIN_SPARSE slots on average (a scattered 4-byte store
+// costs the memory system a sector, so beyond that writing the rows whole is cheaper) go through
+// the shared-memory transpose and are written whole, with 16-byte stores.
+constexpr int FIN_SPARSE = 8;
+constexpr int FIN_BATCH = 8;    // staged rows a lane reads at once
+
+__global__ void __launch_bounds__(FIN_THREADS)
+walk_finalize_sparse_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict__ len, int32_t *__restrict__ plen, int64_t S,
+                     int steps, int32_t invalid, int32_t *__restrict__ out,
+                     unsigned long long *__restrict__ stats) {
+  // a warp owns a group of 32 samples (lane = sample) from start to end: no block barrier anywhere
+  __shared__ int32_t tiles[FIN_THREADS / 32][32][FIN_SAMPLES + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int32_t (*tile)[FIN_SAMPLES + 1] = tiles[warp];
+  const int64_t groups = (S + FIN_SAMPLES - 1) / FIN_SAMPLES;
+  const int64_t warps = (int64_t)gridDim.x * (FIN_THREADS / 32);
+  unsigned long long edges = 0, live = 0;
+  for (int64_t grp = (int64_t)blockIdx.x * (FIN_THREADS / 32) + warp; grp < groups; grp += warps) {
+    const int64_t s0 = grp * FIN_SAMPLES;
+    const int ns = (int)(S - s0 < FIN_SAMPLES ? S - s0 : FIN_SAMPLES);
+    const int32_t l = lane < ns ? len[s0 + lane] : -1;
+    const int32_t had = lane < ns ? plen[s0 + lane] : 0;
+    const int32_t now = l > 0 ? l : 0;
+    const int32_t need = now > had ? now : had;
+    if (lane < ns) {
+      edges += now;
+      live += l < 0 ? 0 : (l < steps ? l + 1 : steps);
+      if (now != had) plen[s0 + lane] = now;
+    }
+    const int width = __reduce_max_sync(0xffffffffu, need);   // slots the widest row of the group has to (re)write
+    const int total = __reduce_add_sync(0xffffffffu, need);   // ... and all its rows together
+    if (total <= FIN_SPARSE * FIN_SAMPLES || (steps & 3) != 0) {
+      // the staged row k is read coalesced, each sample's row gets only its few slots
+      int32_t *row = out + (s0 + lane) * steps;
+      for (int k0 = 0; k0 < width; k0 += FIN_BATCH) {   // the loads of a batch are in flight together
+        int32_t v[FIN_BATCH];
+#pragma unroll
+        for (int j = 0; j < FIN_BATCH; j++) v[j] = k0 + j < now ? tmp[(int64_t)(k0 + j) * S + s0 + lane] : invalid;
+#pragma unroll
+        for (int j = 0; j < FIN_BATCH; j++)
+          if (k0 + j < need) row[k0 + j] = v[j];
+      }
+      continue;
+    }
+    // rows written whole, 32 steps at a time through the warp's tile, 16-byte stores
+    for (int k0 = 0; k0 < steps; k0 += 32) {
+      const int kc = steps - k0 < 32 ? steps - k0 : 32;   // a multiple of 4
+      for (int kb = 0; kb < kc; kb += FIN_BATCH) {
+        int32_t v[FIN_BATCH];
+#pragma unroll
+        for (int j = 0; j < FIN_BATCH; j++) {
+          const int k = k0 + kb + j;
+          v[j] = (lane < ns && kb + j < kc && k < now) ? tmp[(int64_t)k * S + s0 + lane] : invalid;
+        }
+#pragma unroll
+        for (int j = 0; j < FIN_BATCH; j++)
+          if (kb + j < kc) tile[kb + j][lane] = v[j];
+      }
+      __syncwarp();
+      const int qn = kc >> 2;                              // 16-byte pieces per sample in this chunk
+      for (int q = lane; q < ns * qn; q += 32) {
+        const int i = q / qn, c = q - i * qn;
+        const int4 v = make_int4(tile[4 * c][i], tile[4 * c + 1][i], tile[4 * c + 2][i], tile[4 * c + 3][i]);
+        __stcs(reinterpret_cast<int4 *>(out + (s0 + i) * steps + k0) + c, v);
+      }
+      __syncwarp();
+    }
+  }
+  // CTA-level reduction of the counters, one atomic per warp
+  for (int o = 16; o > 0; o >>= 1) {
+    edges += __shfl_xor_sync(0xffffffffu, edges, o);
+    live += __shfl_xor_sync(0xffffffffu, live, o);
+  }
+  if (lane == 0 && stats) {
+    if (edges) atomicAdd(&stats[0], edges);
+    if (live) atomicAdd(&stats[1], live);
+  }
+}
+
+// fills the result array with the invalid id once, when the sampler is made (see walk_finalize_kernel)
+__global__ void walk_fill_kernel(int32_t *__restrict__ out, int64_t n4, int64_t n, int32_t v) {
+  const int4 q = make_int4(v, v, v, v);
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x)
+    reinterpret_cast<int4 *>(out)[i] = q;
+  for (int64_t i = 4 * n4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) out[i] = v;
 }
 
 template <int APP>
@@ -1297,6 +1397,10 @@ int nd_walk_alloc(nd_sampler *s) {
   ND_REQUIRE(steps >= 1 && steps <= 4096, ND_ERR_ARG, "walk length %d out of range [1,4096]", steps);
   ND_CUDA(cudaMalloc(&s->d_tmp, sizeof(int32_t) * (size_t)S * steps));
   ND_CUDA(cudaMalloc(&s->d_len, sizeof(int32_t) * (size_t)S));
+  // the result array starts out all-invalid with no slot in use (walk_finalize_kernel keeps it that way)
+  ND_CUDA(cudaMalloc(&s->d_plen, sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
+  ND_CUDA(cudaMemset(s->d_plen, 0, sizeof(int32_t) * (size_t)(S > 0 ? S : 1)));
+  if (S > 0) walk_fill_kernel<<<s->dev.sms * 8, 256>>>(s->d_out, S * steps / 4, S * steps, s->g->V);
   if (s->p.app == ND_APP_NODE2VEC) {
     ND_CUDA(cudaMalloc(&s->d_state, sizeof(int32_t) * (size_t)S));
     std::lock_guard<std::mutex> lock(g_derived_mutex);
@@ -1481,9 +1585,14 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     }
   }
   nd_phase_begin(s, ND_PHASE_FINALIZE);
-  const int64_t groups = (S + FIN_SAMPLES - 1) / FIN_SAMPLES;
-  const int fgrid = (int)(groups < (int64_t)s->dev.sms * 16 ? groups : (int64_t)s->dev.sms * 16);
-  walk_finalize_kernel<<<fgrid > 0 ? fgrid : 1, FIN_THREADS, 0, st>>>(s->d_tmp, s->d_len, S, steps, s->g->V, s->d_out, s->d_stats);
+  const int64_t groups = (S + FIN_SAMPLES - 1) / FIN_SAMPLES, fblocks = (groups + FIN_THREADS / 32 - 1) / (FIN_THREADS / 32);
+  const int fgrid = (int)(fblocks < (int64_t)s->dev.sms * 16 ? fblocks : (int64_t)s->dev.sms * 16);
+  const int dgrid = (int)(groups < (int64_t)s->dev.sms * 16 ? groups : (int64_t)s->dev.sms * 16);
+  // walks that end early leave most of a row invalid: the sparse kernel; full-length walks: whole rows
+  if (app == ND_APP_PPR && s->p.stop_prob >= 0.04f)
+    walk_finalize_sparse_kernel<<<fgrid > 0 ? fgrid : 1, FIN_THREADS, 0, st>>>(s->d_tmp, s->d_len, s->d_plen, S, steps, s->g->V, s->d_out, s->d_stats);
+  else
+    walk_finalize_kernel<<<dgrid > 0 ? dgrid : 1, FIN_THREADS, 0, st>>>(s->d_tmp, s->d_len, s->d_plen, S, steps, s->g->V, s->d_out, s->d_stats);
   nd_phase_end(s);
   nd_count_launches(1);
   ND_CUDA(cudaGetLastError());
