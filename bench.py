@@ -375,15 +375,17 @@ def roofline_of(nd, smp, wl, workload, mode_name, mode, ms_per_step, hbm_peak, p
     smp.set_profiling(False)
     st = smp.stats()
     nb = next_bytes(wl, st, mode)
+    tail_ms = ph.get("tail", (0.0, 0))[0]
     if wl["kind"] != COLL:
-        next_ms, next_launches = ph["next"]
+        next_ms, next_launches = ph["next"]          # the per-step next() launches ...
+        next_ms += tail_ms                            # ... and the tail launch: its pairs are in the byte count too
     else:
         next_ms, next_launches = ph["next"][0] + ph["collect"][0], ph["next"][1] + ph["collect"][1]
     achieved = nb / (next_ms * 1e-3) / 1e9 if next_ms > 0 else 0.0
     phase_sum = sum(v[0] for v in ph.values())
     # the timed steps replay a CUDA graph, the instrumented pass does not: the same launches, scaled
     # by their share of the instrumented pass, inside the replayed step
-    replay_ms = ms_per_step * next_ms / phase_sum if phase_sum > 0 and ms_per_step else None
+    replay_ms = ms_per_step * (next_ms - tail_ms) / phase_sum if phase_sum > 0 and ms_per_step else None
     pairs_per_launch = st["live_pairs"] / max(next_launches, 1) if wl["kind"] == WALK else None
     traffic, traffic_src = ncu_traffic(workload, mode_name, pairs_per_launch)
     gather = None
@@ -391,7 +393,8 @@ def roofline_of(nd, smp, wl, workload, mode_name, mode, ms_per_step, hbm_peak, p
         gather = gather_ceiling(wl, st, smp.graph, next_ms, next_launches, device)
     r = {"bound": "hbm", "kernel": next_kernel_name(nd, smp, mode), "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
          "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": traffic, "traffic_source": traffic_src,
-         "launches": next_launches, "avg_launch_us": 1e3 * next_ms / max(next_launches, 1),
+         "launches": next_launches, "avg_launch_us": 1e3 * (next_ms - tail_ms) / max(next_launches, 1),
+         "tail_launch_us": 1e3 * tail_ms if tail_ms else None,
          "avg_launch_us_in_replayed_step": 1e3 * replay_ms / max(next_launches, 1) if replay_ms else None,
          "algorithmic_bytes_per_pass": nb, "random_gather": gather}
     return r, ph, st

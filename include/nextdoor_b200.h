@@ -160,7 +160,9 @@ int nd_sampler_live_pairs(nd_sampler *s, int32_t *live, int n);
 /* per-phase device time of the last sample() when profiling is on: see nd_phase */
 typedef enum nd_phase {
   ND_PHASE_NEXT = 0, ND_PHASE_INVERT = 1, ND_PHASE_BIN = 2, ND_PHASE_FINALIZE = 3,
-  ND_PHASE_DEDUP = 4, ND_PHASE_COLLECT = 5, ND_PHASE_COUNT = 6
+  ND_PHASE_DEDUP = 4, ND_PHASE_COLLECT = 5,
+  ND_PHASE_TAIL = 6,   /* the one launch that finishes the surviving walks of a PPR job (also next() work) */
+  ND_PHASE_COUNT = 7
 } nd_phase;
 int nd_sampler_set_profiling(nd_sampler *s, int on);
 int nd_sampler_phase_ms(nd_sampler *s, float *ms, int32_t *launches, int n);

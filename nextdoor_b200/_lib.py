@@ -17,7 +17,7 @@ MAX_FANOUT = 8
 APP_UNIFORM_WALK, APP_DEEPWALK, APP_PPR, APP_NODE2VEC, APP_KHOP, APP_KHOP_DISTINCT = range(6)
 APP_FASTGCN_REF, APP_LADIES_REF, APP_FASTGCN_IS, APP_LADIES_IS = 6, 7, 8, 9
 MODE_TRANSIT_PARALLEL, MODE_TRANSIT_PARALLEL_LB, MODE_SAMPLE_PARALLEL = 0, 1, 2
-PHASES = ("next", "invert", "bin", "finalize", "dedup", "collect")
+PHASES = ("next", "invert", "bin", "finalize", "dedup", "collect", "tail")
 
 
 class AppParams(C.Structure):

@@ -1575,7 +1575,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
       cur ^= 1;
     }
     if (tp_steps < steps) {
-      nd_phase_begin(s, ND_PHASE_NEXT);
+      nd_phase_begin(s, ND_PHASE_TAIL);
       const int64_t tb = (S / 4 + 255) / 256;    // sized for the expected survivors; the loop strides over more
       const int tgrid = (int)(tb < (int64_t)s->dev.sms * 8 ? (tb > 0 ? tb : 1) : (int64_t)s->dev.sms * 8);
       walk_tail_kernel<ND_APP_PPR><<<tgrid, 256, 0, st>>>(nd_view(s->g), wp, tp_steps, s->first, in_rec, s->d_nlive + tp_steps, S,
