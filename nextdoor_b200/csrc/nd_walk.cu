@@ -427,6 +427,30 @@ constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_PER_THREAD = CNT_SUPER / SCAN_THREADS;   // 32 consecutive counters per thread
 constexpr int MAX_SMEM_BINS = 8192;                         // coarse bins kept in shared memory (V <= 2^25)
 
+// ---- opt-in: the reference's grid bin for walks (staged adjacency list shared by all samples on a hub)
+//
+// A tile of HUB_TILE consecutive pairs of the sorted map whose pairs all stand on ONE transit is a
+// hub tile; the consecutive hub tiles of a transit form its run.  The CTA that finds the first
+// tile of a run streams the transit's adjacency list through shared memory once per pass of
+// HUB_PASS tiles and serves all their draws from it (uniform walk: the index is drawn first, the
+// pair picks its neighbour when the chunk that holds the index is staged).  The pairs outside
+// whole hub tiles stay with the thread-per-pair kernel.  Measured slower than plain gathers (a
+// transit of degree d holds d * S / E walkers, so 128 bytes of list are streamed per gather of one
+// sector that is saved), hence off unless ND_WALK_STAGING=1; the weighted apps and node2vec probe
+// several random positions per try and cannot be served from a streamed chunk at all.
+constexpr int HUB_TILE = 256;
+constexpr int HUB_PASS = 8;        // tiles whose pairs a CTA serves per sweep of the list
+constexpr int HUB_CHUNK = 8192;    // neighbour ids staged at once (32 KB)
+
+// transit of hub tile `tau` of the 8-byte-record map, or -1 if the tile is not one
+__device__ __forceinline__ int32_t hub_tile(const void *in_rec, int n, int tau) {
+  const int base = tau * HUB_TILE;
+  if (tau < 0 || base + HUB_TILE > n) return -1;
+  const int2 *rec = reinterpret_cast<const int2 *>(in_rec);
+  const int32_t a = rec[base].x, b = rec[base + HUB_TILE - 1].x;
+  return a == b ? a : -1;
+}
+
 // The kernel.  CTAs take tiles of 256 * PPT pairs of the sorted map (PPT = pairs a thread works on
 // at once, phase by phase; 1 measured best for every app, larger values are kept as a tuning macro).
 //  * uniform walk, DeepWalk, PPR: next() in place, up to 16 CTAs per SM, a tile each.
@@ -533,7 +557,8 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
                        const void *__restrict__ in_rec, const int32_t *__restrict__ d_n,
                        int32_t *__restrict__ out_key, int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
                        int4 *__restrict__ out_ext, uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum, int bins, int32_t *__restrict__ tmp_step,
-                       int32_t *__restrict__ len, int *__restrict__ status, unsigned long long *__restrict__ stats) {
+                       int32_t *__restrict__ len, int *__restrict__ status, unsigned long long *__restrict__ stats,
+                       int skip_hub_tiles) {
   constexpr int PPT = count_ppt<APP>();
   constexpr int QCAP = 32 * PPT + 32;
   constexpr bool N2V = APP == ND_APP_NODE2VEC;
@@ -587,6 +612,9 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
   };
 
   for (int base = blockIdx.x * TILE; base < n; base += gridDim.x * TILE) {
+    // opt-in staging of hub lists (uniform walk): a tile whose 256 pairs all stand on one transit
+    // belongs to walk_next_hub_kernel
+    if (APP == ND_APP_UNIFORM_WALK && PPT == 1 && skip_hub_tiles && hub_tile(in_rec, n, base / HUB_TILE) >= 0) continue;
     int idx[PPT];
     int32_t t[PPT], s[PPT], rs[PPT], deg[PPT], nbr[PPT];
     bool live[PPT], settled[PPT], cont[PPT];
@@ -752,6 +780,55 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
     }
   }
   if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
+}
+
+template <bool COUNT>
+__global__ void __launch_bounds__(HUB_TILE)
+walk_next_hub_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sample, const void *__restrict__ in_rec,
+                     const int32_t *__restrict__ d_n, int32_t *__restrict__ out_key, int32_t *__restrict__ out_val,
+                     int32_t *__restrict__ out_rank, uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum,
+                     int32_t *__restrict__ tmp_step, int32_t *__restrict__ len) {
+  __shared__ int32_t sh_list[HUB_CHUNK];
+  const ndmem::Keep keep;
+  const int n = *d_n;
+  const int tiles = n / HUB_TILE;
+  const int2 *rec = reinterpret_cast<const int2 *>(in_rec);
+  for (int tau = blockIdx.x; tau < tiles; tau += gridDim.x) {
+    const int32_t t = hub_tile(in_rec, n, tau);
+    if (t < 0 || hub_tile(in_rec, n, tau - 1) == t) continue;       // not the first tile of a run
+    int nt = 1;
+    while (hub_tile(in_rec, n, tau + nt) == t) nt++;
+    const bool ok = t < g.V;
+    const int32_t rs = ok ? __ldg(g.row_ptr + t) : 0;
+    const int32_t deg = ok ? __ldg(g.row_ptr + t + 1) - rs : 0;
+    for (int j0 = 0; j0 < nt; j0 += HUB_PASS) {
+      const int m = nt - j0 < HUB_PASS ? nt - j0 : HUB_PASS;
+      int32_t smp[HUB_PASS], x[HUB_PASS], nbr[HUB_PASS];
+#pragma unroll
+      for (int j = 0; j < HUB_PASS; j++) {
+        smp[j] = 0; x[j] = -1; nbr[j] = -1;
+        if (j < m) {
+          smp[j] = rec[(tau + j0 + j) * HUB_TILE + threadIdx.x].y;
+          Rng rng(wp.seed, (uint32_t)(first_sample + smp[j]), (uint32_t)step, 0u);
+          if (deg > 0) x[j] = rng.rand_int(deg);
+        }
+      }
+      for (int c0 = 0; c0 < deg; c0 += HUB_CHUNK) {
+        const int cn = deg - c0 < HUB_CHUNK ? deg - c0 : HUB_CHUNK;
+        for (int i = threadIdx.x; i < cn; i += HUB_TILE) sh_list[i] = __ldg(g.col + rs + c0 + i);
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < HUB_PASS; j++)
+          if (x[j] >= c0 && x[j] < c0 + cn) nbr[j] = sh_list[x[j] - c0];
+        __syncthreads();
+      }
+#pragma unroll
+      for (int j = 0; j < HUB_PASS; j++)
+        if (j < m)
+          count_emit<COUNT>(keep, (int)((tau + j0 + j) * HUB_TILE + threadIdx.x), smp[j], nbr[j], g.V, step, false, nullptr, out_key,
+                            out_val, out_rank, cnt, bsum, tmp_step, len, nullptr, 0, 0, 0);
+    }
+  }
 }
 
 // CTA b owns the counters of coarse bin b: its base is the sum of the bins before it; exclusive
@@ -1245,14 +1322,26 @@ int launch_count(nd_sampler *s, const WalkParams &wp, int step, bool last, int b
   const int grid = (int)(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
   NdGraphView gv = nd_view(s->g);
   int4 *uext = APP == ND_APP_NODE2VEC && !last ? s->d_uext : nullptr;
+  const char *staging_env = getenv("ND_WALK_STAGING");   // opt-in: hub tiles of the uniform walk through walk_next_hub_kernel
+  const int staging = APP == ND_APP_UNIFORM_WALK && count_ppt<APP>() == 1 && staging_env && staging_env[0] == '1' ? 1 : 0;
   if (last)
     walk_next_count_kernel<APP, false><<<grid, COUNT_THREADS, smem, s->stream>>>(
         gv, wp, step, s->first, in_rec, d_n, ukey, uval, s->d_rank, uext, s->d_cnt, s->d_bsum, bins,
-        tmp_step, s->d_len, s->d_status, s->d_stats);
+        tmp_step, s->d_len, s->d_status, s->d_stats, staging);
   else
     walk_next_count_kernel<APP, true><<<grid, COUNT_THREADS, smem, s->stream>>>(
         gv, wp, step, s->first, in_rec, d_n, ukey, uval, s->d_rank, uext, s->d_cnt, s->d_bsum, bins,
-        tmp_step, s->d_len, s->d_status, s->d_stats);
+        tmp_step, s->d_len, s->d_status, s->d_stats, staging);
+  if (staging) {  // the hub tiles the kernel above left out
+    const int hgrid = (int)(tiles < (int64_t)s->dev.sms * 8 ? (tiles > 0 ? tiles : 1) : (int64_t)s->dev.sms * 8);
+    if (last)
+      walk_next_hub_kernel<false><<<hgrid, HUB_TILE, 0, s->stream>>>(gv, wp, step, s->first, in_rec, d_n, ukey, uval, s->d_rank,
+                                                                     s->d_cnt, s->d_bsum, tmp_step, s->d_len);
+    else
+      walk_next_hub_kernel<true><<<hgrid, HUB_TILE, 0, s->stream>>>(gv, wp, step, s->first, in_rec, d_n, ukey, uval, s->d_rank,
+                                                                    s->d_cnt, s->d_bsum, tmp_step, s->d_len);
+    nd_count_launches(1);
+  }
   return ND_OK;
 }
 

@@ -53,6 +53,29 @@ def test_walks_match_oracle(nd, ndo, small_graph, app, mode):
         assert np.array_equal(s.final_samples(), exp["out"])
 
 
+def test_uniform_walk_hub_staging(nd, ndo, monkeypatch):
+    """ND_WALK_STAGING=1: whole tiles of 256 pairs that stand on one transit are served from the
+    transit's adjacency list staged in shared memory (walk_next_hub_kernel), the rest by the
+    thread-per-pair kernel.  A star with a ring: a third of all walkers meet on the hub, whose list
+    (2999 ids here; 20 000 in the second graph, more than one staged chunk) is streamed in chunks."""
+    monkeypatch.setenv("ND_WALK_STAGING", "1")
+    for V, S, steps in ((3000, 30_000, 12), (20_001, 60_000, 6)):
+        spokes = np.arange(1, V, dtype=np.int32)
+        ring_a, ring_b = spokes, np.roll(spokes, -1)
+        src = np.concatenate([np.zeros(V - 1, np.int32), spokes, ring_a, ring_b])
+        dst = np.concatenate([spokes, np.zeros(V - 1, np.int32), ring_b, ring_a])
+        hg = ndo.csr_from_records(src, dst, np.ones(src.shape[0], np.float32), V=V)
+        g = _graph(nd, hg)
+        pr = nd.app_params(0, steps=steps, seed=17)
+        s = nd.Sampler(g, pr, num_samples=S)
+        s.sample(1)
+        exp = ndo.sample(hg, ndo.make_params(0, steps=steps, seed=17), S)
+        assert np.array_equal(s.final_samples(), exp["out"])
+        assert s.stats()["sampled_edges"] == exp["counters"]["sampled_edges"]
+        live = s.live_pairs()
+        assert live[1] == S and live[2] == S          # nobody dies on this graph: the hub holds thousands of pairs
+
+
 @pytest.mark.parametrize("no_tail", ["0", "1"])
 def test_ppr_tail_launch_and_step_loop_agree(nd, ndo, small_graph, monkeypatch, no_tail):
     """PPR in the load-balanced mode finishes the few walks that are still alive with one tail
