@@ -462,9 +462,9 @@ __device__ __forceinline__ int32_t hub_tile(const void *in_rec, int n, int tau) 
 //    continuing behind the rejected tries in the pair's draw sequence, so nothing is gathered
 //    twice.  The draws of a pair depend only on (sample, step), so the queue changes no sample.
 //    The CTAs are persistent here (as many as are resident), so that the queues fill over tiles.
-//  * the coarse histogram is flushed once per CTA.
+//  * the coarse histogram (pairs per 4096 vertices, for the scan) is kept in shared memory and flushed once per CTA.
 // What bounds it: a pair costs a few random 32-byte sector reads that miss the L2 (one neighbour id;
-// node2vec about 1.9 candidates and 0.9 set buckets), and the memory system serves those at a
+// node2vec about 2.6 candidates and 1.3 set buckets in a first round of four tries), and the memory system serves those at a
 // rate far below its streaming bandwidth; occupancy, pairs per thread, cache hints and the L2
 // fetch granularity were all measured and do not move the kernel's time by more than a few per cent.
 constexpr int COUNT_THREADS = 256;
