@@ -156,9 +156,6 @@ int nd_sampler_create(const nd_graph *g, const nd_app_params *p, int64_t num_sam
   ND_REQUIRE(first_sample + num_samples <= 0xffffffffll, ND_ERR_RANGE, "global sample index exceeds 32 bits");
   ND_REQUIRE(num_samples * (int64_t)nd_final_sample_size(p) < ((int64_t)1 << 40), ND_ERR_RANGE, "output too large");
   ND_CUDA(cudaSetDevice(g->device));
-  if (const char *fg = getenv("ND_L2_FETCH")) {  // experiment: L2 fetch granularity of this context (32, 64 or 128 bytes)
-    if (cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, (size_t)atoi(fg)) != cudaSuccess) cudaGetLastError();
-  }
   nd_sampler *s = new nd_sampler();
   s->g = g;
   s->p = *p;
