@@ -383,6 +383,10 @@ def roofline_of(nd, smp, wl, workload, mode_name, mode, ms_per_step, hbm_peak, p
         next_ms, next_launches = ph["next"][0] + ph["collect"][0], ph["next"][1] + ph["collect"][1]
     achieved = nb / (next_ms * 1e-3) / 1e9 if next_ms > 0 else 0.0
     phase_sum = sum(v[0] for v in ph.values())
+    # in the replayed step the tail launch runs on a second stream beside the result update (the
+    # instrumented pass runs them one after the other): the shorter of the two is hidden
+    if tail_ms and "finalize" in ph and os.environ.get("ND_WALK_TAIL_INLINE", "0") in ("", "0"):
+        phase_sum -= min(tail_ms, ph["finalize"][0])
     # the timed steps replay a CUDA graph, the instrumented pass does not: the same launches, scaled
     # by their share of the instrumented pass, inside the replayed step
     replay_ms = ms_per_step * (next_ms - tail_ms) / phase_sum if phase_sum > 0 and ms_per_step else None

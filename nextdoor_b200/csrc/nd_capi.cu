@@ -86,6 +86,9 @@ void free_sampler(nd_sampler *s) {
   for (int i = 0; i < 3; i++) if (s->graph_exec[i]) cudaGraphExecDestroy(s->graph_exec[i]);
   if (s->copy_event) cudaEventDestroy(s->copy_event);
   if (s->copy_done) cudaEventDestroy(s->copy_done);
+  if (s->side_fork) cudaEventDestroy(s->side_fork);
+  if (s->side_join) cudaEventDestroy(s->side_join);
+  if (s->side) cudaStreamDestroy(s->side);
   nd_radix_scratch_free(&s->radix);
   for (cudaEvent_t e : s->timer.ev) cudaEventDestroy(e);
   delete s;

@@ -180,6 +180,9 @@ struct nd_sampler {
   cudaGraphExec_t graph_exec[3] = {nullptr, nullptr, nullptr};
   int graph_launches[3] = {0, 0, 0};
   bool graph_off = false;
+  // PPR, load-balanced mode: the tail launch runs on this stream beside the result update of the walks that ended
+  cudaStream_t side = nullptr;
+  cudaEvent_t side_fork = nullptr, side_join = nullptr;
   cudaEvent_t copy_event = nullptr;  // orders a result copy on another stream after the sampling
   cudaEvent_t copy_done = nullptr;   // ... and the next sampling (which overwrites the result) after that copy
   bool copy_pending = false;

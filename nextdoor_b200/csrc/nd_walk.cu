@@ -311,9 +311,10 @@ __global__ void colw_build_kernel(const int32_t *__restrict__ col, const float *
 
 __global__ void walk_reset_kernel(const int32_t *__restrict__ initial, int32_t V, int64_t S, int steps,
                                   int32_t *__restrict__ len, int32_t *__restrict__ state,
-                                  unsigned long long *__restrict__ stats) {
+                                  unsigned long long *__restrict__ stats, int32_t *__restrict__ tail_ctr) {
   const int64_t s = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (s < 8 && stats) stats[s] = 0ull;
+  if (s == 0 && tail_ctr) *tail_ctr = 0;
   if (s >= S) return;
   const int32_t t = initial[s];
   len[s] = (t >= 0 && t < V) ? steps : -1;
@@ -954,45 +955,126 @@ pack_map_kernel(const int32_t *__restrict__ d_n, const int32_t *__restrict__ key
   }
 }
 
-// The tail of a job whose walks end early (PPR): once only a small fraction of the walks is still
-// alive, a step of the transit-parallel loop is three launches over a few thousand pairs, i.e.
-// pure launch latency.  From there on one launch finishes the job: a thread takes a pair of the
-// sorted map and walks its sample through all remaining steps.  The draws are keyed by (sample,
-// step), so the samples are the ones the step-by-step loop would have produced.
-template <int APP>
-__global__ void __launch_bounds__(256)
+// The tail of a job whose walks end early (PPR): once few walks are still alive, a step of the
+// transit-parallel loop is three launches whose fixed cost outweighs the per-pair work.  From
+// there on one launch finishes the job, a lane per walk: a lane takes a pair of the sorted map
+// (next free index of a device counter, so that the lanes end together) and walks its sample to
+// the end; a warp makes one round of tries per trip as walk_sp_rounds_kernel does, and a lane
+// whose walk ended takes the next pair.  The draws are keyed by (sample, step), so the samples are
+// the ones the step-by-step loop would have produced.
+// DIRECT: the launch lasts at least as long as the longest surviving walk's chain of dependent
+// loads and leaves most of the memory system idle, so it runs on a second stream beside the result
+// update of the walks that ended in the step loop (walk_finalize_sparse_kernel with tail_from =
+// first_step).  The two kernels split the result rows between them: a survivor's slots from
+// first_step on, its entry of plen and its share of the counters belong to this kernel, everything
+// else to the other.
+template <int APP, bool DIRECT>
+__global__ void __launch_bounds__(256, walk_min_ctas_sp<APP>())
 walk_tail_kernel(NdGraphView g, WalkParams wp, int first_step, int64_t first_sample, const void *__restrict__ in_rec,
-                 const int32_t *__restrict__ d_n, int64_t S, int32_t *__restrict__ tmp, int32_t *__restrict__ len,
-                 int *__restrict__ status, unsigned long long *__restrict__ stats) {
-  constexpr bool N2V = APP == ND_APP_NODE2VEC;
+                 const int32_t *__restrict__ d_n, int32_t *__restrict__ next_pair, int64_t S, int32_t *__restrict__ tmp,
+                 int32_t *__restrict__ len, int32_t *__restrict__ plen, int32_t *__restrict__ out, int *__restrict__ status,
+                 unsigned long long *__restrict__ stats) {
+  static_assert(APP == ND_APP_DEEPWALK || APP == ND_APP_PPR, "weighted walks only");
   Events ev;
   const ndmem::Keep keep;
   const int n = *d_n;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const MapRec<N2V> r = map_rec_load<N2V>(keep, in_rec, i);
-    int32_t cur = r.t, st = r.pv;
-    int step = first_step;
-    for (; step < wp.steps; step++) {
-      int32_t nbr = -1;
-      if (cur >= 0 && cur < g.V) {
-        // the walk's chain of dependent loads is what this launch lasts: row offsets and maximum
-        // weight are fetched together, so a step is two memory latencies (vertex, then edge records)
-        const int32_t rs = __ldg(g.row_ptr + cur);
-        const int32_t deg = __ldg(g.row_ptr + cur + 1) - rs;
-        const bool weighted = APP == ND_APP_DEEPWALK || APP == ND_APP_PPR;
-        const float mw = weighted ? __ldg(g.max_w + cur) : 0.f;
-        if (deg > 0) {
-          Rng rng(wp.seed, (uint32_t)(first_sample + r.s), (uint32_t)step, 0u);
-          nbr = app_next<APP, false, N2V_BATCH_SP>(g, wp, step, cur, rs, deg, st, rng, status, ev, weighted, mw);
+  const int lane = threadIdx.x & 31;
+  bool have = false, fresh = true, done = false;
+  int32_t s = 0, cur = 0, rs = 0, deg = 0, had = 0;
+  int step = 0, rounds = 0;
+  float max_w = 0.f;
+  int32_t *row = nullptr;
+  unsigned int edges = 0, live = 0;
+  Rng rng(wp.seed, 0u, 0u, 0u);
+  while (true) {
+    // the lanes without a walk draw consecutive pair indices with one atomic
+    const unsigned want = __ballot_sync(0xffffffffu, !done && !have);
+    if (want) {
+      const int leader = __ffs(want) - 1;
+      int base = 0;
+      if (lane == leader) base = atomicAdd(next_pair, __popc(want));
+      base = __shfl_sync(0xffffffffu, base, leader);
+      if (!done && !have) {
+        const int i = base + __popc(want & ((1u << lane) - 1u));
+        if (i >= n) {
+          done = true;
+        } else {
+          const MapRec<false> r = map_rec_load<false>(keep, in_rec, i);
+          s = r.s;
+          cur = r.t;
+          step = first_step;
+          have = true;
+          fresh = true;
+          if (cur >= 0 && cur < g.V) {
+            rs = __ldg(g.row_ptr + cur);
+            deg = __ldg(g.row_ptr + cur + 1) - rs;
+            max_w = __ldg(g.max_w + cur);
+          } else {
+            deg = 0;
+          }
+          if (DIRECT) {
+            row = out + (int64_t)s * wp.steps;
+            had = plen[s];
+          }
         }
       }
-      if (nbr < 0) break;
-      tmp[(int64_t)step * S + r.s] = nbr;
-      cur = nbr;
     }
-    if (step < wp.steps) len[r.s] = step;
+    if (!__any_sync(0xffffffffu, have)) break;   // no lane holds a walk, so every lane found the map exhausted
+    if (have) {
+      int32_t nbr = ROUND_AGAIN;
+      if (deg == 0) {
+        nbr = -1;
+      } else if (fresh) {  // first trip of a step: the draws of the step start, the cases without a rejection loop
+        rng = Rng(wp.seed, (uint32_t)(first_sample + s), (uint32_t)step, 0u);
+        rounds = 0;
+        fresh = false;
+        if (APP == ND_APP_PPR) {
+          const float pr = rng.uniform();
+          if (pr < wp.stop_prob) nbr = -1;
+        }
+        if (nbr == ROUND_AGAIN && deg == 1) nbr = __ldg(g.col + rs);
+      }
+      if (nbr == ROUND_AGAIN) {
+        nbr = weighted_round<false, 2>(wp, rs, deg, max_w, rng, ev);
+        if (nbr == ROUND_AGAIN && ++rounds > RETRY_CAP) {
+          atomicOr(status, ND_DEV_RETRY_LIMIT);
+          nbr = __ldg(g.col + rs);
+        }
+      }
+      if (nbr >= 0) {
+        if (DIRECT) row[step] = nbr;
+        else tmp[(int64_t)step * S + s] = nbr;
+        cur = nbr;
+        if (++step < wp.steps) {
+          rs = __ldg(g.row_ptr + cur);
+          deg = __ldg(g.row_ptr + cur + 1) - rs;
+          max_w = __ldg(g.max_w + cur);
+          fresh = true;
+        }
+      }
+      if (nbr == -1 || step == wp.steps) {  // the walk ends here, after `step` vertices
+        if (step < wp.steps) len[s] = step;
+        if (DIRECT) {
+          for (int k = step; k < had; k++) row[k] = g.V;   // slots the previous pass filled beyond this walk's end
+          if (had != step) plen[s] = step;
+          edges += step - first_step;
+          live += (step < wp.steps ? step + 1 : wp.steps) - first_step;
+        }
+        have = false;
+      }  // ROUND_AGAIN: the lane stays on its step
+    }
   }
-  if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
+  if (DIRECT) {
+    for (int o = 16; o > 0; o >>= 1) {
+      edges += __shfl_xor_sync(0xffffffffu, edges, o);
+      live += __shfl_xor_sync(0xffffffffu, live, o);
+    }
+    if (lane == 0) {
+      if (edges) atomicAdd(&stats[0], (unsigned long long)edges);
+      if (live) atomicAdd(&stats[1], (unsigned long long)live);
+    }
+  }
+  ev.flush(stats);
 }
 
 // ---------------------------------------------------------------- sample-parallel: a thread owns a walk
@@ -1199,11 +1281,12 @@ walk_finalize_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict_
 // the shared-memory transpose and are written whole, with 16-byte stores.
 constexpr int FIN_SPARSE = 8;
 constexpr int FIN_BATCH = 8;    // staged rows a lane reads at once
+constexpr float FIN_SPARSE_STOP = 0.04f;  // PPR stop probability from which the result update takes this kernel
 
 __global__ void __launch_bounds__(FIN_THREADS)
 walk_finalize_sparse_kernel(const int32_t *__restrict__ tmp, const int32_t *__restrict__ len, int32_t *__restrict__ plen, int64_t S,
                      int steps, int32_t invalid, int32_t *__restrict__ out,
-                     unsigned long long *__restrict__ stats) {
+                     unsigned long long *__restrict__ stats, int tail_from) {
   // a warp owns a group of 32 samples (lane = sample) from start to end: no block barrier anywhere
   __shared__ int32_t tiles[FIN_THREADS / 32][32][FIN_SAMPLES + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1215,17 +1298,23 @@ walk_finalize_sparse_kernel(const int32_t *__restrict__ tmp, const int32_t *__re
     const int64_t s0 = grp * FIN_SAMPLES;
     const int ns = (int)(S - s0 < FIN_SAMPLES ? S - s0 : FIN_SAMPLES);
     const int32_t l = lane < ns ? len[s0 + lane] : -1;
-    const int32_t had = lane < ns ? plen[s0 + lane] : 0;
-    const int32_t now = l > 0 ? l : 0;
+    // A walk that was alive after step tail_from - 1 is being finished by the tail kernel while this
+    // kernel runs (tail_from > steps: no such kernel).  Its length entry reads as `steps` or as its
+    // final length, at least tail_from either way; this kernel writes its slots below tail_from and
+    // leaves the rest of the row, the row's plen entry and the rest of its counts to the tail kernel.
+    const bool surv = l >= tail_from;
+    const int32_t had = lane < ns && !surv ? plen[s0 + lane] : 0;
+    const int32_t now = surv ? tail_from : (l > 0 ? l : 0);
     const int32_t need = now > had ? now : had;
     if (lane < ns) {
       edges += now;
-      live += l < 0 ? 0 : (l < steps ? l + 1 : steps);
-      if (now != had) plen[s0 + lane] = now;
+      live += surv ? tail_from : (l < 0 ? 0 : (l < steps ? l + 1 : steps));
+      if (!surv && now != had) plen[s0 + lane] = now;
     }
     const int width = __reduce_max_sync(0xffffffffu, need);   // slots the widest row of the group has to (re)write
     const int total = __reduce_add_sync(0xffffffffu, need);   // ... and all its rows together
-    if (total <= FIN_SPARSE * FIN_SAMPLES || (steps & 3) != 0) {
+    // (a group with a survivor never takes the whole-row path: that one would write the tail kernel's slots)
+    if (total <= FIN_SPARSE * FIN_SAMPLES || (steps & 3) != 0 || __any_sync(0xffffffffu, surv)) {
       // the staged row k is read coalesced, each sample's row gets only its few slots
       int32_t *row = out + (s0 + lane) * steps;
       for (int k0 = 0; k0 < width; k0 += FIN_BATCH) {   // the loads of a batch are in flight together
@@ -1514,7 +1603,7 @@ int nd_walk_alloc(nd_sampler *s) {
   }
   ND_CUDA(cudaMalloc(&s->d_init_key, sizeof(int32_t) * (size_t)S));
   ND_CUDA(cudaMalloc(&s->d_init_val, sizeof(int32_t) * (size_t)S));
-  ND_CUDA(cudaMalloc(&s->d_nlive, sizeof(int32_t) * (size_t)(steps + 2)));
+  ND_CUDA(cudaMalloc(&s->d_nlive, sizeof(int32_t) * (size_t)(steps + 3)));  // live pairs per step, a spare slot, the tail launch's work counter
   const int key_bits = nd_bit_length((uint32_t)(s->g->V > 1 ? s->g->V - 1 : 1));
   ND_TRY(nd_radix_scratch_alloc(&s->radix, key_bits, S));
   // counting inversion (load-balanced mode)
@@ -1531,6 +1620,11 @@ int nd_walk_alloc(nd_sampler *s) {
   for (int i = 0; i < 2; i++) ND_CUDA(cudaMalloc(&s->d_srec[i], rec * S1));
   ND_CUDA(cudaMalloc(&s->d_init_rec, rec * S1));
   if (s->p.app == ND_APP_NODE2VEC) ND_CUDA(cudaMalloc(&s->d_uext, sizeof(int4) * S1));
+  if (s->p.app == ND_APP_PPR && s->p.stop_prob > 0.f) {  // the tail launch runs beside the result update
+    ND_CUDA(cudaStreamCreateWithFlags(&s->side, cudaStreamNonBlocking));
+    ND_CUDA(cudaEventCreateWithFlags(&s->side_fork, cudaEventDisableTiming));
+    ND_CUDA(cudaEventCreateWithFlags(&s->side_join, cudaEventDisableTiming));
+  }
   return ND_OK;
 }
 
@@ -1570,8 +1664,11 @@ static int walk_enqueue(nd_sampler *s, int mode) {
   const int app = s->p.app;
   cudaStream_t st = s->stream;
   WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps, s->g->adjset, s->g->colw};
+  bool tail_direct = false, join = false;   // PPR tail launch: writes the result rows itself / runs on the side stream
+  int tail_from = 0x7fffffff;               // first step of that launch
   const int rblocks = (int)((S + 255) / 256);
-  walk_reset_kernel<<<rblocks > 1 ? rblocks : 1, 256, 0, st>>>(s->d_initial, s->g->V, S, steps, s->d_len, s->d_state, s->d_stats);
+  walk_reset_kernel<<<rblocks > 1 ? rblocks : 1, 256, 0, st>>>(s->d_initial, s->g->V, S, steps, s->d_len, s->d_state, s->d_stats,
+                                                                s->d_nlive + steps + 2);
   nd_count_launches(1);
   if (mode == ND_MODE_SAMPLE_PARALLEL) {
     nd_phase_begin(s, ND_PHASE_NEXT);
@@ -1629,14 +1726,17 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     const void *in_rec = s->d_init_rec;
     const int64_t sblocks = (S + 256 * SCATTER_PPT - 1) / (256 * SCATTER_PPT);
     const int sgrid = (int)(sblocks < (int64_t)s->dev.sms * 16 ? (sblocks > 0 ? sblocks : 1) : (int64_t)s->dev.sms * 16);
-    // PPR: the step-by-step loop runs while enough walks are expected to be alive for a step to be
-    // more than launch latency (S * (1 - stop probability)^k above S/32 and above 512 K pairs), one
-    // tail launch finishes the rest
+    // PPR: a step of the loop costs about 40 us of launches and of the scan over the per-vertex
+    // counters whatever the number of live pairs, which is what a million pairs cost on top of it.
+    // The loop runs while more than that are expected to be alive (S * (1 - stop probability)^k),
+    // one tail launch finishes the rest (ND_WALK_TAIL_PAIRS moves the hand-over, for tests and A/B runs).
     int tp_steps = steps;
     if (app == ND_APP_PPR && s->p.stop_prob > 0.f && !getenv("ND_WALK_NO_TAIL")) {
+      const char *e = getenv("ND_WALK_TAIL_PAIRS");
+      const double floor_pairs = e ? atof(e) : 1048576.0;
       double alive = 1.0;
       int k = 0;
-      while (k < steps && alive > 1.0 / 32 && alive * (double)S > 524288.0) { alive *= 1.0 - (double)s->p.stop_prob; k++; }
+      while (k < steps && alive * (double)S > floor_pairs) { alive *= 1.0 - (double)s->p.stop_prob; k++; }
       tp_steps = k < 1 ? 1 : k;
     }
     int cur = 0;  // sorted map the scatter of this step writes
@@ -1664,13 +1764,33 @@ static int walk_enqueue(nd_sampler *s, int mode) {
       cur ^= 1;
     }
     if (tp_steps < steps) {
+      // with the sparse result update the tail writes its walks' slots itself and runs beside that
+      // update on the side stream (one after the other on the main stream when the phases are timed)
+      tail_direct = s->p.stop_prob >= FIN_SPARSE_STOP && s->side != nullptr;
+      const char *ti = getenv("ND_WALK_TAIL_INLINE");   // A/B switch: anything but empty or 0 keeps the tail on the main stream
+      const bool forked = tail_direct && !s->timer.on && !(ti && ti[0] && ti[0] != '0');
+      cudaStream_t ts = st;
+      if (forked) {
+        ND_CUDA(cudaEventRecord(s->side_fork, st));
+        ND_CUDA(cudaStreamWaitEvent(s->side, s->side_fork, 0));
+        ts = s->side;
+      }
       nd_phase_begin(s, ND_PHASE_TAIL);
-      const int64_t tb = (S / 4 + 255) / 256;    // sized for the expected survivors; the loop strides over more
-      const int tgrid = (int)(tb < (int64_t)s->dev.sms * 8 ? (tb > 0 ? tb : 1) : (int64_t)s->dev.sms * 8);
-      walk_tail_kernel<ND_APP_PPR><<<tgrid, 256, 0, st>>>(nd_view(s->g), wp, tp_steps, s->first, in_rec, s->d_nlive + tp_steps, S,
-                                                         s->d_tmp, s->d_len, s->d_status, s->d_stats);
+      const int tgrid = s->dev.sms * walk_min_ctas_sp<ND_APP_PPR>();   // resident CTAs; the lanes draw their pairs from a counter
+      int32_t *next_pair = s->d_nlive + steps + 2;
+      if (tail_direct)
+        walk_tail_kernel<ND_APP_PPR, true><<<tgrid, 256, 0, ts>>>(nd_view(s->g), wp, tp_steps, s->first, in_rec, s->d_nlive + tp_steps, next_pair,
+                                                                 S, s->d_tmp, s->d_len, s->d_plen, s->d_out, s->d_status, s->d_stats);
+      else
+        walk_tail_kernel<ND_APP_PPR, false><<<tgrid, 256, 0, ts>>>(nd_view(s->g), wp, tp_steps, s->first, in_rec, s->d_nlive + tp_steps, next_pair,
+                                                                  S, s->d_tmp, s->d_len, s->d_plen, s->d_out, s->d_status, s->d_stats);
       nd_phase_end(s);
       nd_count_launches(1);
+      if (forked) {
+        ND_CUDA(cudaEventRecord(s->side_join, s->side));
+        join = true;
+      }
+      tail_from = tail_direct ? tp_steps : tail_from;
     }
   }
   nd_phase_begin(s, ND_PHASE_FINALIZE);
@@ -1678,12 +1798,13 @@ static int walk_enqueue(nd_sampler *s, int mode) {
   const int fgrid = (int)(fblocks < (int64_t)s->dev.sms * 16 ? fblocks : (int64_t)s->dev.sms * 16);
   const int dgrid = (int)(groups < (int64_t)s->dev.sms * 16 ? groups : (int64_t)s->dev.sms * 16);
   // walks that end early leave most of a row invalid: the sparse kernel; full-length walks: whole rows
-  if (app == ND_APP_PPR && s->p.stop_prob >= 0.04f)
-    walk_finalize_sparse_kernel<<<fgrid > 0 ? fgrid : 1, FIN_THREADS, 0, st>>>(s->d_tmp, s->d_len, s->d_plen, S, steps, s->g->V, s->d_out, s->d_stats);
+  if (app == ND_APP_PPR && s->p.stop_prob >= FIN_SPARSE_STOP)
+    walk_finalize_sparse_kernel<<<fgrid > 0 ? fgrid : 1, FIN_THREADS, 0, st>>>(s->d_tmp, s->d_len, s->d_plen, S, steps, s->g->V, s->d_out, s->d_stats, tail_from);
   else
     walk_finalize_kernel<<<dgrid > 0 ? dgrid : 1, FIN_THREADS, 0, st>>>(s->d_tmp, s->d_len, s->d_plen, S, steps, s->g->V, s->d_out, s->d_stats);
   nd_phase_end(s);
   nd_count_launches(1);
+  if (join) ND_CUDA(cudaStreamWaitEvent(st, s->side_join, 0));
   ND_CUDA(cudaGetLastError());
   return ND_OK;
 }

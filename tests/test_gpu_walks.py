@@ -98,6 +98,47 @@ def test_ppr_tail_launch_and_step_loop_agree(nd, ndo, small_graph, monkeypatch, 
     assert st["weight_tries"] == exp["counters"]["weight_tries"]
 
 
+@pytest.mark.parametrize("inline", ["0", "1"])
+def test_ppr_tail_beside_the_result_update_over_changing_passes(nd, ndo, small_graph, monkeypatch, inline):
+    """The tail launch runs on a second stream beside the result update and writes its walks' rows
+    itself (ND_WALK_TAIL_INLINE=1: on the same stream, one after the other).  The result array
+    keeps its contents between passes, so passes with different start vertices on one sampler --
+    rows that grow and rows that shrink, walks that change sides between the two kernels -- must
+    each give the oracle's array; replayed as a CUDA graph on a caller's stream, with the
+    hand-over to the tail at several steps, and with the phase timers on."""
+    import torch
+    monkeypatch.setenv("ND_WALK_TAIL_INLINE", inline)
+    g = _graph(nd, small_graph)
+    S = 30_000
+    rng = np.random.default_rng(4)
+    for pairs_floor in ("2000", "12000", "100000"):        # hand-over late, in the middle, after step 0
+        monkeypatch.setenv("ND_WALK_TAIL_PAIRS", pairs_floor)
+        pr = nd.app_params(2, steps=48, seed=33, stop_prob=0.15)
+        opr = ndo.make_params(2, steps=48, seed=33, stop_prob=0.15)
+        s = nd.Sampler(g, pr, num_samples=S, first_sample=7)
+        st = torch.cuda.Stream()
+        s.set_stream(st.cuda_stream)
+        for p in range(4):
+            init = rng.integers(0, small_graph.V, S).astype(np.int32)
+            if p == 2:
+                init[::3] = -1                             # a third of the walks never start
+            s.set_initial(init)
+            if p == 3:
+                s.set_profiling(True)
+            s.sample(1)
+            clean = np.where(init < 0, small_graph.V, init).astype(np.int32)
+            exp = ndo.sample(small_graph, opr, S, first=7, initial=clean)
+            assert np.array_equal(s.final_samples(), exp["out"]), (pairs_floor, p)
+            c = s.stats()
+            assert c["sampled_edges"] == exp["counters"]["sampled_edges"], (pairs_floor, p)
+            assert c["live_pairs"] == exp["counters"]["live_pairs"], (pairs_floor, p)
+        assert s.phase_ms()["tail"][1] == 1                # one tail launch in the timed pass
+        s.set_profiling(False)
+        s.sample(2)                                        # the sample-parallel mode on the same result array
+        assert np.array_equal(s.final_samples(), exp["out"])
+        s.free()
+
+
 @pytest.mark.parametrize("mode", MODES)
 def test_node2vec_corrected_comparison(nd, ndo, small_graph, mode):
     g = _graph(nd, small_graph)
