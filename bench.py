@@ -466,6 +466,9 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="c5", choices=list(WORKLOADS))
     ap.add_argument("--mode", default="tp_lb", choices=list(MODES))
+    ap.add_argument("--shard-cut", default="balanced", choices=["balanced", "equal"],
+                    help="N > 1, walk workloads: cut the job's seed range where the ranks' expected work is equal "
+                         "(nextdoor_b200.dist.balanced_bounds) or into the reference's equal counts (src/utils.hpp:26-27)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the c2 roofline pass and the reference-GPU leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end and gather legs (kernel A/B runs)")
@@ -500,7 +503,18 @@ def main():
     mode = MODES[a.mode]
     g = nd.Graph.rmat(V, M, seed, device=local)
     pr = params_for(nd, wl, seed)
-    first, S = nd.shard_range(S_total, rank, world)     # the reference's seed ranges: one job, cut N ways
+    # one job, cut N ways into contiguous seed ranges: the reference's equal counts, or -- walks start
+    # sample i at vertex i and the generator leaves most high vertex ids without neighbours -- ranges
+    # of equal expected work (the samples are the same either way: the draws are keyed by sample index)
+    bounds = None
+    if world > 1 and wl["kind"] == WALK and a.shard_cut == "balanced":
+        from nextdoor_b200 import dist as nd_dist
+        all_init = torch.from_numpy(seeds_for(wl, 0, S_total)).cuda()
+        bounds = nd_dist.balanced_bounds(nd_dist.walk_start_weights(g, all_init), world)
+        del all_init
+        first, S = nd_dist.shard(S_total, rank, world, bounds)
+    else:
+        first, S = nd.shard_range(S_total, rank, world)
     init_np = seeds_for(wl, first, S)
     smp = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=init_np)
     fs = smp.fs
@@ -544,12 +558,15 @@ def main():
     # the next step is sampled (two sampler sets alternate).
     ms_e2e = e2e_check = d2h = None
     if not a.no_e2e:
-        init_host = torch.from_numpy(init_np).pin_memory()
-        out_host = torch.empty(S * fs, dtype=torch.int32).pin_memory()
-        out_host2 = torch.empty(S * fs, dtype=torch.int32).pin_memory()   # consecutive steps land in alternating buffers
+        # this leg is bound by the result rows each rank copies to the host, empty or not: equal counts
+        first_e, S_e = (first, S) if bounds is None else nd.shard_range(S_total, rank, world)
+        init_e = init_np if bounds is None else seeds_for(wl, first_e, S_e)
+        init_host = torch.from_numpy(init_e).pin_memory()
+        out_host = torch.empty(S_e * fs, dtype=torch.int32).pin_memory()
+        out_host2 = torch.empty(S_e * fs, dtype=torch.int32).pin_memory()   # consecutive steps land in alternating buffers
         init_pin, out_pin, out_pin2 = init_host.numpy(), out_host.numpy(), out_host2.numpy()
         copy_stream = torch.cuda.Stream()
-        pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=init_np, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
+        pipe = nd.PipelinedSampler(g, pr, S_e, first_sample=first_e, initial=init_e, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
                                    stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream)
         for _ in range(2):
             pipe.run(init_pin, out_pin, mode)
@@ -566,7 +583,7 @@ def main():
         e2e_check = int((last_pin != V).sum()) if wl["kind"] != COLL else None
         pipe.free()
         # the ceiling of that leg: the same result copy alone (every rank at once, nothing sampled)
-        src = torch.empty(S * fs, dtype=torch.int32, device="cuda")
+        src = torch.empty(S_e * fs, dtype=torch.int32, device="cuda")
         for _ in range(1):
             out_host.copy_(src, non_blocking=True)
         barrier()
@@ -613,7 +630,7 @@ def main():
                 wait_all(k ^ 1)                # the single gathered array is still being written
             with torch.cuda.stream(side):
                 side.wait_event(ev)
-                pending[k] = nd_dist.gather_samples_start(shard_k, S_total, fulls[k % n_full] if rank == 0 else None) or None
+                pending[k] = nd_dist.gather_samples_start(shard_k, S_total, fulls[k % n_full] if rank == 0 else None, bounds=bounds) or None
 
         def gather_drain():
             for k in range(2):
@@ -679,7 +696,10 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
             "config": {"workload": f"{a.workload}: {wl['desc']}", "app": APP_NAMES[app], "mode": a.mode,
                        "samples_total": S_total, "samples_rank0": S, "final_sample_size": fs,
-                       "sharding": "one job, contiguous seed ranges (src/utils.hpp:26-27), graph replicated per GPU",
+                       "sharding": ("one job, contiguous seed ranges of equal expected work (walks that can start weigh 1, the others 1/16), "
+                                    "graph replicated per GPU" if bounds else
+                                    "one job, contiguous seed ranges of equal counts (src/utils.hpp:26-27), graph replicated per GPU"),
+                       "shard_bounds": bounds,
                        "graph": graph_desc,
                        "l2": "working set (graph + sample buffers) larger than L2; no flush between steps",
                        "sampled_edges_per_step": per_step},
@@ -687,6 +707,7 @@ def main():
                 "value": per_step * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
                 "h2d_bytes_per_step": int(4 * S_total * smp.isz), "d2h_bytes_per_step": int(S_total * fs * 4),
                 "chunks": E2E_CHUNKS, "depth": E2E_DEPTH, "mode": a.mode, "valid_vertices_in_host_result": int(e2e_total),
+                "sharding": "equal counts (src/utils.hpp:26-27): the result rows each rank copies out bound this leg",
                 "d2h_ceiling_gbs": S_total * fs * 4 / (d2h * 1e-3) / 1e9 if d2h else None,
                 "d2h_ceiling_note": "all ranks copying their shard of the result to pinned host memory at once, nothing else running; "
                                     "aggregate GB/s; value <= d2h_ceiling / (4 * final_sample_size) * sampled edges per sample slot"},

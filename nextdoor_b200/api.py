@@ -124,6 +124,12 @@ class Graph:
         check(lib.nd_graph_to_host(self._h, _ptr(row_ptr), _ptr(col), _ptr(w), _ptr(mw)))
         return row_ptr, col, w, mw
 
+    def row_ptr_device_ptr(self) -> int:
+        """Address of the replica's row-offset array [V + 1] int32 in device memory (read-only for callers)."""
+        rp = C.c_void_p()
+        check(lib.nd_graph_device_ptrs(self._h, C.byref(rp), None, None, None))
+        return int(rp.value)
+
     def partition(self, budget_bytes, max_parts=4096):
         fv = np.zeros(max_parts, np.int32)
         lv = np.zeros(max_parts, np.int32)

@@ -27,10 +27,21 @@ def _worker(rank, world, port, total, fs_steps, ret):
     full = nd_dist.all_gather_samples(torch.from_numpy(local.copy()), total)
     one = nd_dist.gather_samples_to(torch.from_numpy(local.copy()), total, dst=0)     # the gather the benchmark times
     assert (one is None) == (rank != 0)
+    # the same job cut where the work is balanced: walks from vertices without neighbours weigh little
+    init = np.arange(total) % g.V
+    has = np.diff(g.row_ptr)[init] > 0
+    bounds = nd_dist.balanced_bounds(torch.from_numpy(np.where(has, 1.0, 1.0 / 16)), world)
+    bf, bc = nd_dist.shard(total, rank, world, bounds)
+    blocal = ndo.sample(g, pr, bc, first=bf)["out"]
+    bfull = nd_dist.all_gather_samples(torch.from_numpy(blocal.copy()), total, bounds=bounds)
+    bone = nd_dist.gather_samples_to(torch.from_numpy(blocal.copy()), total, dst=0, bounds=bounds)
     if rank == 0:
         whole = ndo.sample(g, pr, total)["out"]
         ret["ok"] = bool(np.array_equal(full.numpy(), whole)) and bool(np.array_equal(one.numpy(), whole))
+        ret["ok_balanced"] = bool(np.array_equal(bfull.numpy(), whole)) and bool(np.array_equal(bone.numpy(), whole))
         ret["ranges"] = [nd_dist.shard(total, r, world) for r in range(world)]
+        ret["bounds"] = list(bounds)
+        ret["active"] = [int(has[bounds[r]:bounds[r + 1]].sum()) for r in range(world)]
     dist.destroy_process_group()
 
 
@@ -50,6 +61,28 @@ def test_two_ranks_gather_equals_single_job():
         assert ret["ok"]
         (f0, c0), (f1, c1) = ret["ranges"]
         assert (f0, c0) == (0, total // 2) and (f1, c1) == (total // 2, total - total // 2)
+        assert ret["ok_balanced"]
+        b, act = ret["bounds"], ret["active"]
+        assert b[0] == 0 and b[2] == total and 0 < b[1] < total
+        assert abs(act[0] - act[1]) <= 0.1 * sum(act) + 16      # the R-MAT ids put the isolated vertices at the high end
+
+
+def test_balanced_bounds_edge_cases():
+    from nextdoor_b200 import build
+    build.build()
+    from nextdoor_b200 import dist as nd_dist
+    assert nd_dist.balanced_bounds(torch.ones(8), 4) == [0, 2, 4, 6, 8]
+    assert nd_dist.balanced_bounds(torch.ones(0), 3) == [0, 0, 0, 0]
+    assert nd_dist.balanced_bounds(torch.zeros(9), 3) == [0, 3, 6, 9]             # no weight at all: the equal ranges
+    assert nd_dist.balanced_bounds(torch.tensor([0., 0, 0, 5, 0, 0]), 2) == [0, 4, 6]  # one heavy sample: it stays whole
+    b = nd_dist.balanced_bounds(torch.tensor([1., 1, 1, 1, 0, 0, 0, 0, 0, 0]), 4)
+    assert b == [0, 1, 2, 3, 10]
+    w = torch.rand(1000, dtype=torch.float64)
+    b = nd_dist.balanced_bounds(w, 7)
+    assert b[0] == 0 and b[-1] == 1000 and all(x <= y for x, y in zip(b, b[1:]))
+    sums = [float(w[b[i]:b[i + 1]].sum()) for i in range(7)]
+    assert max(sums) - min(sums) <= 2.0                                            # within two samples' weight
+    assert nd_dist.shard(1000, 3, 7, b) == (b[3], b[4] - b[3])
 
 
 class _CpuOps:

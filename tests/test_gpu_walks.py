@@ -190,6 +190,35 @@ def test_shards_concatenate_to_the_single_gpu_answer(nd, ndo, small_graph):
     assert np.array_equal(np.concatenate(parts), whole.final_samples())
 
 
+def test_balanced_seed_ranges_concatenate_to_the_single_gpu_answer(nd, ndo, small_graph):
+    """Seed ranges cut where the expected work is equal (walks from vertices without neighbours
+    weigh 1/16): the weights come from the device's row offsets, and the shards still
+    concatenate to the unsharded job."""
+    import torch
+    from nextdoor_b200 import dist as nd_dist
+    g = _graph(nd, small_graph)
+    S = 5000
+    init = (np.arange(S) % small_graph.V).astype(np.int32)
+    init[100:900] = -1                                  # a stretch of walks that cannot start
+    wts = nd_dist.walk_start_weights(g, torch.from_numpy(init).cuda())
+    clean = np.clip(init, 0, small_graph.V - 1)
+    has = (np.diff(small_graph.row_ptr)[clean] > 0) & (init >= 0)
+    assert np.array_equal(wts.cpu().numpy(), np.where(has, 1.0, 1.0 / 16))
+    bounds = nd_dist.balanced_bounds(wts, 4)
+    act = [int(has[bounds[r]:bounds[r + 1]].sum()) for r in range(4)]
+    assert max(act) - min(act) <= 0.05 * sum(act) + 16
+    pr = nd.app_params(2, steps=30, seed=8, stop_prob=0.15)
+    whole = nd.Sampler(g, pr, num_samples=S, initial=init)
+    whole.sample(1)
+    parts = []
+    for r in range(4):
+        f, c = nd_dist.shard(S, r, 4, bounds)
+        sh = nd.Sampler(g, pr, num_samples=c, first_sample=f, initial=init[f:f + c])
+        sh.sample(1)
+        parts.append(sh.final_samples())
+    assert np.array_equal(np.concatenate(parts), whole.final_samples())
+
+
 @pytest.mark.parametrize("app", [0, 3])
 def test_full_size_properties(nd, ndo, app):
     """Benchmark-sized run (2^20 vertices, 16M undirected edges, one 100-step walk per vertex):
