@@ -696,7 +696,7 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
             "config": {"workload": f"{a.workload}: {wl['desc']}", "app": APP_NAMES[app], "mode": a.mode,
                        "samples_total": S_total, "samples_rank0": S, "final_sample_size": fs,
-                       "sharding": ("one job, contiguous seed ranges of equal expected work (walks that can start weigh 1, the others 1/16), "
+                       "sharding": ("one job, contiguous seed ranges of equal expected work (walks that can start weigh 1, the others 1/7), "
                                     "graph replicated per GPU" if bounds else
                                     "one job, contiguous seed ranges of equal counts (src/utils.hpp:26-27), graph replicated per GPU"),
                        "shard_bounds": bounds,

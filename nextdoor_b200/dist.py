@@ -55,7 +55,10 @@ def balanced_bounds(weights, world: int):
     return [0] + inner + [total]
 
 
-def walk_start_weights(graph: "api.Graph", initial, idle: float = 1.0 / 16):
+IDLE_WALK_WEIGHT = 1.0 / 7   # measured on the 2^24-vertex PPR job cut 4 and 8 ways: the value that levels the ranks' times
+
+
+def walk_start_weights(graph: "api.Graph", initial, idle: float = IDLE_WALK_WEIGHT):
     """Per-sample weights for balanced_bounds of a walk job on a replicated graph: 1 for a walk
     whose start vertex has neighbours, `idle` for one that cannot start (it still costs its slot
     in the first step and its row of the result).  `initial`: the job's start vertices, a CUDA

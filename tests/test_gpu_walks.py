@@ -192,7 +192,7 @@ def test_shards_concatenate_to_the_single_gpu_answer(nd, ndo, small_graph):
 
 def test_balanced_seed_ranges_concatenate_to_the_single_gpu_answer(nd, ndo, small_graph):
     """Seed ranges cut where the expected work is equal (walks from vertices without neighbours
-    weigh 1/16): the weights come from the device's row offsets, and the shards still
+    weigh a seventh): the weights come from the device's row offsets, and the shards still
     concatenate to the unsharded job."""
     import torch
     from nextdoor_b200 import dist as nd_dist
@@ -203,7 +203,7 @@ def test_balanced_seed_ranges_concatenate_to_the_single_gpu_answer(nd, ndo, smal
     wts = nd_dist.walk_start_weights(g, torch.from_numpy(init).cuda())
     clean = np.clip(init, 0, small_graph.V - 1)
     has = (np.diff(small_graph.row_ptr)[clean] > 0) & (init >= 0)
-    assert np.array_equal(wts.cpu().numpy(), np.where(has, 1.0, 1.0 / 16))
+    assert np.allclose(wts.cpu().numpy(), np.where(has, 1.0, nd_dist.IDLE_WALK_WEIGHT))
     bounds = nd_dist.balanced_bounds(wts, 4)
     act = [int(has[bounds[r]:bounds[r + 1]].sum()) for r in range(4)]
     assert max(act) - min(act) <= 0.05 * sum(act) + 16
