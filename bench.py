@@ -556,7 +556,8 @@ def main():
     # H2D from pinned memory, sample, result D2H into pinned memory, through
     # nextdoor_b200.api.PipelinedSampler: the result of a step is copied on a second stream while
     # the next step is sampled (two sampler sets alternate).
-    ms_e2e = e2e_check = d2h = None
+    ms_e2e = e2e_check = d2h = ms_e2e_dense = None
+    e2e_sparse, e2e_values = False, 0
     if not a.no_e2e:
         # this leg is bound by the result rows each rank copies to the host, empty or not: equal counts
         first_e, S_e = (first, S) if bounds is None else nd.shard_range(S_total, rank, world)
@@ -567,21 +568,31 @@ def main():
         init_pin, out_pin, out_pin2 = init_host.numpy(), out_host.numpy(), out_host2.numpy()
         copy_stream = torch.cuda.Stream()
         pipe = nd.PipelinedSampler(g, pr, S_e, first_sample=first_e, initial=init_e, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
-                                   stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream)
-        for _ in range(2):
-            pipe.run(init_pin, out_pin, mode)
-        barrier()
-        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        x0.record(stream)
-        for i in range(a.steps):                  # step i+1 starts sampling while the tail of step i is being copied
-            pipe.run_async(init_pin, out_pin if i % 2 == 0 else out_pin2, mode)
-        pipe.wait()                               # every step's result has landed on the host
-        x1.record(stream)
-        barrier()
-        ms_e2e = x0.elapsed_time(x1)
+                                   stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream, sparse_rows=True)
+        def e2e_passes(p):
+            p.run(init_pin, out_pin, mode)            # untimed: both host arrays have been filled once
+            p.run(init_pin, out_pin2, mode)
+            barrier()
+            x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x0.record(stream)
+            for i in range(a.steps):                  # step i+1 is sampled while the result of step i is on its way
+                p.run_async(init_pin, out_pin if i % 2 == 0 else out_pin2, mode)
+            p.wait()                                  # every step's result has landed in the host array
+            x1.record(stream)
+            barrier()
+            return x0.elapsed_time(x1)
+
+        ms_e2e = e2e_passes(pipe)
         last_pin = out_pin if a.steps % 2 == 1 else out_pin2    # the buffer the last step wrote
         e2e_check = int((last_pin != V).sum()) if wl["kind"] != COLL else None
+        e2e_sparse, e2e_values = pipe.sparse_rows, pipe.values_copied
         pipe.free()
+        ms_e2e_dense = None
+        if e2e_sparse:      # the same leg with the dense array copied every step, for comparison
+            pipe = nd.PipelinedSampler(g, pr, S_e, first_sample=first_e, initial=init_e, chunks=E2E_CHUNKS, depth=E2E_DEPTH,
+                                       stream=stream.cuda_stream, copy_stream=copy_stream.cuda_stream, sparse_rows=False)
+            ms_e2e_dense = e2e_passes(pipe)
+            pipe.free()
         # the ceiling of that leg: the same result copy alone (every rank at once, nothing sampled)
         src = torch.empty(S_e * fs, dtype=torch.int32, device="cuda")
         for _ in range(1):
@@ -658,13 +669,15 @@ def main():
     roof, ph, st = roofline_of(nd, smp, wl, a.workload, a.mode, mode, ms / a.steps, hbm_peak, peak_kind, local,
                                with_gather_probe=(rank == 0))
 
-    tms = torch.tensor([ms, ms_e2e or 0.0, ms_gather or 0.0, ms_sp or 0.0, d2h or 0.0], dtype=torch.float64, device="cuda")
-    tot = torch.tensor([float(edges_step), float(e2e_check or 0)], dtype=torch.float64, device="cuda")
+    tms = torch.tensor([ms, ms_e2e or 0.0, ms_gather or 0.0, ms_sp or 0.0, d2h or 0.0, ms_e2e_dense or 0.0], dtype=torch.float64, device="cuda")
+    tot = torch.tensor([float(edges_step), float(e2e_check or 0), float(e2e_values)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-    ms, ms_e2e, ms_gather, ms_sp, d2h = (float(x) for x in tms)
-    total_edges, e2e_total = float(tot[0]), float(tot[1])
+    ms, ms_e2e, ms_gather, ms_sp, d2h, ms_e2e_dense = (float(x) for x in tms)
+    total_edges, e2e_total, e2e_values = float(tot[0]), float(tot[1]), float(tot[2])
+    if ms_e2e and wl["kind"] == WALK:
+        assert int(e2e_total) == int(total_edges), "the host arrays of the end-to-end leg do not hold the job's sampled vertices"
     if world > 1 and ms_gather and rank == 0 and gathered_edges is not None:
         assert gathered_edges == int(total_edges), "the array gathered on rank 0 does not hold the whole job"
 
@@ -705,12 +718,20 @@ def main():
                        "sampled_edges_per_step": per_step},
             "e2e": None if ms_e2e is None or ms_e2e <= 0 else {
                 "value": per_step * a.steps / (ms_e2e * 1e-3), "unit": "sampled edges/s",
-                "h2d_bytes_per_step": int(4 * S_total * smp.isz), "d2h_bytes_per_step": int(S_total * fs * 4),
+                "h2d_bytes_per_step": int(4 * S_total * smp.isz),
+                "d2h_bytes_per_step": int(4 * (S_total + e2e_values)) if e2e_sparse else int(S_total * fs * 4),
+                "host_result": ("the caller's dense [samples, finalSampleSize] host array, kept from step to step: row lengths and the rows' "
+                                "valid prefixes cross PCIe, host threads rewrite the slots that changed (nd_sampler_host_update_*)"
+                                if e2e_sparse else "the dense [samples, finalSampleSize] array copied every step"),
+                "dense_result_bytes": int(S_total * fs * 4),
+                "dense_copy": None if not ms_e2e_dense else {
+                    "value": per_step * a.steps / (ms_e2e_dense * 1e-3), "unit": "sampled edges/s",
+                    "note": "same leg with the dense array copied every step (PipelinedSampler(sparse_rows=False)), the path d2h_ceiling bounds"},
                 "chunks": E2E_CHUNKS, "depth": E2E_DEPTH, "mode": a.mode, "valid_vertices_in_host_result": int(e2e_total),
                 "sharding": "equal counts (src/utils.hpp:26-27): the result rows each rank copies out bound this leg",
                 "d2h_ceiling_gbs": S_total * fs * 4 / (d2h * 1e-3) / 1e9 if d2h else None,
                 "d2h_ceiling_note": "all ranks copying their shard of the result to pinned host memory at once, nothing else running; "
-                                    "aggregate GB/s; value <= d2h_ceiling / (4 * final_sample_size) * sampled edges per sample slot"},
+                                    "aggregate GB/s; dense_copy.value <= d2h_ceiling / (4 * final_sample_size) * sampled edges per sample slot"},
             "gpu_launches": int(launches),
             "sample_parallel": None if mode == 2 else {"value": per_step * a.steps / (ms_sp * 1e-3), "unit": "sampled edges/s",
                                                        "note": "same sampler, same samples, nd_mode SampleParallel"},

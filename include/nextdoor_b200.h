@@ -139,6 +139,25 @@ int nd_sampler_final_samples(nd_sampler *s, int32_t *out);
  * pinned `out` the copy overlaps the sampling of the next chunk.  Wait for the copy stream
  * (nd_stream_sync) before reading `out` and before the next sample() of this sampler. */
 int nd_sampler_final_samples_async(nd_sampler *s, int32_t *out, void *copy_stream);
+/* Walk apps: bring a caller's dense host array `out` [num_samples, finalSampleSize] up to date with the
+ * sampler's result while moving only the rows' valid prefixes over PCIe (no counterpart in the reference, whose
+ * getFinalSamples copies the dense array, src/nextdoor.cu:3211-3237; the array the caller ends up with is the
+ * same).  `row_len` [num_samples] belongs to `out`: the number of leading slots of each row that may hold a
+ * vertex, every other slot of `out` holding the invalid id (= V).  Start with `out` filled with the invalid id
+ * and `row_len` zero (nd_host_fill_int32), hand the same pair to every later update and leave both alone in
+ * between: an update rewrites only the slots a walk fills now or filled at the array's previous update.
+ *   begin:  packs the prefixes on the device (sampler's stream) and enqueues the copy of the row lengths on
+ *           `copy_stream` (NULL: the sampler's stream); returns at once.
+ *   fetch:  waits for the lengths, then enqueues the copy of the packed vertices (or of the dense array when
+ *           more than half of its slots are in use); optional -- finish calls it when the caller did not.
+ *   finish: waits for that copy and writes the rows with host threads (ND_HOST_THREADS, default: the hardware
+ *           threads, at most 32); `values_copied` (may be NULL) receives the number of vertex slots that crossed.
+ * One update at a time per sampler; the sampler's next sample() waits on the device for the copies. */
+int nd_sampler_host_update_begin(nd_sampler *s, int32_t *out, int32_t *row_len, void *copy_stream);
+int nd_sampler_host_update_fetch(nd_sampler *s);
+int nd_sampler_host_update_finish(nd_sampler *s, int64_t *values_copied);
+/* dst[0..n) = value with the same host threads (first fill of a result array) */
+int nd_host_fill_int32(int32_t *dst, int64_t n, int32_t value);
 int nd_stream_sync(int device, void *stream);
 /* zero-copy variant: device address of the same array.  READ-ONLY for the caller: for the walk
  * applications the library keeps the array between sample() calls and rewrites only the slots a

@@ -199,6 +199,20 @@ class Sampler:
         reading `out`."""
         check(lib.nd_sampler_final_samples_async(self._h, _ptr(out), C.c_void_p(copy_stream) if copy_stream else None))
 
+    def host_update_begin(self, out, row_len, copy_stream=None):
+        """Walk apps: start bringing the dense host array `out` (with its per-row lengths `row_len`,
+        see new_host_result) up to date while copying only the rows' valid prefixes."""
+        check(lib.nd_sampler_host_update_begin(self._h, _ptr(out), _ptr(row_len), C.c_void_p(copy_stream) if copy_stream else None))
+
+    def host_update_fetch(self):
+        check(lib.nd_sampler_host_update_fetch(self._h))
+
+    def host_update_finish(self) -> int:
+        """Blocks until `out` holds this job's result; returns the vertex slots that crossed PCIe."""
+        n = C.c_int64(0)
+        check(lib.nd_sampler_host_update_finish(self._h, C.byref(n)))
+        return int(n.value)
+
     def final_samples_device_ptr(self):
         p = C.c_void_p()
         check(lib.nd_sampler_final_samples_device(self._h, C.byref(p)))
@@ -251,6 +265,12 @@ class Sampler:
             pass
 
 
+def host_fill(arr, value):
+    """arr[:] = value with the library's host threads (the first fill of a large result array)."""
+    flat = arr.reshape(-1)
+    check(lib.nd_host_fill_int32(_ptr(flat), flat.shape[0], int(value)))
+
+
 class PipelinedSampler:
     """The job cut into `chunks` seed ranges that are sampled one after the other on one stream
     while the result of each finished chunk is copied to the host on a second stream, so the
@@ -260,13 +280,26 @@ class PipelinedSampler:
     replay its CUDA graph)."""
 
     def __init__(self, graph: Graph, params: AppParams, num_samples, first_sample=0, initial=None, chunks=4,
-                 stream=None, copy_stream=None, depth=1):
+                 stream=None, copy_stream=None, depth=1, sparse_rows=False):
         """depth > 1 keeps that many independent sets of samplers (own result buffers) and rotates
         through them job by job, so with run_async() a whole job's copy overlaps the next job's
-        sampling even with chunks=1 (no small-launch penalty from cutting the job)."""
+        sampling even with chunks=1 (no small-launch penalty from cutting the job).
+        sparse_rows=True (walk apps; otherwise ignored): a host array handed to run()/run_async() is
+        filled with the invalid id once and remembered by its address; later jobs into the same array
+        copy only the rows' valid prefixes and rewrite only the slots that changed since the array's
+        previous job.  The array ends up exactly as with the dense copy, provided the caller does not
+        write to it in between (forget(out) drops the memory of an array).  The default copies the
+        dense array every time."""
         self.S, self.fs, self.isz = int(num_samples), final_sample_size(params), initial_sample_size(params)
         self.device, self.copy_stream = graph.device, copy_stream
         self.sets, self._job = [], 0
+        # Walk jobs move only the rows' valid prefixes to the host (nd_sampler_host_update_*): the
+        # per-row lengths of every host array this object has filled, by the array's address, and
+        # the jobs whose rows are still to be written (at most one per sampler set).
+        self.sparse_rows = sparse_rows and params.app <= APP_NODE2VEC
+        self.invalid = graph.V
+        self._row_len, self._pending = {}, {}
+        self.values_copied = 0          # vertex slots the last finished job moved over PCIe
         for _ in range(max(1, depth)):
             parts = []
             for c in range(chunks):
@@ -289,15 +322,49 @@ class PipelinedSampler:
         job is sampled while the last chunk of this one is still on its way to the host (the
         library orders a chunk's next sampling after its own pending copy).  Give consecutive
         jobs different `out_host` buffers and call wait() before reading them."""
-        self.parts = self.sets[self._job % len(self.sets)]
+        k = self._job % len(self.sets)
+        self.parts = self.sets[k]
         self._job += 1
+        if not self.sparse_rows:
+            for f, n, smp in self.parts:
+                if initial_host is not None:
+                    smp.set_initial(initial_host[f * self.isz:(f + n) * self.isz])
+                smp.sample(mode, sync=False)
+                smp.final_samples_async(out_host[f * self.fs:(f + n) * self.fs], self.copy_stream)
+            return
+        self._finish(k)                                   # this set's previous job still owns its staging buffers
+        others = [j for j in self._pending if j != k]
+        for j in others:                                  # the lengths of the job before have landed: its vertices
+            for _, _, smp in self.sets[j]:                # cross while this job is sampled
+                smp.host_update_fetch()
+        row_len = self._rows_of(out_host)
         for f, n, smp in self.parts:
             if initial_host is not None:
                 smp.set_initial(initial_host[f * self.isz:(f + n) * self.isz])
             smp.sample(mode, sync=False)
-            smp.final_samples_async(out_host[f * self.fs:(f + n) * self.fs], self.copy_stream)
+            smp.host_update_begin(out_host[f * self.fs:(f + n) * self.fs], row_len[f:f + n], self.copy_stream)
+        self._pending[k] = True
+        for j in others:                                  # ... and its rows are written while the device works on this one
+            self._finish(j)
+
+    def _rows_of(self, out_host):
+        key = (out_host.__array_interface__["data"][0], out_host.size)
+        if key not in self._row_len:
+            host_fill(out_host, self.invalid)
+            self._row_len[key] = np.zeros(self.S, np.int32)
+        return self._row_len[key]
+
+    def forget(self, out_host):
+        """The caller is going to write to `out_host` itself: the next job into it starts from a fresh fill."""
+        self._row_len.pop((out_host.__array_interface__["data"][0], out_host.size), None)
+
+    def _finish(self, k):
+        if self._pending.pop(k, None):
+            self.values_copied = sum(smp.host_update_finish() for _, _, smp in self.sets[k])
 
     def wait(self):
+        for k in list(self._pending):
+            self._finish(k)
         for parts in self.sets:
             for _, _, smp in parts:
                 smp.sync()

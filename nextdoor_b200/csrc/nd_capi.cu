@@ -75,6 +75,7 @@ __global__ void default_initial_kernel(int64_t first, int64_t S, int isz, int32_
 }
 
 void free_sampler(nd_sampler *s) {
+  nd_hostrows_free(s);
   cudaFree(s->d_initial); cudaFree(s->d_out); cudaFree(s->d_tmp); cudaFree(s->d_len); cudaFree(s->d_plen); cudaFree(s->d_state);
   for (int i = 0; i < 2; i++) { cudaFree(s->d_map_key[i]); cudaFree(s->d_map_val[i]); }
   cudaFree(s->d_init_key); cudaFree(s->d_init_val); cudaFree(s->d_nlive); cudaFree(s->d_stats); cudaFree(s->d_status);

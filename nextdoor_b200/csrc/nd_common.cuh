@@ -140,6 +140,8 @@ struct NdPhaseTimer {
   int launches[ND_PHASE_COUNT] = {0};
 };
 
+struct NdHostRows;   // state of the sparse result update of a caller's host array (nd_hostrows.cu)
+
 struct nd_sampler {
   const nd_graph *g = nullptr;
   NdDeviceInfo dev;
@@ -202,9 +204,12 @@ struct nd_sampler {
   double *d_acc = nullptr;        // LADIES: per-CTA accumulators of the candidates' weights
   unsigned char *d_bm = nullptr;  // per-CTA bitmap slices when a bit per vertex does not fit shared memory
 
+  NdHostRows *hostrows = nullptr;
+
   NdPhaseTimer timer;
   int64_t host_stats[8] = {0};
 };
+void nd_hostrows_free(nd_sampler *s);
 
 // phase timing helpers (no-ops unless profiling is on)
 void nd_phase_begin(nd_sampler *s, int phase);

@@ -289,6 +289,87 @@ def test_pipelined_sampler_equals_single_sampler(nd, ndo, small_graph):
     assert pipe.stats()["sampled_edges"] == exp["counters"]["sampled_edges"]
 
 
+def test_host_array_updated_by_row_prefixes(nd, ndo, small_graph):
+    """nd_sampler_host_update_*: only the rows' valid prefixes cross to the host and only the
+    slots that changed are rewritten in the caller's dense array, which must equal the dense copy
+    after every pass -- rows growing, shrinking, vanishing; all three modes; the dense fallback
+    when most slots are in use; zero samples."""
+    g = _graph(nd, small_graph)
+    V = small_graph.V
+    S, steps = 20_011, 40
+    rng = np.random.default_rng(9)
+    pr = nd.app_params(2, steps=steps, seed=5, stop_prob=0.15)
+    s = nd.Sampler(g, pr, num_samples=S, first_sample=2)
+    out = np.empty(S * steps, np.int32)
+    nd.host_fill(out, V)
+    assert (out == V).all()
+    row_len = np.zeros(S, np.int32)
+    copied = []
+    for p, mode in enumerate((1, 2, 0, 1, 1)):
+        init = rng.integers(0, V, S).astype(np.int32)
+        if p == 3:
+            init[: S // 2] = -1                          # half of the rows become empty
+        s.set_initial(init)
+        s.sample(mode)
+        s.host_update_begin(out, row_len)
+        if p % 2:
+            s.host_update_fetch()                        # optional middle call
+        copied.append(s.host_update_finish())
+        dense = s.final_samples()
+        assert np.array_equal(out.reshape(S, steps), dense), p
+        assert np.array_equal(row_len, (dense != V).sum(axis=1)), p
+        assert copied[-1] == int((dense != V).sum()) < S * steps // 4
+    s.free()
+    # full-length walks: more than half of the slots in use, the dense array is copied as it is
+    pr = nd.app_params(0, steps=steps, seed=5)
+    s = nd.Sampler(g, pr, num_samples=S)
+    s.sample(1)
+    s.host_update_begin(out, row_len)
+    assert s.host_update_finish() == S * steps
+    assert np.array_equal(out.reshape(S, steps), s.final_samples())
+    assert np.array_equal(row_len, (s.final_samples() != V).sum(axis=1))
+    s.free()
+    s0 = nd.Sampler(g, pr, num_samples=0)
+    s0.sample(1)
+    s0.host_update_begin(out[:0], row_len[:0])
+    assert s0.host_update_finish() == 0
+    k = nd.Sampler(g, nd.app_params(4, fanout=[3, 2], seed=1), num_samples=10)
+    k.sample(1)
+    with pytest.raises(nd.NdError):
+        k.host_update_begin(out, row_len)                # k-hop rows are not prefixes
+
+
+def test_pipelined_jobs_into_remembered_host_arrays(nd, ndo, small_graph):
+    """PipelinedSampler(sparse_rows=True): jobs with changing seeds alternate between two host
+    arrays without waiting in between; each array must hold its own job's dense result."""
+    import torch
+    g = _graph(nd, small_graph)
+    pr = nd.app_params(2, steps=40, seed=12, stop_prob=0.15)
+    opr = ndo.make_params(2, steps=40, seed=12, stop_prob=0.15)
+    S, first = 20_001, 5
+    st, cst = torch.cuda.Stream(), torch.cuda.Stream()
+    inits = [((np.arange(first, first + S) * k) % small_graph.V).astype(np.int32) for k in (1, 3, 7, 11, 13)]
+    inits[2][::2] = -1
+    for depth, chunks in ((2, 1), (1, 3), (3, 2)):
+        pipe = nd.PipelinedSampler(g, pr, S, first_sample=first, initial=inits[0], chunks=chunks, stream=st.cuda_stream,
+                                   copy_stream=cst.cuda_stream, depth=depth, sparse_rows=True)
+        pins = [torch.from_numpy(i).pin_memory().numpy() for i in inits]
+        outs = [torch.full((S * 40,), -7, dtype=torch.int32).pin_memory().numpy() for _ in range(2)]
+        for j, ip in enumerate(pins):
+            pipe.run_async(ip, outs[j % 2], 1)
+        pipe.wait()
+        for j in (len(inits) - 2, len(inits) - 1):       # the last job of each array
+            clean = np.where(inits[j] < 0, small_graph.V, inits[j]).astype(np.int32)
+            exp = ndo.sample(small_graph, opr, S, first=first, initial=clean)
+            assert np.array_equal(outs[j % 2].reshape(S, 40), exp["out"]), (depth, chunks, j)
+        assert pipe.values_copied == exp["counters"]["sampled_edges"]
+        pipe.forget(outs[0])
+        outs[0][:] = -3                                  # the caller scribbles: after forget() the next job refills the array
+        pipe.run(pins[0], outs[0], 2)
+        assert np.array_equal(outs[0].reshape(S, 40), ndo.sample(small_graph, opr, S, first=first, initial=inits[0])["out"])
+        pipe.free()
+
+
 def test_pipelined_jobs_back_to_back(nd, ndo, small_graph):
     """Jobs enqueued without waiting in between (the next job samples while the previous one's
     last chunk is still copied) land complete and unmixed in their own host buffers."""
