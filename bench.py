@@ -495,6 +495,8 @@ def main():
     import torch
     from nextdoor_b200 import api as nd
     torch.cuda.set_device(local)
+    if world > 1 and "ND_HOST_THREADS" not in os.environ:   # the ranks of one box share its host cores
+        os.environ["ND_HOST_THREADS"] = str(max(4, min(32, len(os.sched_getaffinity(0)) // world)))
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
