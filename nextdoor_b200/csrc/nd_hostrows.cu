@@ -163,16 +163,22 @@ int nd_sampler_host_update_begin(nd_sampler *s, int32_t *out, int32_t *row_len, 
   ND_REQUIRE(s->sampled, ND_ERR_STATE, "host update requested before sample()");
   ND_CUDA(cudaSetDevice(s->g->device));
   if (!s->hostrows) {
-    NdHostRows *h = new NdHostRows();
-    s->hostrows = h;
+    s->hostrows = new NdHostRows();   // a creation that fails half way is taken down again, so the next call starts over
+    NdHostRows *h = s->hostrows;
     const size_t S1 = (size_t)(s->S > 0 ? s->S : 1);
     h->n_chunks = (int)((S1 + PACK_ROWS - 1) / PACK_ROWS);
-    ND_CUDA(cudaMallocHost(&h->h_len, sizeof(int32_t) * S1));
-    ND_CUDA(cudaMalloc(&h->d_chunk, sizeof(uint32_t) * (size_t)h->n_chunks));
-    ND_CUDA(cudaEventCreateWithFlags(&h->packed, cudaEventDisableTiming));
-    ND_CUDA(cudaEventCreateWithFlags(&h->len_done, cudaEventDisableTiming));
-    ND_CUDA(cudaEventCreateWithFlags(&h->vals_done, cudaEventDisableTiming));
     h->threads = host_threads();
+    cudaError_t e = cudaMallocHost(&h->h_len, sizeof(int32_t) * S1);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_chunk, sizeof(uint32_t) * (size_t)h->n_chunks);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->packed, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->len_done, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->vals_done, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      nd_hostrows_free(s);
+      nd_set_error("nd_sampler_host_update_begin: staging buffers: %s", cudaGetErrorString(e));
+      cudaGetLastError();
+      return ND_ERR_CUDA;
+    }
   }
   NdHostRows *h = s->hostrows;
   ND_REQUIRE(h->stage == 0, ND_ERR_STATE, "the previous host update of this sampler was not finished");
@@ -180,6 +186,7 @@ int nd_sampler_host_update_begin(nd_sampler *s, int32_t *out, int32_t *row_len, 
   h->row_len = row_len;
   h->cs = copy_stream ? (cudaStream_t)copy_stream : s->stream;
   if (s->S == 0) { h->stage = 1; return ND_OK; }
+  // (an error below leaves stage 0: nothing was begun as far as the caller is concerned)
   // the rows' prefixes packed into the staging array of the walk (free between two passes)
   pack_sum_kernel<<<h->n_chunks, PACK_THREADS, 0, s->stream>>>(s->d_plen, s->S, h->d_chunk);
   pack_scan_kernel<<<1, 1024, 0, s->stream>>>(h->d_chunk, h->n_chunks);
@@ -204,10 +211,10 @@ int nd_sampler_host_update_begin(nd_sampler *s, int32_t *out, int32_t *row_len, 
 int nd_sampler_host_update_fetch(nd_sampler *s) {
   ND_REQUIRE(s && s->hostrows && s->hostrows->stage == 1, ND_ERR_STATE, "nd_sampler_host_update_fetch without a begun update");
   NdHostRows *h = s->hostrows;
-  h->stage = 2;
+  h->stage = 0;   // an error below abandons the update; stage 2 is set once the copy is enqueued
   h->total = 0;
   h->dense = false;
-  if (s->S == 0) return ND_OK;
+  if (s->S == 0) { h->stage = 2; return ND_OK; }
   ND_CUDA(cudaSetDevice(s->g->device));
   ND_CUDA(cudaEventSynchronize(h->len_done));
   std::vector<int64_t> part((size_t)h->threads, 0);
@@ -235,6 +242,7 @@ int nd_sampler_host_update_fetch(nd_sampler *s) {
     ND_CUDA(cudaEventRecord(s->copy_done, h->cs));
     s->copy_pending = true;
   }
+  h->stage = 2;
   return ND_OK;
 }
 
@@ -242,6 +250,7 @@ int nd_sampler_host_update_finish(nd_sampler *s, int64_t *values_copied) {
   ND_REQUIRE(s && s->hostrows && s->hostrows->stage >= 1, ND_ERR_STATE, "nd_sampler_host_update_finish without a begun update");
   NdHostRows *h = s->hostrows;
   if (h->stage == 1) ND_TRY(nd_sampler_host_update_fetch(s));
+  ND_REQUIRE(h->stage == 2, ND_ERR_STATE, "nd_sampler_host_update_finish: the update was abandoned after an error");
   h->stage = 0;
   if (values_copied) *values_copied = h->dense ? s->S * (int64_t)s->fs : h->total;
   if (s->S == 0) return ND_OK;
