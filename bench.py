@@ -615,7 +615,8 @@ def main():
     # src/nextdoor.cu:3211-3237).  Two samplers alternate: the transfer of a step's samples runs on
     # NCCL's stream while the next step is sampled; a sampler's next run waits for the transfer
     # that still reads its buffer.
-    ms_gather = None
+    ms_gather = ms_gather_dense = None
+    gather_values = 0
     if world > 1 and not a.no_e2e:
         from nextdoor_b200 import dist as nd_dist
         smp2 = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=init_np)
@@ -665,18 +666,58 @@ def main():
         if rank == 0:      # the gathered array holds the job: its valid vertices are the job's sampled edges (checked below)
             gathered_edges = int((fulls[((a.steps - 1) % 2) % n_full] != V).sum()) if wl["kind"] != COLL else None
         del fulls
+        # ---- walks: the same gather by row prefixes (every rank packs, rank 0 unpacks into the dense
+        # array it keeps from step to step); the transfer and unpacking of a step run on the side stream
+        # under the next step's sampling
+        if wl["kind"] == WALK:
+            ms_gather_dense = ms_gather
+            pg = nd_dist.PackedRowsGather(S_total, fs, V, dst=0, bounds=bounds)
+            waiting = [None]
+
+            def packed_step(i):
+                s_k = pair[i % 2][0]
+                s_k.sample(mode, sync=False)
+                h = pg.start(s_k)
+                if waiting[0] is not None:
+                    with torch.cuda.stream(side):
+                        pg.finish(waiting[0])
+                waiting[0] = h
+
+            def packed_drain():
+                if waiting[0] is not None:
+                    with torch.cuda.stream(side):
+                        pg.finish(waiting[0])
+                    waiting[0] = None
+
+            for i in range(2):
+                packed_step(i)
+            packed_drain()
+            barrier()
+            y0, y1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            y0.record(stream)
+            for i in range(a.steps):
+                packed_step(i)
+            packed_drain()
+            y1.record(stream)
+            barrier()
+            ms_gather = y0.elapsed_time(y1)
+            gather_values = pg.values_moved
+            if rank == 0:
+                assert int((pg.full != V).sum()) == gathered_edges, "the array gathered by row prefixes differs from the dense gather"
+            del pg
         smp2.free()
 
     # ---- per-phase device time of one instrumented pass (roofline of the next() kernels)
     roof, ph, st = roofline_of(nd, smp, wl, a.workload, a.mode, mode, ms / a.steps, hbm_peak, peak_kind, local,
                                with_gather_probe=(rank == 0))
 
-    tms = torch.tensor([ms, ms_e2e or 0.0, ms_gather or 0.0, ms_sp or 0.0, d2h or 0.0, ms_e2e_dense or 0.0], dtype=torch.float64, device="cuda")
+    tms = torch.tensor([ms, ms_e2e or 0.0, ms_gather or 0.0, ms_sp or 0.0, d2h or 0.0, ms_e2e_dense or 0.0, ms_gather_dense or 0.0],
+                       dtype=torch.float64, device="cuda")
     tot = torch.tensor([float(edges_step), float(e2e_check or 0), float(e2e_values)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-    ms, ms_e2e, ms_gather, ms_sp, d2h, ms_e2e_dense = (float(x) for x in tms)
+    ms, ms_e2e, ms_gather, ms_sp, d2h, ms_e2e_dense, ms_gather_dense = (float(x) for x in tms)
     total_edges, e2e_total, e2e_values = float(tot[0]), float(tot[1]), float(tot[2])
     if ms_e2e and wl["kind"] == WALK:
         assert int(e2e_total) == int(total_edges), "the host arrays of the end-to-end leg do not hold the job's sampled vertices"
@@ -739,9 +780,16 @@ def main():
                                                        "note": "same sampler, same samples, nd_mode SampleParallel"},
             "with_gather": None if not ms_gather else {
                 "value": per_step * a.steps / (ms_gather * 1e-3), "unit": "sampled edges/s",
-                "collective": "every rank sends its shard to rank 0 (NCCL send/recv), overlapped with the next step's sampling (two samplers alternate)",
-                "bytes_into_rank0_per_step": int((S_total - S) * fs * 4),
-                "floor_ms_at_770_GBps": (S_total - S) * fs * 4 / 770e9 * 1e3},
+                "collective": ("every rank packs its rows' valid prefixes and sends lengths + vertices to rank 0 (NCCL send/recv), which unpacks them "
+                               "into the dense [samples, finalSampleSize] array it keeps (nextdoor_b200.dist.PackedRowsGather); a step's transfer runs "
+                               "under the next step's sampling (two samplers alternate)" if ms_gather_dense else
+                               "every rank sends its dense shard to rank 0 (NCCL send/recv), overlapped with the next step's sampling (two samplers alternate)"),
+                "bytes_into_rank0_per_step": int(4 * (S_total - S) + 4 * gather_values) if ms_gather_dense else int((S_total - S) * fs * 4),
+                "dense_rows": None if not ms_gather_dense else {
+                    "value": per_step * a.steps / (ms_gather_dense * 1e-3), "unit": "sampled edges/s",
+                    "bytes_into_rank0_per_step": int((S_total - S) * fs * 4),
+                    "floor_ms_at_770_GBps": (S_total - S) * fs * 4 / 770e9 * 1e3,
+                    "note": "the same gather with every rank's dense shard sent (nextdoor_b200.dist.gather_samples_start)"}},
             "roofline": roof,
             "c2_next_roofline": c2_roof,
             "reference_gpu": ref_gpu,

@@ -158,6 +158,19 @@ int nd_sampler_host_update_fetch(nd_sampler *s);
 int nd_sampler_host_update_finish(nd_sampler *s, int64_t *values_copied);
 /* dst[0..n) = value with the same host threads (first fill of a result array) */
 int nd_host_fill_int32(int32_t *dst, int64_t n, int32_t value);
+/* The same packing between GPUs (no counterpart in the reference, which concatenates dense per-device arrays on the
+ * host, src/nextdoor.cu:3211-3237).  nd_sampler_pack_rows enqueues the packing on the sampler's stream and returns
+ * the device addresses of the row lengths [num_samples] and of the packed vertices (valid until the sampler's next
+ * sample()); nd_sampler_pack_rows_total waits for it and returns the number of packed vertices, i.e. how much of
+ * `d_vals` to send.  On the receiving GPU nd_rows_unpack writes `n_rows` rows into the dense array `d_out`
+ * [n_rows, steps] whose per-row state `d_row_len` it keeps (all zero over an array filled with `invalid` to start
+ * with): vertices from d_vals, the invalid id into slots a row held before and does not hold now.  `d_scratch`:
+ * nd_rows_scratch_words(n_rows) 32-bit words.  Everything is stream-ordered; nothing allocates. */
+int nd_sampler_pack_rows(nd_sampler *s, const int32_t **d_row_len, const int32_t **d_vals);
+int nd_sampler_pack_rows_total(nd_sampler *s, int64_t *total);
+int64_t nd_rows_scratch_words(int64_t n_rows);
+int nd_rows_unpack(int device, void *stream, int64_t n_rows, int steps, int32_t invalid, const int32_t *d_len,
+                   const int32_t *d_vals, int32_t *d_out, int32_t *d_row_len, uint32_t *d_scratch);
 int nd_stream_sync(int device, void *stream);
 /* zero-copy variant: device address of the same array.  READ-ONLY for the caller: for the walk
  * applications the library keeps the array between sample() calls and rewrites only the slots a

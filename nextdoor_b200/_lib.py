@@ -77,6 +77,10 @@ _SIGS = {
     "nd_sampler_host_update_fetch": (C.c_int, [VP]),
     "nd_sampler_host_update_finish": (C.c_int, [VP, C.POINTER(C.c_int64)]),
     "nd_host_fill_int32": (C.c_int, [VP, C.c_int64, C.c_int32]),
+    "nd_sampler_pack_rows": (C.c_int, [VP, C.POINTER(VP), C.POINTER(VP)]),
+    "nd_sampler_pack_rows_total": (C.c_int, [VP, C.POINTER(C.c_int64)]),
+    "nd_rows_scratch_words": (C.c_int64, [C.c_int64]),
+    "nd_rows_unpack": (C.c_int, [C.c_int, VP, C.c_int64, C.c_int, C.c_int32, VP, VP, VP, VP, VP]),
     "nd_stream_sync": (C.c_int, [C.c_int, VP]),
     "nd_sampler_final_samples_device": (C.c_int, [VP, C.POINTER(VP)]),
     "nd_sampler_aux": (C.c_int, [VP, VP, VP, VP, VP]),

@@ -213,6 +213,19 @@ class Sampler:
         check(lib.nd_sampler_host_update_finish(self._h, C.byref(n)))
         return int(n.value)
 
+    def pack_rows(self):
+        """Walk apps: enqueue the packing of the rows' valid prefixes; returns the device addresses
+        (row lengths [S] int32, packed vertices int32), valid until this sampler's next sample()."""
+        a, b = C.c_void_p(), C.c_void_p()
+        check(lib.nd_sampler_pack_rows(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def pack_rows_total(self) -> int:
+        """Waits for pack_rows(); the number of packed vertices."""
+        n = C.c_int64(0)
+        check(lib.nd_sampler_pack_rows_total(self._h, C.byref(n)))
+        return int(n.value)
+
     def final_samples_device_ptr(self):
         p = C.c_void_p()
         check(lib.nd_sampler_final_samples_device(self._h, C.byref(p)))
@@ -263,6 +276,16 @@ class Sampler:
             self.free()
         except Exception:
             pass
+
+
+def rows_scratch_words(n_rows: int) -> int:
+    return int(lib.nd_rows_scratch_words(n_rows))
+
+
+def rows_unpack(device, stream, n_rows, steps, invalid, len_ptr, vals_ptr, out_ptr, row_len_ptr, scratch_ptr):
+    """nd_rows_unpack on raw device addresses (ints); `stream` a raw cudaStream_t or None."""
+    check(lib.nd_rows_unpack(device, C.c_void_p(stream) if stream else None, n_rows, steps, invalid, C.c_void_p(len_ptr),
+                             C.c_void_p(vals_ptr), C.c_void_p(out_ptr), C.c_void_p(row_len_ptr), C.c_void_p(scratch_ptr)))
 
 
 def host_fill(arr, value):

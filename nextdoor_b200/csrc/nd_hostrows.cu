@@ -25,7 +25,8 @@ struct NdHostRows {
   size_t vals_cap = 0;
   uint32_t *d_chunk = nullptr;  // per chunk of PACK_ROWS rows: sum of lengths, then exclusive prefix
   int n_chunks = 0;
-  cudaEvent_t packed = nullptr, len_done = nullptr, vals_done = nullptr;
+  cudaEvent_t packed = nullptr, len_done = nullptr, vals_done = nullptr, total_done = nullptr;
+  uint32_t *h_total = nullptr;  // pinned: number of packed vertices (nd_sampler_pack_rows)
   cudaStream_t cs = nullptr;
   int32_t *out = nullptr, *row_len = nullptr;
   int64_t total = 0;
@@ -55,7 +56,7 @@ pack_sum_kernel(const int32_t *__restrict__ plen, int64_t S, uint32_t *__restric
   }
 }
 
-// one CTA: chunk sums -> exclusive prefix in place
+// one CTA: chunk sums -> exclusive prefix in place, the grand total in chunk[n]
 __global__ void __launch_bounds__(1024) pack_scan_kernel(uint32_t *__restrict__ chunk, int n) {
   __shared__ uint32_t wsum[32];
   __shared__ uint32_t carry_sh;
@@ -78,6 +79,43 @@ __global__ void __launch_bounds__(1024) pack_scan_kernel(uint32_t *__restrict__ 
     __syncthreads();
     if (threadIdx.x == 1023) carry_sh = before + inc;
     __syncthreads();
+  }
+  if (threadIdx.x == 0) chunk[n] = carry_sh;
+}
+
+// the inverse of pack_rows_kernel on the receiving side: row r of `out` takes its len[r] vertices
+// from vals, the slots it held before beyond that (row_len[r]) go back to the invalid id
+__global__ void __launch_bounds__(PACK_THREADS)
+unpack_rows_kernel(const int32_t *__restrict__ len, const int32_t *__restrict__ vals, const uint32_t *__restrict__ chunk_base,
+                   int64_t S, int steps, int32_t invalid, int32_t *__restrict__ out, int32_t *__restrict__ row_len) {
+  __shared__ uint32_t wsum[PACK_THREADS / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t first = (int64_t)blockIdx.x * PACK_ROWS + (int64_t)threadIdx.x * PACK_PER_THREAD;
+  int32_t l[PACK_PER_THREAD];
+  uint32_t t = 0;
+#pragma unroll
+  for (int r = 0; r < PACK_PER_THREAD; r++) {
+    l[r] = first + r < S ? len[first + r] : 0;
+    t += (uint32_t)l[r];
+  }
+  uint32_t inc = t;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t u = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += u;
+  }
+  if (lane == 31) wsum[warp] = inc;
+  __syncthreads();
+  size_t pos = (size_t)chunk_base[blockIdx.x] + inc - t;
+  for (int w = 0; w < warp; w++) pos += wsum[w];
+#pragma unroll
+  for (int r = 0; r < PACK_PER_THREAD; r++) {
+    if (first + r >= S) break;
+    int32_t *row = out + (first + r) * steps;
+    const int32_t had = row_len[first + r];
+    for (int k = 0; k < l[r]; k++) row[k] = vals[pos + k];
+    for (int k = l[r]; k < had; k++) row[k] = invalid;
+    if (had != l[r]) row_len[first + r] = l[r];
+    pos += (size_t)l[r];
   }
 }
 
@@ -112,6 +150,9 @@ pack_rows_kernel(const int32_t *__restrict__ plen, const int32_t *__restrict__ o
   }
 }
 
+// positions in the packed array are 32-bit
+bool packable(const nd_sampler *s) { return s->S * (int64_t)s->fs < ((int64_t)1 << 32); }
+
 int host_threads() {
   if (const char *e = getenv("ND_HOST_THREADS")) {
     const int n = atoi(e);
@@ -131,7 +172,44 @@ void for_row_ranges(int64_t S, int threads, F fn) {
   for (auto &th : pool) th.join();
 }
 
+// staging state of a sampler, made at the first use
+int hostrows_init(nd_sampler *s) {
+  if (s->hostrows) return ND_OK;
+  s->hostrows = new NdHostRows();   // a creation that fails half way is taken down again, so the next call starts over
+  NdHostRows *h = s->hostrows;
+  const size_t S1 = (size_t)(s->S > 0 ? s->S : 1);
+  h->n_chunks = (int)((S1 + PACK_ROWS - 1) / PACK_ROWS);
+  h->threads = host_threads();
+  cudaError_t e = cudaMallocHost(&h->h_len, sizeof(int32_t) * S1);
+  if (e == cudaSuccess) e = cudaMallocHost(&h->h_total, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(&h->d_chunk, sizeof(uint32_t) * ((size_t)h->n_chunks + 1));
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->packed, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->len_done, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->vals_done, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->total_done, cudaEventDisableTiming);
+  if (e != cudaSuccess) {
+    nd_hostrows_free(s);
+    nd_set_error("staging buffers of the packed result: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return ND_ERR_CUDA;
+  }
+  return ND_OK;
+}
+
+// the rows' prefixes packed into the staging array of the walk (free between two passes), on the sampler's stream
+int pack_enqueue(nd_sampler *s) {
+  NdHostRows *h = s->hostrows;
+  pack_sum_kernel<<<h->n_chunks, PACK_THREADS, 0, s->stream>>>(s->d_plen, s->S, h->d_chunk);
+  pack_scan_kernel<<<1, 1024, 0, s->stream>>>(h->d_chunk, h->n_chunks);
+  pack_rows_kernel<<<h->n_chunks, PACK_THREADS, 0, s->stream>>>(s->d_plen, s->d_out, s->S, s->fs, h->d_chunk, s->d_tmp);
+  nd_count_launches(3);
+  ND_CUDA(cudaGetLastError());
+  return ND_OK;
+}
+
 }  // namespace
+
+void nd_hostrows_free(nd_sampler *s);
 
 void nd_hostrows_free(nd_sampler *s) {
   NdHostRows *h = s->hostrows;
@@ -142,6 +220,8 @@ void nd_hostrows_free(nd_sampler *s) {
   if (h->packed) cudaEventDestroy(h->packed);
   if (h->len_done) cudaEventDestroy(h->len_done);
   if (h->vals_done) cudaEventDestroy(h->vals_done);
+  if (h->total_done) cudaEventDestroy(h->total_done);
+  if (h->h_total) cudaFreeHost(h->h_total);
   delete h;
   s->hostrows = nullptr;
 }
@@ -162,24 +242,7 @@ int nd_sampler_host_update_begin(nd_sampler *s, int32_t *out, int32_t *row_len, 
   ND_REQUIRE(nd_is_walk(s->p.app), ND_ERR_ARG, "host row updates exist for the walk apps (their rows are prefixes)");
   ND_REQUIRE(s->sampled, ND_ERR_STATE, "host update requested before sample()");
   ND_CUDA(cudaSetDevice(s->g->device));
-  if (!s->hostrows) {
-    s->hostrows = new NdHostRows();   // a creation that fails half way is taken down again, so the next call starts over
-    NdHostRows *h = s->hostrows;
-    const size_t S1 = (size_t)(s->S > 0 ? s->S : 1);
-    h->n_chunks = (int)((S1 + PACK_ROWS - 1) / PACK_ROWS);
-    h->threads = host_threads();
-    cudaError_t e = cudaMallocHost(&h->h_len, sizeof(int32_t) * S1);
-    if (e == cudaSuccess) e = cudaMalloc(&h->d_chunk, sizeof(uint32_t) * (size_t)h->n_chunks);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->packed, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->len_done, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->vals_done, cudaEventDisableTiming);
-    if (e != cudaSuccess) {
-      nd_hostrows_free(s);
-      nd_set_error("nd_sampler_host_update_begin: staging buffers: %s", cudaGetErrorString(e));
-      cudaGetLastError();
-      return ND_ERR_CUDA;
-    }
-  }
+  ND_TRY(hostrows_init(s));
   NdHostRows *h = s->hostrows;
   ND_REQUIRE(h->stage == 0, ND_ERR_STATE, "the previous host update of this sampler was not finished");
   h->out = out;
@@ -187,12 +250,7 @@ int nd_sampler_host_update_begin(nd_sampler *s, int32_t *out, int32_t *row_len, 
   h->cs = copy_stream ? (cudaStream_t)copy_stream : s->stream;
   if (s->S == 0) { h->stage = 1; return ND_OK; }
   // (an error below leaves stage 0: nothing was begun as far as the caller is concerned)
-  // the rows' prefixes packed into the staging array of the walk (free between two passes)
-  pack_sum_kernel<<<h->n_chunks, PACK_THREADS, 0, s->stream>>>(s->d_plen, s->S, h->d_chunk);
-  pack_scan_kernel<<<1, 1024, 0, s->stream>>>(h->d_chunk, h->n_chunks);
-  pack_rows_kernel<<<h->n_chunks, PACK_THREADS, 0, s->stream>>>(s->d_plen, s->d_out, s->S, s->fs, h->d_chunk, s->d_tmp);
-  nd_count_launches(3);
-  ND_CUDA(cudaGetLastError());
+  if (packable(s)) ND_TRY(pack_enqueue(s));   // (larger arrays take the dense copy in fetch)
   if (h->cs != s->stream) {
     ND_CUDA(cudaEventRecord(h->packed, s->stream));
     ND_CUDA(cudaStreamWaitEvent(h->cs, h->packed, 0));
@@ -225,7 +283,7 @@ int nd_sampler_host_update_fetch(nd_sampler *s) {
     part[(size_t)t] = sum;
   });
   for (int64_t v : part) h->total += v;
-  h->dense = 2 * h->total > s->S * (int64_t)s->fs;
+  h->dense = 2 * h->total > s->S * (int64_t)s->fs || !packable(s);
   if (h->dense) {
     ND_CUDA(cudaMemcpyAsync(h->out, s->d_out, sizeof(int32_t) * (size_t)s->S * s->fs, cudaMemcpyDeviceToHost, h->cs));
   } else if (h->total > 0) {
@@ -285,6 +343,55 @@ int nd_sampler_host_update_finish(nd_sampler *s, int64_t *values_copied) {
       if (now != had) row_len[i] = now;
     }
   });
+  return ND_OK;
+}
+
+// ---- the same packing between GPUs: the sender packs, the receiver unpacks into its dense array
+
+int nd_sampler_pack_rows(nd_sampler *s, const int32_t **d_row_len, const int32_t **d_vals) {
+  ND_REQUIRE(s && d_row_len && d_vals, ND_ERR_ARG, "nd_sampler_pack_rows: null argument");
+  ND_REQUIRE(nd_is_walk(s->p.app), ND_ERR_ARG, "packed rows exist for the walk apps (their rows are prefixes)");
+  ND_REQUIRE(s->sampled, ND_ERR_STATE, "packed rows requested before sample()");
+  ND_REQUIRE(packable(s), ND_ERR_RANGE, "result array too large for 32-bit positions in the packed form");
+  ND_CUDA(cudaSetDevice(s->g->device));
+  ND_TRY(hostrows_init(s));
+  NdHostRows *h = s->hostrows;
+  ND_REQUIRE(h->stage == 0, ND_ERR_STATE, "a host update of this sampler is using the staging array");
+  *d_row_len = s->d_plen;
+  *d_vals = s->d_tmp;
+  *h->h_total = 0;
+  if (s->S > 0) {
+    ND_TRY(pack_enqueue(s));
+    ND_CUDA(cudaMemcpyAsync(h->h_total, h->d_chunk + h->n_chunks, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream));
+  }
+  ND_CUDA(cudaEventRecord(h->total_done, s->stream));
+  return ND_OK;
+}
+
+int nd_sampler_pack_rows_total(nd_sampler *s, int64_t *total) {
+  ND_REQUIRE(s && total && s->hostrows && s->hostrows->total_done, ND_ERR_STATE, "nd_sampler_pack_rows_total before nd_sampler_pack_rows");
+  ND_CUDA(cudaSetDevice(s->g->device));
+  ND_CUDA(cudaEventSynchronize(s->hostrows->total_done));
+  *total = (int64_t)*s->hostrows->h_total;
+  return ND_OK;
+}
+
+int64_t nd_rows_scratch_words(int64_t n_rows) { return (n_rows + PACK_ROWS - 1) / PACK_ROWS + 1; }
+
+int nd_rows_unpack(int device, void *stream, int64_t n_rows, int steps, int32_t invalid, const int32_t *d_len,
+                   const int32_t *d_vals, int32_t *d_out, int32_t *d_row_len, uint32_t *d_scratch) {
+  ND_REQUIRE(n_rows >= 0 && steps >= 1, ND_ERR_ARG, "nd_rows_unpack: bad size");
+  if (n_rows == 0) return ND_OK;
+  ND_REQUIRE(d_len && d_out && d_row_len && d_scratch, ND_ERR_ARG, "nd_rows_unpack: null argument");
+  ND_REQUIRE(n_rows * (int64_t)steps < ((int64_t)1 << 32), ND_ERR_RANGE, "nd_rows_unpack: array too large for 32-bit positions");
+  ND_CUDA(cudaSetDevice(device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n_chunks = (int)((n_rows + PACK_ROWS - 1) / PACK_ROWS);
+  pack_sum_kernel<<<n_chunks, PACK_THREADS, 0, st>>>(d_len, n_rows, d_scratch);
+  pack_scan_kernel<<<1, 1024, 0, st>>>(d_scratch, n_chunks);
+  unpack_rows_kernel<<<n_chunks, PACK_THREADS, 0, st>>>(d_len, d_vals, d_scratch, n_rows, steps, invalid, d_out, d_row_len);
+  nd_count_launches(3);
+  ND_CUDA(cudaGetLastError());
   return ND_OK;
 }
 

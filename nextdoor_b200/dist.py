@@ -128,3 +128,107 @@ def gather_samples_to(local: torch.Tensor, total: int, dst: int = 0, group=None,
     for w in gather_samples_start(local.contiguous(), total, full, dst, group, bounds):
         w.wait()
     return full
+
+
+class PackedRowsGather:
+    """The result of a sharded WALK job on rank `dst`, moved by row prefixes.
+
+    getFinalSamples concatenates the devices' dense arrays (src/nextdoor.cu:3211-3237); for walks
+    that end early almost every slot of those arrays is the invalid id.  Here every rank packs its
+    rows' valid prefixes (nd_sampler_pack_rows), sends the row lengths and the packed vertices, and
+    `dst` writes them into ITS dense [total, fs] array (nd_rows_unpack), which it keeps from job to
+    job with a per-row length, so that a job rewrites only the slots a walk fills now or filled in
+    the previous job.  `full` on `dst` ends up equal to the concatenation of the dense shards.
+
+    Per job: h = start(sampler) right after sampler.sample(sync=False); later finish(h) -- it waits
+    on the host for that sampler's packing only, so another sampler's job can be running on the
+    device meanwhile -- and returns when `full` holds the job (the calling thread's current stream
+    is synchronised) and the sampler may be run again."""
+
+    def __init__(self, total: int, fs: int, invalid: int, dst: int = 0, group=None, bounds=None, device=None):
+        self.group, self.dst, self.total, self.fs, self.invalid = group, dst, int(total), int(fs), int(invalid)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.ranges = [shard(self.total, r, self.world, bounds) for r in range(self.world)]
+        self._comm_cpu = dist.get_backend(group) == "gloo"
+        self.full = self.full_len = None
+        self.values_moved = 0            # vertices of the last finished job, all ranks together
+        if self.rank == dst:
+            self.full = torch.full((self.total, self.fs), self.invalid, dtype=torch.int32, device=self.device)
+            self.full_len = torch.zeros(self.total, dtype=torch.int32, device=self.device)
+            longest = max(c for _, c in self.ranges)
+            self._scratch = torch.empty(api.rows_scratch_words(longest), dtype=torch.int32, device=self.device)
+            self._lens = {r: torch.empty(c, dtype=torch.int32, device=self.device)
+                          for r, (_, c) in enumerate(self.ranges) if r != dst}
+            self._vals = {r: torch.empty(0, dtype=torch.int32, device=self.device) for r in self._lens}
+
+    def start(self, sampler: "api.Sampler"):
+        assert sampler.S == self.ranges[self.rank][1], "the sampler does not hold this rank's seed range"
+        len_ptr, vals_ptr = sampler.pack_rows()
+        return sampler, len_ptr, vals_ptr
+
+    def _view(self, ptr, n):
+        return torch.as_tensor(_DevicePtr(ptr, (n,)), device=self.device) if n > 0 else torch.empty(0, dtype=torch.int32, device=self.device)
+
+    def _unpack(self, r, len_ptr, vals_ptr):
+        f, c = self.ranges[r]
+        if c == 0:
+            return
+        api.rows_unpack(self.device.index, torch.cuda.current_stream(self.device).cuda_stream, c, self.fs, self.invalid,
+                        len_ptr, vals_ptr, self.full[f:f + c].data_ptr(), self.full_len[f:f + c].data_ptr(),
+                        self._scratch.data_ptr())
+
+    def finish(self, handle):
+        sampler, len_ptr, vals_ptr = handle
+        n = sampler.pack_rows_total()
+        mine = torch.tensor([n], dtype=torch.int64, device="cpu" if self._comm_cpu else self.device)
+        totals = torch.empty(self.world, dtype=torch.int64, device=mine.device)
+        dist.all_gather_into_tensor(totals, mine, group=self.group)
+        totals = totals.tolist()
+        self.values_moved = int(sum(totals))
+        count = self.ranges[self.rank][1]
+        if self.rank != self.dst:
+            if count > 0:
+                lens, vals = self._view(len_ptr, count), self._view(vals_ptr, n)
+                if self._comm_cpu:
+                    dist.send(lens.cpu(), self.dst, group=self.group)
+                    if n > 0:
+                        dist.send(vals.cpu(), self.dst, group=self.group)
+                else:
+                    ops = [dist.P2POp(dist.isend, lens, self.dst, self.group)]
+                    if n > 0:
+                        ops.append(dist.P2POp(dist.isend, vals, self.dst, self.group))
+                    for w in dist.batch_isend_irecv(ops):
+                        w.wait()
+        else:
+            for r in self._lens:                                   # room for the incoming vertices
+                if totals[r] > self._vals[r].shape[0]:
+                    self._vals[r] = torch.empty(int(totals[r]) + int(totals[r]) // 4 + 1024, dtype=torch.int32, device=self.device)
+            if self._comm_cpu:
+                for r, lens in self._lens.items():
+                    if lens.shape[0] == 0:
+                        continue
+                    buf = torch.empty(lens.shape[0], dtype=torch.int32)
+                    dist.recv(buf, r, group=self.group)
+                    lens.copy_(buf)
+                    if totals[r] > 0:
+                        buf = torch.empty(int(totals[r]), dtype=torch.int32)
+                        dist.recv(buf, r, group=self.group)
+                        self._vals[r][:totals[r]].copy_(buf)
+            else:
+                ops = []
+                for r, lens in self._lens.items():
+                    if lens.shape[0] == 0:
+                        continue
+                    ops.append(dist.P2POp(dist.irecv, lens, r, self.group))
+                    if totals[r] > 0:
+                        ops.append(dist.P2POp(dist.irecv, self._vals[r][:totals[r]], r, self.group))
+                works = dist.batch_isend_irecv(ops) if ops else []
+                self._unpack(self.dst, len_ptr, vals_ptr)          # this rank's own rows meanwhile
+                for w in works:
+                    w.wait()
+            if self._comm_cpu:
+                self._unpack(self.dst, len_ptr, vals_ptr)
+            for r, lens in self._lens.items():
+                self._unpack(r, lens.data_ptr(), self._vals[r].data_ptr())
+        torch.cuda.current_stream(self.device).synchronize()
