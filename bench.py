@@ -246,6 +246,39 @@ def cpu_baseline(hg, wl, seed, budget_s=12.0):
             "sample": f"first {n} of {S_all} samples, {t:.2f} s", "seconds": t}
 
 
+def emulated_shards(a, wl, nd, torch, local, seed):
+    """--emulate-shards N on ONE GPU: the job is cut into the N seed ranges `--gpus N` would give
+    the ranks, and every range is timed by itself, one after the other, on this GPU.  The slowest
+    range is what the N-GPU job's device time (max over ranks) comes to, short of the barrier: at
+    N = 2 and 4 the figure is within 3 % of the real runs.  Prints its own JSON line."""
+    from nextdoor_b200 import dist as nd_dist
+    V, S_total, N = wl["V"], wl.get("S", wl["V"]), a.emulate_shards
+    mode = MODES[a.mode]
+    g = nd.Graph.rmat(V, wl["M"], seed, device=local)
+    pr = params_for(nd, wl, seed)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    bounds = None
+    if wl["kind"] == WALK and a.shard_cut == "balanced":
+        all_init = torch.from_numpy(seeds_for(wl, 0, S_total)).cuda()
+        bounds = nd_dist.balanced_bounds(nd_dist.walk_start_weights(g, all_init), N)
+        del all_init
+    rows, edges = [], 0
+    for r in range(N):
+        first, S = nd_dist.shard(S_total, r, N, bounds)
+        smp = nd.Sampler(g, pr, num_samples=S, first_sample=first, initial=seeds_for(wl, first, S))
+        smp.set_stream(stream.cuda_stream)
+        ms = timed_passes(torch, stream, torch.cuda.synchronize, lambda: smp.sample(mode, sync=False), a.steps, a.warmup) / a.steps
+        e = smp.stats()["sampled_edges"]
+        edges += e
+        rows.append({"rank": r, "first_sample": first, "samples": S, "ms_per_step": round(ms, 4), "sampled_edges": e})
+        smp.free()
+    worst = max(x["ms_per_step"] for x in rows)
+    print(json.dumps({"emulated_shards": N, "workload": f"{a.workload}: {wl['desc']}", "mode": a.mode, "shard_cut": a.shard_cut if bounds else "equal",
+                      "steps": a.steps, "warmup": a.warmup, "slowest_shard_ms": worst, "value_at_slowest_shard": edges / (worst * 1e-3),
+                      "unit": "sampled edges/s", "note": "every shard timed alone on one GPU; not a multi-GPU measurement", "shards": rows}))
+
+
 def partitioned_bench(a, wl, nd, torch, rank, world, local, seed):
     """Strong-scaling figure of the partitioned path: the workload's walks over a graph whose rows
     are split across the ranks (each GPU holds 1/N of the CSR entries), walkers routed by
@@ -469,6 +502,8 @@ def main():
     ap.add_argument("--shard-cut", default="balanced", choices=["balanced", "equal"],
                     help="N > 1, walk workloads: cut the job's seed range where the ranks' expected work is equal "
                          "(nextdoor_b200.dist.balanced_bounds) or into the reference's equal counts (src/utils.hpp:26-27)")
+    ap.add_argument("--emulate-shards", type=int, default=0,
+                    help="one GPU: time each of the N seed ranges an N-GPU run would use, one after the other; prints the slowest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side", action="store_true", help="skip the c2 roofline pass and the reference-GPU leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end and gather legs (kernel A/B runs)")
@@ -502,6 +537,9 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if a.partitioned:
         return partitioned_bench(a, wl, nd, torch, rank, world, local, seed)
+    if a.emulate_shards:
+        assert world == 1, "--emulate-shards runs on one GPU"
+        return emulated_shards(a, wl, nd, torch, local, seed)
     mode = MODES[a.mode]
     g = nd.Graph.rmat(V, M, seed, device=local)
     pr = params_for(nd, wl, seed)
