@@ -339,6 +339,35 @@ def test_host_array_updated_by_row_prefixes(nd, ndo, small_graph):
         k.host_update_begin(out, row_len)                # k-hop rows are not prefixes
 
 
+@pytest.mark.parametrize("S,steps,stop", [(37, 7, 0.5), (4096, 7, 0.3), (8193, 101, 0.02), (1, 3, 0.5)])
+def test_host_array_row_prefixes_odd_sizes(nd, ndo, small_graph, S, steps, stop):
+    """Row lengths that are no multiple of four, fewer rows than one packing chunk, exactly one
+    chunk, one row, long rows: the host array and an unpacked device array follow the sampler."""
+    import torch
+    g = _graph(nd, small_graph)
+    V = small_graph.V
+    pr = nd.app_params(2, steps=steps, seed=2, stop_prob=stop)
+    s = nd.Sampler(g, pr, num_samples=S, first_sample=11)
+    out = np.full(S * steps, V, np.int32)
+    row_len = np.zeros(S, np.int32)
+    full = torch.full((S, steps), V, dtype=torch.int32, device="cuda")
+    full_len = torch.zeros(S, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(nd.rows_scratch_words(S), dtype=torch.int32, device="cuda")
+    rng = np.random.default_rng(S)
+    for p in range(3):
+        s.set_initial(rng.integers(0, V, S).astype(np.int32))
+        s.sample(1)
+        dense = s.final_samples()
+        s.host_update_begin(out, row_len)
+        s.host_update_finish()
+        assert np.array_equal(out.reshape(S, steps), dense), p
+        len_ptr, vals_ptr = s.pack_rows()
+        assert s.pack_rows_total() == int((dense != V).sum())
+        nd.rows_unpack(0, None, S, steps, V, len_ptr, vals_ptr, full.data_ptr(), full_len.data_ptr(), scratch.data_ptr())
+        torch.cuda.synchronize()
+        assert np.array_equal(full.cpu().numpy(), dense), p
+
+
 def test_pipelined_jobs_into_remembered_host_arrays(nd, ndo, small_graph):
     """PipelinedSampler(sparse_rows=True): jobs with changing seeds alternate between two host
     arrays without waiting in between; each array must hold its own job's dense result."""
