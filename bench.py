@@ -136,6 +136,7 @@ def next_bytes(wl, st, mode):
     app = wl["app"]
     if wl["kind"] == WALK:
         steps = wl["steps"]
+        pairs -= st.get("pairs_not_entered", 0)   # PPR, load-balanced mode: pairs that were never written to or read from a map
         b = 8 * pairs + 8 * edges
         if mode != 2:
             b += 8 * pairs + 8 * pairs * (steps - 1) / steps

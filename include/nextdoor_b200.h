@@ -182,7 +182,9 @@ int nd_sampler_aux(nd_sampler *s, int32_t *adj_row, int32_t *adj_col, float *pro
 /* counters of the last sample(): [0] sampled edges (valid vertices written), [1] live
  * (transit,sample) pairs summed over steps, [2] weight reads of the rejection loops, [3] node2vec
  * tries, [4] node2vec binary-search probes, [5] neighbour ids gathered for collective unions,
- * [6] unique candidates; n <= 8 */
+ * [6] unique candidates, [7] PPR in the load-balanced mode: pairs counted in [1] that never entered a
+ * map because their walk was known to stop at that step (its stop draw does not depend on the vertex);
+ * n <= 8 */
 int nd_sampler_stats(nd_sampler *s, int64_t *stats, int n);
 /* walks in a transit-parallel mode: live[k] = (transit, sample) pairs that entered step k of the last
  * sample(), i.e. the size of the step's map (the reference prints the same as "totalThreads" per

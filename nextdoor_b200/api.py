@@ -249,10 +249,12 @@ class Sampler:
         st = np.zeros(8, np.int64)
         check(lib.nd_sampler_stats(self._h, _ptr(st), 8))
         return dict(sampled_edges=int(st[0]), live_pairs=int(st[1]), weight_tries=int(st[2]),
-                    n2v_tries=int(st[3]), n2v_probes=int(st[4]), union_ids=int(st[5]), union_unique=int(st[6]))
+                    n2v_tries=int(st[3]), n2v_probes=int(st[4]), union_ids=int(st[5]), union_unique=int(st[6]),
+                    pairs_not_entered=int(st[7]))
 
     def live_pairs(self):
-        """Walks, transit-parallel modes: pairs that entered each step of the last sample()."""
+        """Walks, transit-parallel modes: pairs in the map of each step of the last sample() (PPR in
+        the load-balanced mode leaves out pairs whose walk is known to stop at that step)."""
         live = np.zeros(self.params.steps, np.int32)
         check(lib.nd_sampler_live_pairs(self._h, _ptr(live), live.shape[0]))
         return live

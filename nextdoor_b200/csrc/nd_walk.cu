@@ -31,6 +31,7 @@ struct WalkParams {
   int steps;
   const int32_t *adjset;  // node2vec: per-vertex hash sets of the neighbour ids
   const int2 *colw;       // DeepWalk / PPR: (neighbour id, weight bits) records
+  int keep_all_step = -1; // PPR, load-balanced loop: the step whose map goes to the tail launch keeps every pair (see walk_next_count_kernel)
 };
 
 // node2vec asks "is v a neighbour of the previous vertex t?" for its candidates, and t is usually a
@@ -58,18 +59,46 @@ constexpr int RETRY_CAP = 1 << 16;
 // flushed once per warp when the kernel ends
 struct Events {
   uint32_t weight_tries = 0, n2v_tries = 0, n2v_probes = 0;
+  uint32_t not_entered = 0;  // PPR: pairs left out of the next map because the walk is known to stop there (stats[7])
   __device__ __forceinline__ void flush(unsigned long long *stats) {
-    uint32_t a = weight_tries, b = n2v_tries, c = n2v_probes;
+    uint32_t a = weight_tries, b = n2v_tries, c = n2v_probes, d = not_entered;
     for (int o = 16; o > 0; o >>= 1) {
       a += __shfl_xor_sync(0xffffffffu, a, o);
       b += __shfl_xor_sync(0xffffffffu, b, o);
       c += __shfl_xor_sync(0xffffffffu, c, o);
+      d += __shfl_xor_sync(0xffffffffu, d, o);
     }
     if ((threadIdx.x & 31) == 0) {
       if (a) atomicAdd(&stats[2], (unsigned long long)a);
       if (b) atomicAdd(&stats[3], (unsigned long long)b);
       if (c) atomicAdd(&stats[4], (unsigned long long)c);
+      if (d) atomicAdd(&stats[7], (unsigned long long)d);
     }
+  }
+  // The same for a kernel whose CTAs are short-lived (a tile each): the warps' sums meet in shared
+  // memory and the CTA adds them once -- with one atomic per warp the half a million warps of a large
+  // step queue up on the four counters (measured: 0.4 ms per pass and counter on the 2^24-vertex job).
+  // Every thread of the CTA must call it.
+  __device__ __forceinline__ void flush_cta(unsigned long long *stats) {
+    __shared__ uint32_t sums[4];
+    uint32_t a = weight_tries, b = n2v_tries, c = n2v_probes, d = not_entered;
+    for (int o = 16; o > 0; o >>= 1) {
+      a += __shfl_xor_sync(0xffffffffu, a, o);
+      b += __shfl_xor_sync(0xffffffffu, b, o);
+      c += __shfl_xor_sync(0xffffffffu, c, o);
+      d += __shfl_xor_sync(0xffffffffu, d, o);
+    }
+    __syncthreads();
+    if (threadIdx.x < 4) sums[threadIdx.x] = 0u;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+      if (a) atomicAdd(&sums[0], a);
+      if (b) atomicAdd(&sums[1], b);
+      if (c) atomicAdd(&sums[2], c);
+      if (d) atomicAdd(&sums[3], d);
+    }
+    __syncthreads();
+    if (threadIdx.x < 4 && sums[threadIdx.x]) atomicAdd(&stats[threadIdx.x < 3 ? 2 + threadIdx.x : 7], (unsigned long long)sums[threadIdx.x]);
   }
 };
 
@@ -538,11 +567,14 @@ __device__ __forceinline__ void count_emit(const ndmem::Keep &keep, int i, int32
                                            int32_t *__restrict__ out_val, int32_t *__restrict__ out_rank,
                                            uint32_t *__restrict__ cnt, uint32_t *__restrict__ bsum,
                                            int32_t *__restrict__ tmp_step, int32_t *__restrict__ len,
-                                           int4 *__restrict__ out_ext, int32_t t, int32_t rs, int32_t deg) {
+                                           int4 *__restrict__ out_ext, int32_t t, int32_t rs, int32_t deg,
+                                           bool ends_next = false) {  // the walk takes this vertex and is known to stop at the next step
   if (nbr >= 0) keep.st(tmp_step + s, nbr); else len[s] = step;
+  if (ends_next) len[s] = step + 1;
   if (COUNT) {
-    keep.st(out_key + i, nbr >= 0 ? nbr : V);
-    if (nbr >= 0) {
+    const bool in_map = nbr >= 0 && !ends_next;
+    keep.st(out_key + i, in_map ? nbr : V);
+    if (in_map) {
       keep.st(out_val + i, s);
       keep.st(out_rank + i, (int32_t)keep.atom_add(cnt + nbr, 1u));
       if (out_ext) keep.st(out_ext + i, make_int4(t, rs, deg, 0));  // node2vec: this transit is the pair's previous vertex next step
@@ -757,9 +789,22 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
     // ---- settled pairs are written, the others queued
 #pragma unroll
     for (int k = 0; k < PPT; k++)
-      if (live[k] && settled[k])
+      if (live[k] && settled[k]) {
+        // PPR: whether a walk stops at a step is the first draw of that step's keyed sequence and does
+        // not depend on where the walk stands, so the next step's verdict is known now: a pair that
+        // would only enter the next map to be dropped from it takes no ticket and is not scattered.
+        // (Not in the step that feeds the tail launch: the result update that runs beside the tail
+        // tells the tail's walks from the others by their length, and a walk ended here would have
+        // the length of one that the tail is about to continue.)
+        bool ends_next = false;
+        if (APP == ND_APP_PPR && COUNT && nbr[k] >= 0 && step != wp.keep_all_step) {
+          Rng ahead(wp.seed, (uint32_t)(first_sample + s[k]), (uint32_t)(step + 1), 0u);
+          ends_next = ahead.uniform() < wp.stop_prob;
+          ev.not_entered += ends_next ? 1u : 0u;
+        }
         count_emit<COUNT>(keep, idx[k], s[k], nbr[k], g.V, step, smem_bins, sh_bins, out_key, out_val, out_rank, cnt, bsum, tmp_step, len,
-                          out_ext, t[k], rs[k], deg[k]);
+                          out_ext, t[k], rs[k], deg[k], ends_next);
+      }
     if (APP != ND_APP_UNIFORM_WALK) {
 #pragma unroll
       for (int k = 0; k < PPT; k++) {
@@ -780,7 +825,7 @@ walk_next_count_kernel(NdGraphView g, WalkParams wp, int step, int64_t first_sam
       if (cb) atomicAdd(&bsum[b], cb);
     }
   }
-  if (APP != ND_APP_UNIFORM_WALK) ev.flush(stats);
+  if (APP != ND_APP_UNIFORM_WALK) ev.flush_cta(stats);
 }
 
 template <bool COUNT>
@@ -1739,6 +1784,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
       while (k < steps && alive * (double)S > floor_pairs) { alive *= 1.0 - (double)s->p.stop_prob; k++; }
       tp_steps = k < 1 ? 1 : k;
     }
+    wp.keep_all_step = tp_steps < steps ? tp_steps - 1 : -1;
     int cur = 0;  // sorted map the scatter of this step writes
     for (int step = 0; step < tp_steps; step++) {
       const bool last = step == steps - 1;
