@@ -424,7 +424,9 @@ def roofline_of(nd, smp, wl, workload, mode_name, mode, ms_per_step, hbm_peak, p
     # the timed steps replay a CUDA graph, the instrumented pass does not: the same launches, scaled
     # by their share of the instrumented pass, inside the replayed step
     replay_ms = ms_per_step * (next_ms - tail_ms) / phase_sum if phase_sum > 0 and ms_per_step else None
-    pairs_per_launch = st["live_pairs"] / max(next_launches, 1) if wl["kind"] == WALK else None
+    pairs_per_launch = None
+    if wl["kind"] == WALK:      # pairs in the maps the step launches read (the tail launch and its pairs are not among them)
+        pairs_per_launch = (float(smp.live_pairs()[:next_launches].sum()) if mode != 2 else float(st["live_pairs"])) / max(next_launches, 1)
     traffic, traffic_src = ncu_traffic(workload, mode_name, pairs_per_launch)
     gather = None
     if wl["kind"] == WALK and with_gather_probe:
