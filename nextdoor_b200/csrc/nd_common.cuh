@@ -73,6 +73,7 @@ struct nd_graph {
   float *max_w = nullptr;
   // Derived layouts, built on the first sampler that needs them and shared by all samplers of the graph:
   mutable int2 *colw = nullptr;        // [E] (neighbour id, weight bits) records: one 8-byte gather per weighted try
+  mutable int2 *vrec = nullptr;        // [V+1] (row start, max weight bits) per vertex: what a thread-per-walk kernel needs of a vertex in one sector
   mutable int32_t *adjset = nullptr;   // node2vec membership: per-vertex hash sets of the neighbour ids, 8-slot buckets
 };
 

@@ -480,7 +480,7 @@ int nd_graph_destroy(nd_graph *g) {
   if (!g) return ND_OK;
   cudaSetDevice(g->device);
   cudaFree(g->row_ptr); cudaFree(g->col); cudaFree(g->w); cudaFree(g->max_w);
-  cudaFree(g->colw); cudaFree(g->adjset);
+  cudaFree(g->colw); cudaFree(g->vrec); cudaFree(g->adjset);
   delete g;
   return ND_OK;
 }

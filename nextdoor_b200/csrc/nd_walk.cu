@@ -31,6 +31,7 @@ struct WalkParams {
   int steps;
   const int32_t *adjset;  // node2vec: per-vertex hash sets of the neighbour ids
   const int2 *colw;       // DeepWalk / PPR: (neighbour id, weight bits) records
+  const int2 *vrec = nullptr;  // DeepWalk / PPR: (row start, max weight bits) per vertex, V + 1 entries
   int keep_all_step = -1; // PPR, load-balanced loop: the step whose map goes to the tail launch keeps every pair (see walk_next_count_kernel)
 };
 
@@ -336,6 +337,12 @@ __global__ void colw_build_kernel(const int32_t *__restrict__ col, const float *
                                   int2 *__restrict__ colw) {
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x)
     colw[e] = make_int2(col[e], __float_as_int(w[e]));
+}
+
+__global__ void vrec_build_kernel(const int32_t *__restrict__ row_ptr, const float *__restrict__ max_w, int32_t V,
+                                  int2 *__restrict__ vrec) {
+  for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v <= V; v += (int64_t)gridDim.x * blockDim.x)
+    vrec[v] = make_int2(row_ptr[v], v < V ? __float_as_int(max_w[v]) : 0);
 }
 
 __global__ void walk_reset_kernel(const int32_t *__restrict__ initial, int32_t V, int64_t S, int steps,
@@ -1000,6 +1007,16 @@ pack_map_kernel(const int32_t *__restrict__ d_n, const int32_t *__restrict__ key
   }
 }
 
+// Row start, degree and maximum weight of a vertex for a kernel that reaches it by a random id: the
+// two neighbouring 8-byte records share a 32-byte sector three times out of four, where the row
+// offsets and the maximum weights are two arrays and two sectors.
+__device__ __forceinline__ void vertex_of(const WalkParams &wp, int32_t v, int32_t &rs, int32_t &deg, float &max_w) {
+  const int2 a = __ldg(wp.vrec + v), b = __ldg(wp.vrec + v + 1);
+  rs = a.x;
+  deg = b.x - rs;
+  max_w = __int_as_float(a.y);
+}
+
 // The tail of a job whose walks end early (PPR): once few walks are still alive, a step of the
 // transit-parallel loop is three launches whose fixed cost outweighs the per-pair work.  From
 // there on one launch finishes the job, a lane per walk: a lane takes a pair of the sorted map
@@ -1051,9 +1068,7 @@ walk_tail_kernel(NdGraphView g, WalkParams wp, int first_step, int64_t first_sam
           have = true;
           fresh = true;
           if (cur >= 0 && cur < g.V) {
-            rs = __ldg(g.row_ptr + cur);
-            deg = __ldg(g.row_ptr + cur + 1) - rs;
-            max_w = __ldg(g.max_w + cur);
+            vertex_of(wp, cur, rs, deg, max_w);
           } else {
             deg = 0;
           }
@@ -1091,9 +1106,7 @@ walk_tail_kernel(NdGraphView g, WalkParams wp, int first_step, int64_t first_sam
         else tmp[(int64_t)step * S + s] = nbr;
         cur = nbr;
         if (++step < wp.steps) {
-          rs = __ldg(g.row_ptr + cur);
-          deg = __ldg(g.row_ptr + cur + 1) - rs;
-          max_w = __ldg(g.max_w + cur);
+          vertex_of(wp, cur, rs, deg, max_w);
           fresh = true;
         }
       }
@@ -1188,9 +1201,12 @@ walk_sp_rounds_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_
       } else {
         cur = initial[s];
         if (cur >= 0 && cur < g.V) {  // otherwise len is -1 already and the lane tries the next walk in the next trip
-          rs = __ldg(g.row_ptr + cur);
-          deg = __ldg(g.row_ptr + cur + 1) - rs;
-          if (!N2V) max_w = __ldg(g.max_w + cur);
+          if (N2V) {
+            rs = __ldg(g.row_ptr + cur);
+            deg = __ldg(g.row_ptr + cur + 1) - rs;
+          } else {
+            vertex_of(wp, cur, rs, deg, max_w);
+          }
           step = 0;
           have = true;
           fresh = true;
@@ -1229,9 +1245,12 @@ walk_sp_rounds_kernel(NdGraphView g, WalkParams wp, int64_t first_sample, int64_
         if (++step == wp.steps) {
           have = false;
         } else {
-          rs = __ldg(g.row_ptr + cur);
-          deg = __ldg(g.row_ptr + cur + 1) - rs;
-          if (!N2V) max_w = __ldg(g.max_w + cur);
+          if (N2V) {
+            rs = __ldg(g.row_ptr + cur);
+            deg = __ldg(g.row_ptr + cur + 1) - rs;
+          } else {
+            vertex_of(wp, cur, rs, deg, max_w);
+          }
           fresh = true;
         }
       }  // ROUND_AGAIN: the lane stays on its step
@@ -1503,10 +1522,18 @@ static std::mutex g_derived_mutex;
 int nd_graph_ensure_colw(const nd_graph *g, int sms) {
   std::lock_guard<std::mutex> lock(g_derived_mutex);
   if (g->colw || g->E == 0) return ND_OK;
-  int2 *cw = nullptr;
+  int2 *cw = nullptr, *vr = nullptr;
   ND_CUDA(cudaMalloc(&cw, sizeof(int2) * (size_t)g->E));
+  if (cudaMalloc(&vr, sizeof(int2) * ((size_t)g->V + 1)) != cudaSuccess) {
+    cudaFree(cw);
+    nd_set_error("per-vertex records: out of device memory");
+    cudaGetLastError();
+    return ND_ERR_CUDA;
+  }
   colw_build_kernel<<<sms * 16, 256>>>(g->col, g->w, g->E, cw);
+  vrec_build_kernel<<<sms * 16, 256>>>(g->row_ptr, g->max_w, g->V, vr);
   ND_CUDA(cudaDeviceSynchronize());
+  g->vrec = vr;
   g->colw = cw;
   return ND_OK;
 }
@@ -1708,7 +1735,7 @@ static int walk_enqueue(nd_sampler *s, int mode) {
   const int steps = s->p.steps;
   const int app = s->p.app;
   cudaStream_t st = s->stream;
-  WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps, s->g->adjset, s->g->colw};
+  WalkParams wp{s->p.seed, s->p.p, s->p.q, s->p.stop_prob, s->p.n2v_ref_compat, steps, s->g->adjset, s->g->colw, s->g->vrec};
   bool tail_direct = false, join = false;   // PPR tail launch: writes the result rows itself / runs on the side stream
   int tail_from = 0x7fffffff;               // first step of that launch
   const int rblocks = (int)((S + 255) / 256);
