@@ -162,13 +162,23 @@ int host_threads() {
   return hc == 0 ? 4 : (hc > 32 ? 32 : (int)hc);
 }
 
-// runs fn(t, first_row, end_row) on `threads` contiguous row ranges
+// runs fn(t, first_row, end_row) on `threads` contiguous row ranges; a range whose thread cannot be
+// started (the process is out of threads) is run by the caller, so nothing escapes the C boundary
 template <class F>
 void for_row_ranges(int64_t S, int threads, F fn) {
   if (threads > S) threads = S > 0 ? (int)S : 1;
   std::vector<std::thread> pool;
-  for (int t = 1; t < threads; t++) pool.emplace_back(fn, t, S * t / threads, S * (t + 1) / threads);
+  pool.reserve((size_t)threads);
+  int started = 1;
+  for (; started < threads; started++) {
+    try {
+      pool.emplace_back(fn, started, S * started / threads, S * (started + 1) / threads);
+    } catch (...) {
+      break;
+    }
+  }
   fn(0, (int64_t)0, S / threads);
+  for (int t = started; t < threads; t++) fn(t, S * t / threads, S * (t + 1) / threads);
   for (auto &th : pool) th.join();
 }
 

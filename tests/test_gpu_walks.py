@@ -340,10 +340,12 @@ def test_host_array_updated_by_row_prefixes(nd, ndo, small_graph):
 
 
 @pytest.mark.parametrize("S,steps,stop", [(37, 7, 0.5), (4096, 7, 0.3), (8193, 101, 0.02), (1, 3, 0.5)])
-def test_host_array_row_prefixes_odd_sizes(nd, ndo, small_graph, S, steps, stop):
+def test_host_array_row_prefixes_odd_sizes(nd, ndo, small_graph, monkeypatch, S, steps, stop):
     """Row lengths that are no multiple of four, fewer rows than one packing chunk, exactly one
-    chunk, one row, long rows: the host array and an unpacked device array follow the sampler."""
+    chunk, one row, long rows, a thread count that does not divide the rows: the host array and an
+    unpacked device array follow the sampler."""
     import torch
+    monkeypatch.setenv("ND_HOST_THREADS", "3" if S > 1 else "5")
     g = _graph(nd, small_graph)
     V = small_graph.V
     pr = nd.app_params(2, steps=steps, seed=2, stop_prob=stop)
