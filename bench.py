@@ -247,6 +247,10 @@ def cpu_baseline(hg, wl, seed, budget_s=12.0):
             "sample": f"first {n} of {S_all} samples, {t:.2f} s", "seconds": t}
 
 
+def idle_kw(a):
+    return {} if a.idle_weight is None else {"idle": a.idle_weight}
+
+
 def emulated_shards(a, wl, nd, torch, local, seed):
     """--emulate-shards N on ONE GPU: the job is cut into the N seed ranges `--gpus N` would give
     the ranks, and every range is timed by itself, one after the other, on this GPU.  The slowest
@@ -262,7 +266,7 @@ def emulated_shards(a, wl, nd, torch, local, seed):
     bounds = None
     if wl["kind"] == WALK and a.shard_cut == "balanced":
         all_init = torch.from_numpy(seeds_for(wl, 0, S_total)).cuda()
-        bounds = nd_dist.balanced_bounds(nd_dist.walk_start_weights(g, all_init), N)
+        bounds = nd_dist.balanced_bounds(nd_dist.walk_start_weights(g, all_init, **idle_kw(a)), N)
         del all_init
     rows, edges = [], 0
     for r in range(N):
@@ -505,6 +509,8 @@ def main():
     ap.add_argument("--shard-cut", default="balanced", choices=["balanced", "equal"],
                     help="N > 1, walk workloads: cut the job's seed range where the ranks' expected work is equal "
                          "(nextdoor_b200.dist.balanced_bounds) or into the reference's equal counts (src/utils.hpp:26-27)")
+    ap.add_argument("--idle-weight", type=float, default=None,
+                    help="balanced cut: weight of a walk that cannot start (default: nextdoor_b200.dist.IDLE_WALK_WEIGHT)")
     ap.add_argument("--emulate-shards", type=int, default=0,
                     help="one GPU: time each of the N seed ranges an N-GPU run would use, one after the other; prints the slowest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -553,7 +559,7 @@ def main():
     if world > 1 and wl["kind"] == WALK and a.shard_cut == "balanced":
         from nextdoor_b200 import dist as nd_dist
         all_init = torch.from_numpy(seeds_for(wl, 0, S_total)).cuda()
-        bounds = nd_dist.balanced_bounds(nd_dist.walk_start_weights(g, all_init), world)
+        bounds = nd_dist.balanced_bounds(nd_dist.walk_start_weights(g, all_init, **idle_kw(a)), world)
         del all_init
         first, S = nd_dist.shard(S_total, rank, world, bounds)
     else:
@@ -793,7 +799,7 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
             "config": {"workload": f"{a.workload}: {wl['desc']}", "app": APP_NAMES[app], "mode": a.mode,
                        "samples_total": S_total, "samples_rank0": S, "final_sample_size": fs,
-                       "sharding": ("one job, contiguous seed ranges of equal expected work (walks that can start weigh 1, the others 1/7), "
+                       "sharding": ("one job, contiguous seed ranges of equal expected work (walks that can start weigh 1, the others 1/20), "
                                     "graph replicated per GPU" if bounds else
                                     "one job, contiguous seed ranges of equal counts (src/utils.hpp:26-27), graph replicated per GPU"),
                        "shard_bounds": bounds,

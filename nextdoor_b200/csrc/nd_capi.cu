@@ -90,6 +90,8 @@ void free_sampler(nd_sampler *s) {
   if (s->side_fork) cudaEventDestroy(s->side_fork);
   if (s->side_join) cudaEventDestroy(s->side_join);
   if (s->side) cudaStreamDestroy(s->side);
+  if (s->active_done) cudaEventDestroy(s->active_done);
+  if (s->h_active) cudaFreeHost(s->h_active);
   nd_radix_scratch_free(&s->radix);
   for (cudaEvent_t e : s->timer.ev) cudaEventDestroy(e);
   delete s;

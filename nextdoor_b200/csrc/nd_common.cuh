@@ -186,6 +186,11 @@ struct nd_sampler {
   // PPR, load-balanced mode: the tail launch runs on this stream beside the result update of the walks that ended
   cudaStream_t side = nullptr;
   cudaEvent_t side_fork = nullptr, side_join = nullptr;
+  // ... and the number of walks whose start vertex has neighbours, counted when the seeds are set (pinned word + event):
+  // the hand-over to the tail launch is placed by the pairs the maps will really hold
+  int32_t *h_active = nullptr;
+  cudaEvent_t active_done = nullptr;
+  int64_t active_starts = -1;   // -1: not read yet
   cudaEvent_t copy_event = nullptr;  // orders a result copy on another stream after the sampling
   cudaEvent_t copy_done = nullptr;   // ... and the next sampling (which overwrites the result) after that copy
   bool copy_pending = false;

@@ -357,6 +357,18 @@ __global__ void walk_reset_kernel(const int32_t *__restrict__ initial, int32_t V
   if (state) state[s] = 0;
 }
 
+// walks whose start vertex is valid and has neighbours
+__global__ void count_active_kernel(const int32_t *__restrict__ initial, int64_t n, int32_t V,
+                                    const int32_t *__restrict__ row_ptr, int32_t *__restrict__ out) {
+  int c = 0;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t t = initial[i];
+    if (t >= 0 && t < V && row_ptr[t + 1] > row_ptr[t]) c++;
+  }
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0 && c) atomicAdd(out, c);
+}
+
 __global__ void init_map_kernel(const int32_t *__restrict__ initial, int32_t V, int64_t n,
                                 int32_t *__restrict__ keys, int32_t *__restrict__ vals) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -1675,7 +1687,7 @@ int nd_walk_alloc(nd_sampler *s) {
   }
   ND_CUDA(cudaMalloc(&s->d_init_key, sizeof(int32_t) * (size_t)S));
   ND_CUDA(cudaMalloc(&s->d_init_val, sizeof(int32_t) * (size_t)S));
-  ND_CUDA(cudaMalloc(&s->d_nlive, sizeof(int32_t) * (size_t)(steps + 3)));  // live pairs per step, a spare slot, the tail launch's work counter
+  ND_CUDA(cudaMalloc(&s->d_nlive, sizeof(int32_t) * (size_t)(steps + 4)));  // live pairs per step, a spare slot, the tail launch's work counter, walks that can start
   const int key_bits = nd_bit_length((uint32_t)(s->g->V > 1 ? s->g->V - 1 : 1));
   ND_TRY(nd_radix_scratch_alloc(&s->radix, key_bits, S));
   // counting inversion (load-balanced mode)
@@ -1696,6 +1708,9 @@ int nd_walk_alloc(nd_sampler *s) {
     ND_CUDA(cudaStreamCreateWithFlags(&s->side, cudaStreamNonBlocking));
     ND_CUDA(cudaEventCreateWithFlags(&s->side_fork, cudaEventDisableTiming));
     ND_CUDA(cudaEventCreateWithFlags(&s->side_join, cudaEventDisableTiming));
+    ND_CUDA(cudaMallocHost(&s->h_active, sizeof(int32_t)));
+    *s->h_active = -1;
+    ND_CUDA(cudaEventCreateWithFlags(&s->active_done, cudaEventDisableTiming));
   }
   return ND_OK;
 }
@@ -1723,6 +1738,15 @@ int nd_sampler_build_initial_map(nd_sampler *s) {
     const int pg = (int)(blocks < s->dev.sms * 16 ? (blocks > 0 ? blocks : 1) : s->dev.sms * 16);
     if (s->p.app == ND_APP_NODE2VEC) pack_map_kernel<true><<<pg, 256, 0, s->stream>>>(s->d_nlive, s->d_map_key[src], s->d_map_val[src], s->d_init_rec);
     else pack_map_kernel<false><<<pg, 256, 0, s->stream>>>(s->d_nlive, s->d_map_key[src], s->d_map_val[src], s->d_init_rec);
+  }
+  if (s->h_active) {  // PPR: how many walks can start (read when the step loop is laid out, not waited for here)
+    s->active_starts = -1;
+    *s->h_active = -1;
+    int32_t *d_active = s->d_nlive + s->p.steps + 3;
+    ND_CUDA(cudaMemsetAsync(d_active, 0, sizeof(int32_t), s->stream));
+    count_active_kernel<<<s->dev.sms * 4, 256, 0, s->stream>>>(s->d_initial, n, s->g->V, s->g->row_ptr, d_active);
+    ND_CUDA(cudaMemcpyAsync(s->h_active, d_active, sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
+    ND_CUDA(cudaEventRecord(s->active_done, s->stream));
   }
   return ND_OK;  // stream-ordered: no host synchronisation, so chunks on different streams overlap
 }
@@ -1799,17 +1823,22 @@ static int walk_enqueue(nd_sampler *s, int mode) {
     const int64_t sblocks = (S + 256 * SCATTER_PPT - 1) / (256 * SCATTER_PPT);
     const int sgrid = (int)(sblocks < (int64_t)s->dev.sms * 16 ? (sblocks > 0 ? sblocks : 1) : (int64_t)s->dev.sms * 16);
     // PPR: a step of the loop costs about 40 us of launches and of the scan over the per-vertex
-    // counters whatever the number of live pairs, which is what a million pairs cost on top of it.
-    // The loop runs while more than that are expected to be alive (S * (1 - stop probability)^k),
-    // one tail launch finishes the rest (ND_WALK_TAIL_PAIRS moves the hand-over, for tests and A/B runs).
+    // counters whatever the number of pairs, which is what a million pairs cost on top of it.  The
+    // map of step k >= 1 holds the walks that can start and pass the stop draws of steps 1..k
+    // (pairs known to stop are not entered): active * (1 - stop probability)^(k+1).  The loop runs
+    // while that is above a million, one tail launch finishes the rest (ND_WALK_TAIL_PAIRS moves the
+    // hand-over, for tests and A/B runs).  `active` was counted when the seeds were set; the layout
+    // is fixed when the loop is first captured and kept for later seeds.
     int tp_steps = steps;
     if (app == ND_APP_PPR && s->p.stop_prob > 0.f && !getenv("ND_WALK_NO_TAIL")) {
       const char *e = getenv("ND_WALK_TAIL_PAIRS");
       const double floor_pairs = e ? atof(e) : 1048576.0;
-      double alive = 1.0;
-      int k = 0;
-      while (k < steps && alive * (double)S > floor_pairs) { alive *= 1.0 - (double)s->p.stop_prob; k++; }
-      tp_steps = k < 1 ? 1 : k;
+      const double active = s->active_starts >= 0 ? (double)s->active_starts : (double)S;
+      const double keep = 1.0 - (double)s->p.stop_prob;
+      double in_map = active * keep * keep;   // step 1
+      int k = 1;
+      while (k < steps && in_map > floor_pairs) { in_map *= keep; k++; }
+      tp_steps = k;
     }
     wp.keep_all_step = tp_steps < steps ? tp_steps - 1 : -1;
     int cur = 0;  // sorted map the scatter of this step writes
@@ -1883,6 +1912,15 @@ static int walk_enqueue(nd_sampler *s, int mode) {
 }
 
 int nd_walk_sample(nd_sampler *s, int mode) {
+  // the count of walks that can start is waited for here, outside any stream capture, the first
+  // time a step loop is laid out after the seeds were set
+  if (s->h_active && s->active_starts < 0 && s->active_done) {
+    const bool lays_out = s->stream != nullptr && s->stream != cudaStreamLegacy && s->stream != cudaStreamPerThread &&
+                          !s->timer.on && !s->graph_off && !s->graph_exec[mode];   // about to capture this mode's loop
+    const cudaError_t ready = lays_out ? cudaEventSynchronize(s->active_done) : cudaEventQuery(s->active_done);
+    if (ready == cudaSuccess) s->active_starts = *s->h_active;
+    else cudaGetLastError();   // not there yet: this (uncaptured) run is laid out by the number of samples
+  }
   // Graph replay needs a capturable stream (not the legacy default stream) and no phase timers.
   const bool capturable = s->stream != nullptr && s->stream != cudaStreamLegacy && s->stream != cudaStreamPerThread;
   if (!capturable || s->timer.on || s->graph_off) return walk_enqueue(s, mode);

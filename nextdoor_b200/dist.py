@@ -55,7 +55,7 @@ def balanced_bounds(weights, world: int):
     return [0] + inner + [total]
 
 
-IDLE_WALK_WEIGHT = 1.0 / 7   # measured on the 2^24-vertex PPR job cut 4 and 8 ways: the value that levels the ranks' times
+IDLE_WALK_WEIGHT = 1.0 / 20  # measured on the 2^24-vertex PPR job cut 4 and 8 ways: the value that levels the ranks' times
 
 
 def walk_start_weights(graph: "api.Graph", initial, idle: float = IDLE_WALK_WEIGHT):

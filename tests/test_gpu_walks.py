@@ -192,7 +192,7 @@ def test_shards_concatenate_to_the_single_gpu_answer(nd, ndo, small_graph):
 
 def test_balanced_seed_ranges_concatenate_to_the_single_gpu_answer(nd, ndo, small_graph):
     """Seed ranges cut where the expected work is equal (walks from vertices without neighbours
-    weigh a seventh): the weights come from the device's row offsets, and the shards still
+    weigh a twentieth): the weights come from the device's row offsets, and the shards still
     concatenate to the unsharded job."""
     import torch
     from nextdoor_b200 import dist as nd_dist
