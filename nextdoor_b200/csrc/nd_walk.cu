@@ -1032,7 +1032,7 @@ __device__ __forceinline__ void vertex_of(const WalkParams &wp, int32_t v, int32
 // The tail of a job whose walks end early (PPR): once few walks are still alive, a step of the
 // transit-parallel loop is three launches whose fixed cost outweighs the per-pair work.  From
 // there on one launch finishes the job, a lane per walk: a lane takes a pair of the sorted map
-// (next free index of a device counter, so that the lanes end together) and walks its sample to
+// (a batch of indices per warp from a device counter, so that the lanes end together) and walks its sample to
 // the end; a warp makes one round of tries per trip as walk_sp_rounds_kernel does, and a lane
 // whose walk ended takes the next pair.  The draws are keyed by (sample, step), so the samples are
 // the ones the step-by-step loop would have produced.
@@ -1053,23 +1053,37 @@ walk_tail_kernel(NdGraphView g, WalkParams wp, int first_step, int64_t first_sam
   const ndmem::Keep keep;
   const int n = *d_n;
   const int lane = threadIdx.x & 31;
+  constexpr int TAIL_BATCH = 64;   // at least the 32 indices one trip can ask for
   bool have = false, fresh = true, done = false;
   int32_t s = 0, cur = 0, rs = 0, deg = 0, had = 0;
   int step = 0, rounds = 0;
+  int w_cur = 0, w_end = 0;
   float max_w = 0.f;
   int32_t *row = nullptr;
   unsigned int edges = 0, live = 0;
   Rng rng(wp.seed, 0u, 0u, 0u);
   while (true) {
-    // the lanes without a walk draw consecutive pair indices with one atomic
+    // The lanes without a walk take the next pair indices of the warp's batch; the warp draws a
+    // batch of TAIL_BATCH indices from the device counter when the batch runs out.  (Some lane's
+    // walk ends in almost every trip, and an atomic with its round trip to the L2 in every trip
+    // doubled the trip: the 1 M-pair tail of the 2^24-vertex job took 0.75 ms with one atomic per
+    // trip.)  w_cur / w_end are the same in all lanes.
     const unsigned want = __ballot_sync(0xffffffffu, !done && !have);
     if (want) {
-      const int leader = __ffs(want) - 1;
-      int base = 0;
-      if (lane == leader) base = atomicAdd(next_pair, __popc(want));
-      base = __shfl_sync(0xffffffffu, base, leader);
+      const int need = __popc(want), avail = w_end - w_cur;
+      const int my = __popc(want & ((1u << lane) - 1u));
+      int i = w_cur + my;
+      if (need <= avail) {
+        w_cur += need;
+      } else {
+        int nb = 0;
+        if (lane == 0) nb = atomicAdd(next_pair, TAIL_BATCH);
+        nb = __shfl_sync(0xffffffffu, nb, 0);
+        if (my >= avail) i = nb + (my - avail);
+        w_cur = nb + (need - avail);
+        w_end = nb + TAIL_BATCH;
+      }
       if (!done && !have) {
-        const int i = base + __popc(want & ((1u << lane) - 1u));
         if (i >= n) {
           done = true;
         } else {
