@@ -41,6 +41,24 @@ def test_host_only_helpers(lib):
     assert total == 56944
 
 
+@pytest.mark.parametrize("threads", ["1", "3", "16"])
+def test_host_fill_and_row_helpers(lib, monkeypatch, threads):
+    """The host-side helpers of the row-prefix result path run without a device: the threaded fill
+    (thread counts that do not divide the length, lengths below the thread count) and the scratch
+    size of nd_rows_unpack; the update calls refuse a null sampler."""
+    from nextdoor_b200 import api
+    monkeypatch.setenv("ND_HOST_THREADS", threads)
+    for n in (0, 1, 2, 7, 1000, 100003):
+        a = np.full(n + 2, -5, np.int32)
+        api.host_fill(a[1:n + 1], 42)
+        assert (a[1:n + 1] == 42).all() and a[0] == -5 and a[n + 1] == -5
+    assert lib.lib.nd_host_fill_int32(None, 4, 1) == 1
+    assert api.rows_scratch_words(0) == 1 and api.rows_scratch_words(1) == 2
+    assert api.rows_scratch_words(4096) == 2 and api.rows_scratch_words(4097) == 3
+    assert lib.lib.nd_sampler_host_update_begin(None, None, None, None) == 1
+    assert lib.lib.nd_sampler_pack_rows(None, None, None) == 1
+
+
 def test_struct_layout_matches_oracle(lib, ndo):
     a, b = lib.AppParams, ndo.Params
     assert C.sizeof(a) == C.sizeof(b)
